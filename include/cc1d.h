@@ -1,0 +1,193 @@
+/*
+ * cc1d.h — C ABI of the B200 (sm_100a) causal depthwise conv1d kernels.
+ *
+ * Every entry point takes a plain-old-data parameter block and a CUDA stream,
+ * launches on the *current* device, allocates nothing, never synchronises and
+ * returns an int status (CC1D_OK == 0).  All strides are in ELEMENTS (not bytes)
+ * and are 64-bit.  Pointers are device pointers unless stated otherwise.
+ *
+ * Each entry point replaces one host function + kernel family of the reference
+ * (Dao-AILab/causal-conv1d v1.6.1); the replaced interface is cited above it.
+ */
+#ifndef CC1D_H_
+#define CC1D_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque stream handle: pass a cudaStream_t (0 == legacy default stream). */
+typedef void *cc1d_stream_t;
+
+typedef enum cc1d_dtype {
+    CC1D_F32 = 0,
+    CC1D_F16 = 1,
+    CC1D_BF16 = 2
+} cc1d_dtype;
+
+typedef enum cc1d_status {
+    CC1D_OK = 0,
+    CC1D_ERR_NULL = 1,          /* a required pointer is NULL                        */
+    CC1D_ERR_DTYPE = 2,         /* dtype enum out of range                           */
+    CC1D_ERR_WIDTH = 3,         /* width not in {2,3,4}                              */
+    CC1D_ERR_SHAPE = 4,         /* negative size / inconsistent sizes                */
+    CC1D_ERR_STRIDE = 5,        /* neither the channel nor the seqlen stride is 1    */
+    CC1D_ERR_CL_DIM = 6,        /* channel-last needs dim % 8 == 0                   */
+    CC1D_ERR_CL_STRIDE = 7,     /* channel-last needs batch/seqlen strides % 8 == 0  */
+    CC1D_ERR_LAYOUT = 8,        /* seq_idx / states given with channel-first x       */
+    CC1D_ERR_STATE_STRIDE = 9,  /* a state tensor needs channel stride 1             */
+    CC1D_ERR_STATE_LEN = 10,    /* conv_state_len < width - 1                        */
+    CC1D_ERR_WORKSPACE = 11,    /* workspace missing or too small                    */
+    CC1D_ERR_ALIGN = 12,        /* pointer not aligned for its element type          */
+    CC1D_ERR_TOO_LARGE = 13,    /* problem exceeds an internal index range           */
+    CC1D_ERR_LAUNCH = 14        /* the CUDA launch itself failed (see cudaGetLastError) */
+} cc1d_status;
+
+/* ---------------------------------------------------------------------------
+ * Forward.  Replaces causal_conv1d_fwd() (csrc/causal_conv1d.cpp:149-258) and
+ * the kernels behind it (csrc/causal_conv1d_fwd.cu:46-137 channel-first,
+ * :205-348 channel-last); the block mirrors ConvParamsBase
+ * (csrc/causal_conv1d.h:9-54).
+ *
+ *   out[b,c,t] = act(bias[c] + sum_w weight[c,w] * x[b,c,t-(width-1-w)])
+ *
+ * Layout rule (csrc/causal_conv1d.cpp:176): channel-last iff
+ * x_c_stride == 1 && x_l_stride > 1, otherwise channel-first (x_l_stride == 1).
+ * seq_idx, initial_states and final_states are channel-last only.
+ * ------------------------------------------------------------------------- */
+typedef struct cc1d_fwd_params {
+    int32_t itype;            /* cc1d_dtype of x, out, states                   */
+    int32_t wtype;            /* cc1d_dtype of weight and bias                  */
+    int32_t width;            /* 2, 3 or 4                                      */
+    int32_t silu;             /* 0: identity, 1: SiLU                           */
+    int64_t batch, dim, seqlen;
+
+    const void *x;            /* (batch, dim, seqlen)                           */
+    int64_t x_batch_stride, x_c_stride, x_l_stride;
+    const void *weight;       /* (dim, width)                                   */
+    int64_t weight_c_stride, weight_width_stride;
+    const void *bias;         /* (dim,) contiguous, or NULL                     */
+    void *out;                /* (batch, dim, seqlen), same layout class as x   */
+    int64_t out_batch_stride, out_c_stride, out_l_stride;
+
+    const int32_t *seq_idx;   /* (batch, seqlen) contiguous int32, or NULL      */
+    const void *initial_states; /* (batch, dim, width-1), c stride 1, or NULL   */
+    int64_t initial_states_batch_stride, initial_states_c_stride, initial_states_l_stride;
+    void *final_states;       /* (batch, dim, width-1), c stride 1, or NULL     */
+    int64_t final_states_batch_stride, final_states_c_stride, final_states_l_stride;
+} cc1d_fwd_params;
+
+int cc1d_fwd(const cc1d_fwd_params *p, cc1d_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * Backward.  Replaces causal_conv1d_bwd() (csrc/causal_conv1d.cpp:260-463) and
+ * its kernels (csrc/causal_conv1d_bwd.cu:53-259 channel-first, :329-589
+ * channel-last); the block mirrors ConvParamsBwd (csrc/causal_conv1d.h:56-88).
+ *
+ * dweight / dbias are fp32.  They are produced by a fixed-order reduction
+ * (warp shuffle tree -> per-CTA partial rows in `workspace` -> one finishing
+ * kernel), never by float atomics, so results are bitwise run-to-run
+ * reproducible — the behaviour the reference only offers under
+ * CAUSAL_CONV1D_DETERMINISTIC=1 (csrc/causal_conv1d.cpp:21-28,388-462).
+ * With accumulate != 0 the finishing kernel adds to the existing contents of
+ * dweight/dbias (the reference's contract: the caller zero-fills them,
+ * causal_conv1d/cpp_functions.py:134-137); with accumulate == 0 it overwrites.
+ * ------------------------------------------------------------------------- */
+typedef struct cc1d_bwd_params {
+    int32_t itype, wtype, width, silu;
+    int64_t batch, dim, seqlen;
+
+    const void *x;
+    int64_t x_batch_stride, x_c_stride, x_l_stride;
+    const void *weight;
+    int64_t weight_c_stride, weight_width_stride;
+    const void *bias;         /* may be NULL                                    */
+    const void *dout;         /* same layout class as x                         */
+    int64_t dout_batch_stride, dout_c_stride, dout_l_stride;
+    void *dx;                 /* same layout class as x                         */
+    int64_t dx_batch_stride, dx_c_stride, dx_l_stride;
+    float *dweight;           /* (dim, width) fp32                              */
+    int64_t dweight_c_stride, dweight_width_stride;
+    float *dbias;             /* (dim,) fp32 contiguous, or NULL                */
+    int32_t accumulate;       /* see above                                      */
+    int32_t reserved0;
+
+    const int32_t *seq_idx;
+    const void *initial_states;
+    int64_t initial_states_batch_stride, initial_states_c_stride, initial_states_l_stride;
+    const void *dfinal_states;   /* (batch, dim, width-1), any strides, or NULL */
+    int64_t dfinal_states_batch_stride, dfinal_states_c_stride, dfinal_states_l_stride;
+    void *dinitial_states;       /* (batch, dim, width-1), c stride 1, or NULL  */
+    int64_t dinitial_states_batch_stride, dinitial_states_c_stride, dinitial_states_l_stride;
+
+    void *workspace;          /* >= cc1d_bwd_workspace_bytes() bytes, 16-B aligned, need not be zeroed */
+    size_t workspace_bytes;
+} cc1d_bwd_params;
+
+/* Bytes of scratch cc1d_bwd needs for this problem (host-only arithmetic).
+ * Returns 0 on invalid parameters. */
+size_t cc1d_bwd_workspace_bytes(const cc1d_bwd_params *p);
+int cc1d_bwd(const cc1d_bwd_params *p, cc1d_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * Decode-step state update.  Replaces causal_conv1d_update()
+ * (csrc/causal_conv1d.cpp:465-557) and causal_conv1d_update_kernel
+ * (csrc/causal_conv1d_update.cu:23-114).  conv_state is updated in place.
+ * cache_seqlens != NULL selects the circular-buffer mode;
+ * conv_state_indices != NULL gathers the state row per batch entry, a negative
+ * index marks a padded entry: its outputs are zero and no state is touched.
+ * ------------------------------------------------------------------------- */
+typedef struct cc1d_update_params {
+    int32_t itype, wtype, width, silu;
+    int64_t batch, dim, seqlen;
+
+    const void *x;            /* (batch, dim, seqlen), any strides              */
+    int64_t x_batch_stride, x_c_stride, x_l_stride;
+    const void *weight;
+    int64_t weight_c_stride, weight_width_stride;
+    const void *bias;
+    void *out;                /* (batch, dim, seqlen), any strides              */
+    int64_t out_batch_stride, out_c_stride, out_l_stride;
+
+    void *conv_state;         /* (entries, dim, conv_state_len), any strides    */
+    int64_t conv_state_len;
+    int64_t conv_state_batch_stride, conv_state_c_stride, conv_state_l_stride;
+    const int32_t *cache_seqlens;       /* (batch,) or NULL                     */
+    const int32_t *conv_state_indices;  /* (batch,) or NULL                     */
+} cc1d_update_params;
+
+int cc1d_update(const cc1d_update_params *p, cc1d_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * Variable-length "last tokens -> conv state" gather.  Replaces the Triton
+ * kernel _causal_conv1d_varlen_states and its wrapper
+ * (causal_conv1d/causal_conv1d_varlen.py:8-32, :35-64):
+ *   n = min(state_len, cu[b+1]-cu[b]);
+ *   states[b, :, state_len-n:] = x[cu[b+1]-n : cu[b+1], :].T ; the rest is 0.
+ * ------------------------------------------------------------------------- */
+typedef struct cc1d_varlen_states_params {
+    int32_t itype;
+    int32_t cu_seqlens_is_int64;  /* 0: int32 cu_seqlens, 1: int64              */
+    int64_t total_tokens, dim, batch, state_len;
+    const void *x;                /* (total_tokens, dim)                         */
+    int64_t x_l_stride, x_c_stride;
+    const void *cu_seqlens;       /* (batch + 1,) contiguous                     */
+    void *states;                 /* (batch, dim, state_len)                     */
+    int64_t states_batch_stride, states_c_stride, states_l_stride;
+} cc1d_varlen_states_params;
+
+int cc1d_varlen_states(const cc1d_varlen_states_params *p, cc1d_stream_t stream);
+
+/* Human-readable text for a status code (static storage, never NULL). */
+const char *cc1d_status_str(int status);
+
+/* Library ABI version: bumped when a parameter block changes layout. */
+int cc1d_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CC1D_H_ */

@@ -1,0 +1,274 @@
+// PyTorch extension: the host side of the reference's pybind module `causal_conv1d_cuda`
+// (csrc/causal_conv1d.cpp:559-563 — causal_conv1d_fwd / _bwd / _update, same argument
+// lists) plus causal_conv1d_varlen_states.  It only inspects tensors, fills the C-ABI
+// parameter blocks of include/cc1d.h and calls libcc1d.so on the current stream of the
+// tensors' device.  No kernels live here and there is no CPU path: a non-CUDA tensor is an
+// error.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <optional>
+
+#include "cc1d.h"
+
+namespace {
+
+using OptTensor = std::optional<at::Tensor>;
+
+int dtype_code(const at::Tensor &t, const char *what) {
+    switch (t.scalar_type()) {
+        case at::ScalarType::Float: return CC1D_F32;
+        case at::ScalarType::Half: return CC1D_F16;
+        case at::ScalarType::BFloat16: return CC1D_BF16;
+        default: TORCH_CHECK(false, what, " must be float32, float16 or bfloat16, got ", t.scalar_type());
+    }
+}
+
+void need_cuda(const at::Tensor &t, const char *what) {
+    TORCH_CHECK(t.is_cuda(), what, " must be a CUDA tensor (this build has no CPU path)");
+}
+
+void need_shape(const at::Tensor &t, at::IntArrayRef shape, const char *what) {
+    TORCH_CHECK(t.sizes() == shape, what, " must have shape ", shape, ", got ", t.sizes());
+}
+
+void raise_on(int rc, const char *fn) {
+    TORCH_CHECK(rc == CC1D_OK, fn, ": ", cc1d_status_str(rc));
+}
+
+struct ConvDims {
+    int64_t batch, dim, seqlen, width;
+};
+
+ConvDims conv_dims(const at::Tensor &x, const at::Tensor &weight) {
+    TORCH_CHECK(x.dim() == 3, "x must be (batch, dim, seqlen)");
+    TORCH_CHECK(weight.dim() == 2, "weight must be (dim, width)");
+    ConvDims d{x.size(0), x.size(1), x.size(2), weight.size(1)};
+    need_shape(weight, {d.dim, d.width}, "weight");
+    TORCH_CHECK(d.width >= 2 && d.width <= 4, "causal_conv1d only supports width between 2 and 4");
+    return d;
+}
+
+const void *bias_ptr(const OptTensor &bias, const at::Tensor &weight, int64_t dim) {
+    if (!bias.has_value()) return nullptr;
+    const at::Tensor &b = *bias;
+    need_cuda(b, "bias");
+    TORCH_CHECK(b.scalar_type() == weight.scalar_type(), "bias must have the dtype of weight");
+    need_shape(b, {dim}, "bias");
+    TORCH_CHECK(b.stride(-1) == 1 || dim <= 1, "bias must be contiguous");
+    return b.data_ptr();
+}
+
+const int32_t *seq_idx_ptr(const OptTensor &seq_idx, const ConvDims &d) {
+    if (!seq_idx.has_value()) return nullptr;
+    const at::Tensor &s = *seq_idx;
+    need_cuda(s, "seq_idx");
+    TORCH_CHECK(s.scalar_type() == at::kInt, "seq_idx must be int32");
+    TORCH_CHECK(s.is_contiguous(), "seq_idx must be contiguous");
+    need_shape(s, {d.batch, d.seqlen}, "seq_idx");
+    return s.data_ptr<int32_t>();
+}
+
+// (batch, dim, width-1) state tensor of x's dtype
+void check_state(const at::Tensor &t, const at::Tensor &x, const ConvDims &d, const char *what) {
+    need_cuda(t, what);
+    TORCH_CHECK(t.scalar_type() == x.scalar_type(), what, " must have the dtype of x");
+    need_shape(t, {d.batch, d.dim, d.width - 1}, what);
+}
+
+bool channel_last(const at::Tensor &x) { return x.stride(1) == 1 && x.stride(2) > 1; }
+
+}  // namespace
+
+void causal_conv1d_fwd(const at::Tensor &x, const at::Tensor &weight, const OptTensor &bias_,
+                       const OptTensor &seq_idx_, const OptTensor &initial_states_, at::Tensor &out,
+                       OptTensor &final_states_out_, bool silu_activation) {
+    need_cuda(x, "x"); need_cuda(weight, "weight"); need_cuda(out, "out");
+    const ConvDims d = conv_dims(x, weight);
+    need_shape(out, {d.batch, d.dim, d.seqlen}, "out");
+    TORCH_CHECK(out.scalar_type() == x.scalar_type(), "out must have the dtype of x");
+    TORCH_CHECK(x.stride(2) == 1 || x.stride(1) == 1, "x must be contiguous along seqlen or along dim");
+
+    cc1d_fwd_params p = {};
+    p.itype = dtype_code(x, "x"); p.wtype = dtype_code(weight, "weight");
+    p.width = (int32_t)d.width; p.silu = silu_activation;
+    p.batch = d.batch; p.dim = d.dim; p.seqlen = d.seqlen;
+    p.x = x.data_ptr(); p.x_batch_stride = x.stride(0); p.x_c_stride = x.stride(1); p.x_l_stride = x.stride(2);
+    p.weight = weight.data_ptr(); p.weight_c_stride = weight.stride(0); p.weight_width_stride = weight.stride(1);
+    p.bias = bias_ptr(bias_, weight, d.dim);
+    p.out = out.data_ptr(); p.out_batch_stride = out.stride(0); p.out_c_stride = out.stride(1); p.out_l_stride = out.stride(2);
+    p.seq_idx = seq_idx_ptr(seq_idx_, d);
+    const bool cl = channel_last(x);
+    if (seq_idx_.has_value()) TORCH_CHECK(cl, "seq_idx is only supported for channel last layout");
+    if (initial_states_.has_value()) {
+        TORCH_CHECK(cl, "initial_states is only supported for channel last layout");
+        const at::Tensor &s = *initial_states_;
+        check_state(s, x, d, "initial_states");
+        TORCH_CHECK(s.stride(1) == 1, "initial_states must have stride(1) == 1");
+        p.initial_states = s.data_ptr();
+        p.initial_states_batch_stride = s.stride(0); p.initial_states_c_stride = s.stride(1); p.initial_states_l_stride = s.stride(2);
+    }
+    if (final_states_out_.has_value()) {
+        TORCH_CHECK(cl, "final_states is only supported for channel last layout");
+        at::Tensor &s = *final_states_out_;
+        check_state(s, x, d, "final_states_out");
+        TORCH_CHECK(s.stride(1) == 1, "final_states_out must have stride(1) == 1");
+        p.final_states = s.data_ptr();
+        p.final_states_batch_stride = s.stride(0); p.final_states_c_stride = s.stride(1); p.final_states_l_stride = s.stride(2);
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    raise_on(cc1d_fwd(&p, at::cuda::getCurrentCUDAStream().stream()), "causal_conv1d_fwd");
+}
+
+void causal_conv1d_bwd(const at::Tensor &x, const at::Tensor &weight, const OptTensor &bias_, at::Tensor &dout,
+                       const OptTensor &seq_idx_, const OptTensor &initial_states_, const OptTensor &dfinal_states_,
+                       at::Tensor &dx, at::Tensor &dweight, OptTensor &dbias_, OptTensor &dinitial_states_,
+                       bool silu_activation, bool accumulate) {
+    need_cuda(x, "x"); need_cuda(weight, "weight"); need_cuda(dout, "dout"); need_cuda(dx, "dx"); need_cuda(dweight, "dweight");
+    TORCH_CHECK(bias_.has_value() == dbias_.has_value(), "dbias must be given exactly when bias is");
+    const ConvDims d = conv_dims(x, weight);
+    need_shape(dout, {d.batch, d.dim, d.seqlen}, "dout");
+    need_shape(dx, {d.batch, d.dim, d.seqlen}, "dx");
+    need_shape(dweight, {d.dim, d.width}, "dweight");
+    TORCH_CHECK(dout.scalar_type() == x.scalar_type() && dx.scalar_type() == x.scalar_type(), "dout and dx must have the dtype of x");
+    TORCH_CHECK(dweight.scalar_type() == at::kFloat, "dweight must be float32");
+    TORCH_CHECK(x.stride(2) == 1 || x.stride(1) == 1, "x must be contiguous along seqlen or along dim");
+    const bool cl = channel_last(x);
+    // bring dout into x's layout class if autograd handed over a different one
+    at::Tensor dout_l = dout;
+    if (!cl && dout.stride(2) != 1) dout_l = dout.contiguous();
+    if (cl && dout.stride(1) != 1) dout_l = dout.transpose(-1, -2).contiguous().transpose(-1, -2);
+    if (!cl) TORCH_CHECK(dx.stride(2) == 1 || d.seqlen <= 1, "dx must be contiguous along seqlen");
+    if (cl) TORCH_CHECK(dx.stride(1) == 1 || d.dim <= 1, "dx must be contiguous along dim");
+
+    cc1d_bwd_params p = {};
+    p.itype = dtype_code(x, "x"); p.wtype = dtype_code(weight, "weight");
+    p.width = (int32_t)d.width; p.silu = silu_activation;
+    p.batch = d.batch; p.dim = d.dim; p.seqlen = d.seqlen;
+    p.x = x.data_ptr(); p.x_batch_stride = x.stride(0); p.x_c_stride = x.stride(1); p.x_l_stride = x.stride(2);
+    p.weight = weight.data_ptr(); p.weight_c_stride = weight.stride(0); p.weight_width_stride = weight.stride(1);
+    p.bias = bias_ptr(bias_, weight, d.dim);
+    p.dout = dout_l.data_ptr(); p.dout_batch_stride = dout_l.stride(0); p.dout_c_stride = dout_l.stride(1); p.dout_l_stride = dout_l.stride(2);
+    p.dx = dx.data_ptr(); p.dx_batch_stride = dx.stride(0); p.dx_c_stride = dx.stride(1); p.dx_l_stride = dx.stride(2);
+    p.dweight = dweight.data_ptr<float>(); p.dweight_c_stride = dweight.stride(0); p.dweight_width_stride = dweight.stride(1);
+    if (dbias_.has_value()) {
+        at::Tensor &db = *dbias_;
+        need_cuda(db, "dbias");
+        TORCH_CHECK(db.scalar_type() == at::kFloat, "dbias must be float32");
+        need_shape(db, {d.dim}, "dbias");
+        TORCH_CHECK(db.stride(0) == 1 || d.dim <= 1, "dbias must be contiguous");
+        p.dbias = db.data_ptr<float>();
+    }
+    p.accumulate = accumulate;
+    p.seq_idx = seq_idx_ptr(seq_idx_, d);
+    if (seq_idx_.has_value()) TORCH_CHECK(cl, "seq_idx only supported for channel last layout");
+    if (initial_states_.has_value()) {
+        TORCH_CHECK(cl, "initial_states is only supported for channel last layout");
+        const at::Tensor &s = *initial_states_;
+        check_state(s, x, d, "initial_states");
+        TORCH_CHECK(s.stride(1) == 1, "initial_states must have stride(1) == 1");
+        p.initial_states = s.data_ptr();
+        p.initial_states_batch_stride = s.stride(0); p.initial_states_c_stride = s.stride(1); p.initial_states_l_stride = s.stride(2);
+    }
+    if (dfinal_states_.has_value()) {
+        TORCH_CHECK(cl, "dfinal_states is only supported for channel last layout");
+        const at::Tensor &s = *dfinal_states_;
+        check_state(s, x, d, "dfinal_states");
+        p.dfinal_states = s.data_ptr();
+        p.dfinal_states_batch_stride = s.stride(0); p.dfinal_states_c_stride = s.stride(1); p.dfinal_states_l_stride = s.stride(2);
+    }
+    if (dinitial_states_.has_value()) {
+        TORCH_CHECK(cl, "dinitial_states is only supported for channel last layout");
+        at::Tensor &s = *dinitial_states_;
+        check_state(s, x, d, "dinitial_states");
+        TORCH_CHECK(s.stride(1) == 1, "dinitial_states must have stride(1) == 1");
+        p.dinitial_states = s.data_ptr();
+        p.dinitial_states_batch_stride = s.stride(0); p.dinitial_states_c_stride = s.stride(1); p.dinitial_states_l_stride = s.stride(2);
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    // scratch for the fixed-order dweight/dbias reduction, from torch's caching allocator
+    const size_t ws_bytes = cc1d_bwd_workspace_bytes(&p);
+    at::Tensor ws = at::empty({(int64_t)ws_bytes}, x.options().dtype(at::kByte));
+    p.workspace = ws.data_ptr();
+    p.workspace_bytes = ws_bytes;
+    raise_on(cc1d_bwd(&p, at::cuda::getCurrentCUDAStream().stream()), "causal_conv1d_bwd");
+}
+
+void causal_conv1d_update(const at::Tensor &x, const at::Tensor &conv_state, const at::Tensor &weight,
+                          const OptTensor &bias_, at::Tensor &out, bool silu_activation,
+                          const OptTensor &cache_seqlens_, const OptTensor &conv_state_indices_) {
+    need_cuda(x, "x"); need_cuda(conv_state, "conv_state"); need_cuda(weight, "weight"); need_cuda(out, "out");
+    const ConvDims d = conv_dims(x, weight);
+    TORCH_CHECK(conv_state.dim() == 3, "conv_state must be (batch, dim, state_len)");
+    TORCH_CHECK(conv_state.scalar_type() == x.scalar_type(), "conv_state must have the dtype of x");
+    const int64_t state_len = conv_state.size(2);
+    TORCH_CHECK(state_len >= d.width - 1, "conv_state_len must be >= width - 1");
+    need_shape(out, {d.batch, d.dim, d.seqlen}, "out");
+    TORCH_CHECK(out.scalar_type() == x.scalar_type(), "out must have the dtype of x");
+
+    cc1d_update_params p = {};
+    p.itype = dtype_code(x, "x"); p.wtype = dtype_code(weight, "weight");
+    p.width = (int32_t)d.width; p.silu = silu_activation;
+    p.batch = d.batch; p.dim = d.dim; p.seqlen = d.seqlen;
+    p.x = x.data_ptr(); p.x_batch_stride = x.stride(0); p.x_c_stride = x.stride(1); p.x_l_stride = x.stride(2);
+    p.weight = weight.data_ptr(); p.weight_c_stride = weight.stride(0); p.weight_width_stride = weight.stride(1);
+    p.bias = bias_ptr(bias_, weight, d.dim);
+    p.out = out.data_ptr(); p.out_batch_stride = out.stride(0); p.out_c_stride = out.stride(1); p.out_l_stride = out.stride(2);
+    p.conv_state = conv_state.data_ptr(); p.conv_state_len = state_len;
+    p.conv_state_batch_stride = conv_state.stride(0); p.conv_state_c_stride = conv_state.stride(1); p.conv_state_l_stride = conv_state.stride(2);
+    if (conv_state_indices_.has_value()) {
+        const at::Tensor &idx = *conv_state_indices_;
+        need_cuda(idx, "conv_state_indices");
+        TORCH_CHECK(idx.scalar_type() == at::kInt, "conv_state_indices must be int32");
+        need_shape(idx, {d.batch}, "conv_state_indices");
+        TORCH_CHECK(idx.stride(0) == 1 || d.batch <= 1, "conv_state_indices must be contiguous");
+        need_shape(conv_state, {conv_state.size(0), d.dim, state_len}, "conv_state");
+        p.conv_state_indices = idx.data_ptr<int32_t>();
+    } else {
+        need_shape(conv_state, {d.batch, d.dim, state_len}, "conv_state");
+    }
+    if (cache_seqlens_.has_value()) {
+        const at::Tensor &cs = *cache_seqlens_;
+        need_cuda(cs, "cache_seqlens");
+        TORCH_CHECK(cs.scalar_type() == at::kInt, "cache_seqlens must be int32");
+        need_shape(cs, {d.batch}, "cache_seqlens");
+        TORCH_CHECK(cs.stride(-1) == 1 || d.batch <= 1, "cache_seqlens must be contiguous");
+        p.cache_seqlens = cs.data_ptr<int32_t>();
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    raise_on(cc1d_update(&p, at::cuda::getCurrentCUDAStream().stream()), "causal_conv1d_update");
+}
+
+// x: (total_tokens, dim); cu_seqlens: (batch + 1,) int32 or int64; states: (batch, dim, state_len)
+void causal_conv1d_varlen_states(const at::Tensor &x, const at::Tensor &cu_seqlens, at::Tensor &states) {
+    need_cuda(x, "x"); need_cuda(cu_seqlens, "cu_seqlens"); need_cuda(states, "states");
+    TORCH_CHECK(x.dim() == 2 && states.dim() == 3 && cu_seqlens.dim() == 1, "expected x (tokens, dim), cu_seqlens (batch+1,), states (batch, dim, state_len)");
+    TORCH_CHECK(cu_seqlens.scalar_type() == at::kInt || cu_seqlens.scalar_type() == at::kLong, "cu_seqlens must be int32 or int64");
+    TORCH_CHECK(cu_seqlens.is_contiguous(), "cu_seqlens must be contiguous");
+    TORCH_CHECK(states.scalar_type() == x.scalar_type(), "states must have the dtype of x");
+    const int64_t batch = cu_seqlens.size(0) - 1;
+    need_shape(states, {batch, x.size(1), states.size(2)}, "states");
+    cc1d_varlen_states_params p = {};
+    p.itype = dtype_code(x, "x");
+    p.cu_seqlens_is_int64 = cu_seqlens.scalar_type() == at::kLong;
+    p.total_tokens = x.size(0); p.dim = x.size(1); p.batch = batch; p.state_len = states.size(2);
+    p.x = x.data_ptr(); p.x_l_stride = x.stride(0); p.x_c_stride = x.stride(1);
+    p.cu_seqlens = cu_seqlens.data_ptr();
+    p.states = states.data_ptr();
+    p.states_batch_stride = states.stride(0); p.states_c_stride = states.stride(1); p.states_l_stride = states.stride(2);
+    c10::cuda::CUDAGuard guard(x.device());
+    raise_on(cc1d_varlen_states(&p, at::cuda::getCurrentCUDAStream().stream()), "causal_conv1d_varlen_states");
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("causal_conv1d_fwd", &causal_conv1d_fwd, "Causal conv1d forward");
+    m.def("causal_conv1d_bwd", &causal_conv1d_bwd, "Causal conv1d backward",
+          py::arg("x"), py::arg("weight"), py::arg("bias"), py::arg("dout"), py::arg("seq_idx"),
+          py::arg("initial_states"), py::arg("dfinal_states"), py::arg("dx"), py::arg("dweight"),
+          py::arg("dbias"), py::arg("dinitial_states"), py::arg("silu_activation"),
+          py::arg("accumulate") = true);
+    m.def("causal_conv1d_update", &causal_conv1d_update, "Causal conv1d update");
+    m.def("causal_conv1d_varlen_states", &causal_conv1d_varlen_states, "Last tokens of each packed sequence -> conv state");
+    m.def("abi_version", []() { return cc1d_abi_version(); });
+}

@@ -1,0 +1,163 @@
+// extern "C" entry points declared in include/cc1d.h: parameter validation (the checks the
+// reference does with TORCH_CHECK in csrc/causal_conv1d.cpp) and hand-off to the launchers.
+#include <cuda_runtime.h>
+
+#include "cc1d.h"
+#include "cc1d_kernels.h"
+
+namespace cc1d {
+
+int num_sms() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+namespace {
+
+bool bad_dtype(int d) { return d != CC1D_F32 && d != CC1D_F16 && d != CC1D_BF16; }
+bool elem_aligned(const void *p, int dtype) {
+    return (reinterpret_cast<uintptr_t>(p) % (uintptr_t)elem_size(dtype)) == 0;
+}
+
+// Shared front checks; sets *channel_last by the reference's rule
+// (csrc/causal_conv1d.cpp:175-181).
+int check_conv_common(int itype, int wtype, int width, int64_t batch, int64_t dim, int64_t seqlen,
+                      const void *x, int64_t x_bs, int64_t x_cs, int64_t x_ls, const void *weight,
+                      bool *channel_last) {
+    if (bad_dtype(itype) || bad_dtype(wtype)) return CC1D_ERR_DTYPE;
+    if (width < 2 || width > 4) return CC1D_ERR_WIDTH;
+    if (batch < 0 || dim < 0 || seqlen < 0) return CC1D_ERR_SHAPE;
+    if (x == nullptr || weight == nullptr) return CC1D_ERR_NULL;
+    if (x_ls != 1 && x_cs != 1) return CC1D_ERR_STRIDE;
+    if (!elem_aligned(x, itype) || !elem_aligned(weight, wtype)) return CC1D_ERR_ALIGN;
+    *channel_last = x_cs == 1 && x_ls > 1;
+    if (*channel_last) {
+        if (dim % 8 != 0) return CC1D_ERR_CL_DIM;
+        if (x_ls % 8 != 0 || x_bs % 8 != 0) return CC1D_ERR_CL_STRIDE;
+    }
+    return CC1D_OK;
+}
+
+int check_same_layout(bool channel_last, int64_t bs, int64_t cs, int64_t ls, int64_t seqlen, int64_t dim) {
+    if (channel_last) {
+        if (cs != 1 && dim > 1) return CC1D_ERR_STRIDE;
+        if (ls % 8 != 0 || bs % 8 != 0) return CC1D_ERR_CL_STRIDE;
+    } else {
+        if (ls != 1 && seqlen > 1) return CC1D_ERR_STRIDE;
+    }
+    return CC1D_OK;
+}
+
+}  // namespace
+}  // namespace cc1d
+
+using namespace cc1d;
+
+extern "C" {
+
+int cc1d_abi_version(void) { return 1; }
+
+const char *cc1d_status_str(int status) {
+    switch (status) {
+        case CC1D_OK: return "ok";
+        case CC1D_ERR_NULL: return "a required pointer is NULL";
+        case CC1D_ERR_DTYPE: return "unsupported dtype (need float32, float16 or bfloat16)";
+        case CC1D_ERR_WIDTH: return "causal_conv1d only supports width between 2 and 4";
+        case CC1D_ERR_SHAPE: return "invalid or inconsistent sizes";
+        case CC1D_ERR_STRIDE: return "tensor must be contiguous along seqlen (channel-first) or along channels (channel-last), matching x";
+        case CC1D_ERR_CL_DIM: return "causal_conv1d only supports channel dimension divisible by 8 for now";
+        case CC1D_ERR_CL_STRIDE: return "causal_conv1d with channel last layout requires strides (stride(0) and stride(2)) to be multiples of 8";
+        case CC1D_ERR_LAYOUT: return "seq_idx, initial_states and final_states are only supported for channel last layout";
+        case CC1D_ERR_STATE_STRIDE: return "state tensors must have stride(1) == 1";
+        case CC1D_ERR_STATE_LEN: return "conv_state_len must be >= width - 1";
+        case CC1D_ERR_WORKSPACE: return "backward workspace missing or smaller than cc1d_bwd_workspace_bytes()";
+        case CC1D_ERR_ALIGN: return "pointer or stride not aligned for the required access width";
+        case CC1D_ERR_TOO_LARGE: return "problem size exceeds an internal index range";
+        case CC1D_ERR_LAUNCH: return "CUDA kernel launch failed";
+        default: return "unknown cc1d status";
+    }
+}
+
+int cc1d_fwd(const cc1d_fwd_params *p, cc1d_stream_t stream) {
+    if (p == nullptr) return CC1D_ERR_NULL;
+    bool cl = false;
+    int rc = check_conv_common(p->itype, p->wtype, p->width, p->batch, p->dim, p->seqlen, p->x,
+                               p->x_batch_stride, p->x_c_stride, p->x_l_stride, p->weight, &cl);
+    if (rc != CC1D_OK) return rc;
+    if (p->out == nullptr) return CC1D_ERR_NULL;
+    if (!elem_aligned(p->out, p->itype)) return CC1D_ERR_ALIGN;
+    rc = check_same_layout(cl, p->out_batch_stride, p->out_c_stride, p->out_l_stride, p->seqlen, p->dim);
+    if (rc != CC1D_OK) return rc;
+    if (!cl && (p->seq_idx || p->initial_states || p->final_states)) return CC1D_ERR_LAYOUT;
+    if (p->initial_states && p->initial_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
+    if (p->final_states && p->final_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    return cl ? launch_fwd_channel_last(*p, s) : launch_fwd_channel_first(*p, s);
+}
+
+static int check_bwd(const cc1d_bwd_params *p, bool *cl) {
+    if (p == nullptr) return CC1D_ERR_NULL;
+    int rc = check_conv_common(p->itype, p->wtype, p->width, p->batch, p->dim, p->seqlen, p->x,
+                               p->x_batch_stride, p->x_c_stride, p->x_l_stride, p->weight, cl);
+    if (rc != CC1D_OK) return rc;
+    if (p->dout == nullptr || p->dx == nullptr || p->dweight == nullptr) return CC1D_ERR_NULL;
+    if ((p->bias == nullptr) != (p->dbias == nullptr)) return CC1D_ERR_NULL;
+    if (!elem_aligned(p->dout, p->itype) || !elem_aligned(p->dx, p->itype) ||
+        !elem_aligned(p->dweight, CC1D_F32) || !elem_aligned(p->dbias, CC1D_F32)) return CC1D_ERR_ALIGN;
+    rc = check_same_layout(*cl, p->dout_batch_stride, p->dout_c_stride, p->dout_l_stride, p->seqlen, p->dim);
+    if (rc != CC1D_OK) return rc;
+    rc = check_same_layout(*cl, p->dx_batch_stride, p->dx_c_stride, p->dx_l_stride, p->seqlen, p->dim);
+    if (rc != CC1D_OK) return rc;
+    if (!*cl && (p->seq_idx || p->initial_states || p->dfinal_states || p->dinitial_states)) return CC1D_ERR_LAYOUT;
+    if (p->initial_states && p->initial_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
+    if (p->dinitial_states && p->dinitial_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
+    return CC1D_OK;
+}
+
+size_t cc1d_bwd_workspace_bytes(const cc1d_bwd_params *p) {
+    if (p == nullptr || bad_dtype(p->itype) || p->width < 2 || p->width > 4 || p->batch < 0 || p->dim < 0 ||
+        p->seqlen < 0) return 0;
+    const bool cl = p->x_c_stride == 1 && p->x_l_stride > 1;
+    const size_t n = cl ? bwd_workspace_bytes_channel_last(*p) : bwd_workspace_bytes_channel_first(*p);
+    return n < 16 ? 16 : n;   // never 0 for a valid problem, so callers can always allocate
+}
+
+int cc1d_bwd(const cc1d_bwd_params *p, cc1d_stream_t stream) {
+    bool cl = false;
+    const int rc = check_bwd(p, &cl);
+    if (rc != CC1D_OK) return rc;
+    if (p->workspace == nullptr || p->workspace_bytes < cc1d_bwd_workspace_bytes(p)) return CC1D_ERR_WORKSPACE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    return cl ? launch_bwd_channel_last(*p, s) : launch_bwd_channel_first(*p, s);
+}
+
+int cc1d_update(const cc1d_update_params *p, cc1d_stream_t stream) {
+    if (p == nullptr) return CC1D_ERR_NULL;
+    if (bad_dtype(p->itype) || bad_dtype(p->wtype)) return CC1D_ERR_DTYPE;
+    if (p->width < 2 || p->width > 4) return CC1D_ERR_WIDTH;
+    if (p->batch < 0 || p->dim < 0 || p->seqlen < 0 || p->conv_state_len < 0) return CC1D_ERR_SHAPE;
+    if (p->x == nullptr || p->weight == nullptr || p->out == nullptr || p->conv_state == nullptr) return CC1D_ERR_NULL;
+    if (p->conv_state_len < p->width - 1) return CC1D_ERR_STATE_LEN;
+    if (!elem_aligned(p->x, p->itype) || !elem_aligned(p->out, p->itype) || !elem_aligned(p->conv_state, p->itype) ||
+        !elem_aligned(p->weight, p->wtype)) return CC1D_ERR_ALIGN;
+    return launch_update(*p, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cc1d_varlen_states(const cc1d_varlen_states_params *p, cc1d_stream_t stream) {
+    if (p == nullptr) return CC1D_ERR_NULL;
+    if (bad_dtype(p->itype)) return CC1D_ERR_DTYPE;
+    if (p->total_tokens < 0 || p->dim < 0 || p->batch < 0 || p->state_len < 0) return CC1D_ERR_SHAPE;
+    if (p->batch == 0 || p->dim == 0 || p->state_len == 0) return CC1D_OK;
+    if (p->x == nullptr || p->cu_seqlens == nullptr || p->states == nullptr) return CC1D_ERR_NULL;
+    if (!elem_aligned(p->x, p->itype) || !elem_aligned(p->states, p->itype)) return CC1D_ERR_ALIGN;
+    return launch_varlen_states(*p, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

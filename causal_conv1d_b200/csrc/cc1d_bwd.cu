@@ -1,0 +1,707 @@
+// Backward kernels (sm_100a): dx, dweight, dbias, dinitial_states.
+//
+// Both layouts recompute the pre-activation from x (SiLU case), form
+// g = dout * silu'(y), and produce dx as the transposed convolution of g.  dweight/dbias
+// are reduced in a fixed order: per-thread fp32 accumulators -> warp shuffle tree (channel-
+// first) or fixed-order shared-memory sum over the CTA's token chunks (channel-last) -> one
+// partial row per warp unit / CTA in the caller's workspace -> reduce_partials_kernel sums
+// the rows in index order.  No float atomics anywhere, so repeated runs are bitwise equal.
+//
+// Replaces csrc/causal_conv1d_bwd.cu:53-259 (channel-first), :329-589 (channel-last) and
+// the deterministic-mode workspaces + ATen sums of csrc/causal_conv1d.cpp:388-462.
+#include "cc1d_common.cuh"
+#include "cc1d_kernels.h"
+
+namespace cc1d {
+
+constexpr int kTilingSMs = 148;  // tiling (and so workspace size) is fixed for B200, not queried
+
+// ======================================================================================
+// final reduction of the partial rows
+// ======================================================================================
+struct ReduceArgs {
+    const float *ws;
+    float *dweight;
+    float *dbias;
+    int64_t dw_cs, dw_ws;
+    int64_t dim;
+    int64_t n_outer, outer_stride;   // e.g. batch
+    int64_t n_inner, inner_stride;   // e.g. units per row
+    int64_t chan_stride;
+    int accumulate;
+};
+
+// One warp per channel.  Lane l sums partial rows l, l+32, ... in ascending order, then a
+// fixed xor tree combines the lanes: the summation order never depends on timing.
+template <int W>
+__global__ void __launch_bounds__(128) reduce_partials_kernel(const ReduceArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t c = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (c >= a.dim) return;
+    float acc[W + 1];
+    #pragma unroll
+    for (int k = 0; k <= W; ++k) acc[k] = 0.f;
+    const int64_t n = a.n_outer * a.n_inner;
+    for (int64_t i = lane; i < n; i += 32) {
+        const int64_t o = i / a.n_inner, j = i - o * a.n_inner;
+        const float *p = a.ws + o * a.outer_stride + c * a.chan_stride + j * a.inner_stride;
+        #pragma unroll
+        for (int k = 0; k <= W; ++k) acc[k] += p[k];
+    }
+    #pragma unroll
+    for (int k = 0; k <= W; ++k) {
+        #pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc[k] += __shfl_xor_sync(kFullMask, acc[k], off);
+    }
+    if (lane == 0) {
+        #pragma unroll
+        for (int k = 0; k < W; ++k) {
+            float *d = a.dweight + c * a.dw_cs + k * a.dw_ws;
+            *d = a.accumulate ? *d + acc[k] : acc[k];
+        }
+        if (a.dbias != nullptr) a.dbias[c] = a.accumulate ? a.dbias[c] + acc[W] : acc[W];
+    }
+}
+
+static int launch_reduce(const ReduceArgs &a, int width, cudaStream_t stream) {
+    const unsigned grid = (unsigned)((a.dim + 3) / 4);
+    CC1D_DISPATCH_WIDTH(width, { reduce_partials_kernel<W><<<grid, 128, 0, stream>>>(a); });
+    return check_launch();
+}
+
+// ======================================================================================
+// channel-first
+// ======================================================================================
+struct BwdCfArgs {
+    const void *x;
+    const void *dout;
+    void *dx;
+    const void *weight;
+    const void *bias;
+    float *ws;
+    int64_t x_bs, x_cs, d_bs, d_cs, o_bs, o_cs, w_cs, w_ws;
+    uint32_t dim, seqlen;
+    int wtype;
+    uint32_t vpr, upr, n_units;
+};
+
+// Vector v of a row: a 16-byte load when it lies fully inside the row, element loads for the
+// ragged last vector, zeros beyond.
+template <typename T>
+__device__ __forceinline__ uint4 load_row_vec(const T *__restrict__ row, uint32_t v, uint32_t vpr, uint32_t L) {
+    constexpr int V = Elem<T>::kVec;
+    if ((uint64_t)(v + 1) * V <= L) return ld_stream(row + (uint64_t)v * V);
+    if (v >= vpr) return make_uint4(0, 0, 0, 0);
+    float f[V];
+    #pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const uint64_t t = (uint64_t)v * V + i;
+        f[i] = t < L ? Elem<T>::to_f(row[t]) : 0.f;
+    }
+    return pack<T>(f);
+}
+
+template <typename T>
+__device__ __forceinline__ void store_row_vec(T *__restrict__ row, uint32_t v, uint32_t L, const float *f) {
+    constexpr int V = Elem<T>::kVec;
+    if ((uint64_t)(v + 1) * V <= L) {
+        st_stream(row + (uint64_t)v * V, pack<T>(f));
+    } else {
+        #pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const uint64_t t = (uint64_t)v * V + i;
+            if (t < L) row[t] = Elem<T>::from_f(f[i]);
+        }
+    }
+}
+
+// Fetch the trailing width-1 elements' registers of the previous lane's vector (lane 0 gets
+// lane 31's `old`), see fwd_cf_vec_kernel.
+template <int V, int W>
+__device__ __forceinline__ uint4 prev_vector_tail(const uint4 &own, const uint4 &old, int lane) {
+    const int src_lane = (lane + 31) & 31;
+    uint4 prev = make_uint4(0, 0, 0, 0);
+    if (V == 4) {
+        if (W >= 4) prev.y = __shfl_sync(kFullMask, lane == 31 ? old.y : own.y, src_lane);
+        if (W >= 3) prev.z = __shfl_sync(kFullMask, lane == 31 ? old.z : own.z, src_lane);
+    } else {
+        if (W >= 4) prev.z = __shfl_sync(kFullMask, lane == 31 ? old.z : own.z, src_lane);
+    }
+    prev.w = __shfl_sync(kFullMask, lane == 31 ? old.w : own.w, src_lane);
+    return prev;
+}
+
+template <typename T, int W, bool kSilu, int kVecs>
+__global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
+    constexpr int V = Elem<T>::kVec;
+    const int lane = threadIdx.x & 31;
+    const uint32_t warps_per_cta = blockDim.x >> 5;
+    const uint32_t nwarps = gridDim.x * warps_per_cta;
+    const uint32_t L = a.seqlen;
+
+    for (uint32_t unit = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); unit < a.n_units; unit += nwarps) {
+        const uint32_t row = unit / a.upr;
+        const uint32_t seg = unit - row * a.upr;
+        const uint32_t b = row / a.dim;
+        const uint32_t c = row - b * a.dim;
+        const T *__restrict__ xr = reinterpret_cast<const T *>(a.x) + b * a.x_bs + c * a.x_cs;
+        const T *__restrict__ dr = reinterpret_cast<const T *>(a.dout) + b * a.d_bs + c * a.d_cs;
+        T *__restrict__ dxr = reinterpret_cast<T *>(a.dx) + b * a.o_bs + c * a.o_cs;
+        const uint32_t v0 = seg * (32 * kVecs);
+
+        uint4 xraw[kVecs], draw[kVecs];
+        #pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const uint32_t v = v0 + j * 32 + lane;
+            xraw[j] = load_row_vec<T>(xr, v, a.vpr, L);
+            draw[j] = load_row_vec<T>(dr, v, a.vpr, L);
+        }
+        // left halo of the unit (x only) and the first vector of the next unit (x and dout),
+        // needed by lane 0 and lane 31 respectively
+        uint4 halo0 = make_uint4(0, 0, 0, 0), xedge = make_uint4(0, 0, 0, 0), dedge = make_uint4(0, 0, 0, 0);
+        if (lane == 0 && v0 > 0) halo0 = ld_cached(xr + (uint64_t)(v0 - 1) * V);
+        if (lane == 31) {
+            const uint32_t vn = v0 + kVecs * 32;
+            if (vn < a.vpr) {
+                if (kSilu) xedge = load_row_vec<T>(xr, vn, a.vpr, L);
+                dedge = load_row_vec<T>(dr, vn, a.vpr, L);
+            }
+        }
+
+        float wv[W];
+        #pragma unroll
+        for (int k = 0; k < W; ++k) wv[k] = load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype);
+        const float bv = a.bias != nullptr ? load_w(a.bias, c, a.wtype) : 0.f;
+
+        float g[kVecs][V];
+        float dw[W], db = 0.f;
+        #pragma unroll
+        for (int k = 0; k < W; ++k) dw[k] = 0.f;
+
+        // pass 1: g, dweight, dbias
+        #pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            uint4 prev = prev_vector_tail<V, W>(xraw[j], xraw[j > 0 ? j - 1 : 0], lane);
+            if (j == 0 && lane == 0) prev = halo0;
+            float xx[W - 1 + V];
+            {
+                float pf[V];
+                unpack<T>(prev, pf);
+                #pragma unroll
+                for (int k = 0; k < W - 1; ++k) xx[k] = pf[V - (W - 1) + k];
+            }
+            unpack<T>(xraw[j], xx + (W - 1));
+            unpack<T>(draw[j], g[j]);
+            #pragma unroll
+            for (int i = 0; i < V; ++i) {
+                if (kSilu) {
+                    float y = bv;
+                    #pragma unroll
+                    for (int k = 0; k < W; ++k) y = fmaf(wv[k], xx[i + k], y);
+                    g[j][i] *= dsilu_f(y);
+                }
+                db += g[j][i];
+                #pragma unroll
+                for (int k = 0; k < W; ++k) dw[k] = fmaf(xx[i + k], g[j][i], dw[k]);
+            }
+        }
+        // g of the first width-1 elements of the next unit (only lane 31's copy is used)
+        float ge[W - 1];
+        {
+            float xt[V], xn[V], dn[V];
+            unpack<T>(xraw[kVecs - 1], xt);
+            unpack<T>(xedge, xn);
+            unpack<T>(dedge, dn);
+            float xx[2 * (W - 1)];
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) { xx[k] = xt[V - (W - 1) + k]; xx[W - 1 + k] = xn[k]; }
+            #pragma unroll
+            for (int i = 0; i < W - 1; ++i) {
+                ge[i] = dn[i];
+                if (kSilu) {
+                    float y = bv;
+                    #pragma unroll
+                    for (int k = 0; k < W; ++k) y = fmaf(wv[k], xx[i + k], y);
+                    ge[i] *= dsilu_f(y);
+                }
+            }
+        }
+
+        // pass 2: dx[t] = sum_k w[k] * g[t + (W-1-k)]
+        const int dst_lane = (lane + 1) & 31;
+        #pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            float gg[V + W - 1];
+            #pragma unroll
+            for (int i = 0; i < V; ++i) gg[i] = g[j][i];
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) {
+                // lane l takes lane l+1's g[j][k]; lane 31 takes lane 0's g[j+1][k]
+                const float send = (lane == 0 && j + 1 < kVecs) ? g[j + 1 < kVecs ? j + 1 : j][k] : g[j][k];
+                float r = __shfl_sync(kFullMask, send, dst_lane);
+                if (j == kVecs - 1 && lane == 31) r = ge[k];
+                gg[V + k] = r;
+            }
+            const uint32_t v = v0 + j * 32 + lane;
+            if (v >= a.vpr) continue;
+            float o[V];
+            #pragma unroll
+            for (int i = 0; i < V; ++i) {
+                float acc = 0.f;
+                #pragma unroll
+                for (int k = 0; k < W; ++k) acc = fmaf(wv[k], gg[i + (W - 1 - k)], acc);
+                o[i] = acc;
+            }
+            store_row_vec<T>(dxr, v, L, o);
+        }
+
+        // warp tree (fixed order), one partial row per unit
+        #pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            #pragma unroll
+            for (int k = 0; k < W; ++k) dw[k] += __shfl_xor_sync(kFullMask, dw[k], off);
+            db += __shfl_xor_sync(kFullMask, db, off);
+        }
+        if (lane == 0) {
+            float *p = a.ws + (uint64_t)unit * (W + 1);
+            #pragma unroll
+            for (int k = 0; k < W; ++k) p[k] = dw[k];
+            p[W] = db;
+        }
+    }
+}
+
+// Any alignment: one (row, 256-element tile) per CTA, a thread per element; block tree in
+// shared memory.  Partial row per tile.
+template <typename T, int W, bool kSilu>
+__global__ void __launch_bounds__(256) bwd_cf_scalar_kernel(const BwdCfArgs a) {
+    __shared__ float red[8][W + 1];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (uint32_t tile = blockIdx.x; tile < a.n_units; tile += gridDim.x) {
+        const uint32_t row = tile / a.vpr;
+        const int64_t t = (int64_t)(tile - row * a.vpr) * 256 + threadIdx.x;
+        const uint32_t b = row / a.dim;
+        const uint32_t c = row - b * a.dim;
+        const T *__restrict__ xr = reinterpret_cast<const T *>(a.x) + b * a.x_bs + c * a.x_cs;
+        const T *__restrict__ dr = reinterpret_cast<const T *>(a.dout) + b * a.d_bs + c * a.d_cs;
+        T *__restrict__ dxr = reinterpret_cast<T *>(a.dx) + b * a.o_bs + c * a.o_cs;
+        float wv[W];
+        #pragma unroll
+        for (int k = 0; k < W; ++k) wv[k] = load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype);
+        const float bv = a.bias != nullptr ? load_w(a.bias, c, a.wtype) : 0.f;
+        const int64_t L = a.seqlen;
+        // g at t .. t+W-1 (each needs x at s-(W-1) .. s)
+        float xs[2 * W - 1];
+        #pragma unroll
+        for (int i = 0; i < 2 * W - 1; ++i) {
+            const int64_t p = t - (W - 1) + i;
+            xs[i] = (p >= 0 && p < L) ? Elem<T>::to_f(xr[p]) : 0.f;
+        }
+        float gs[W];
+        #pragma unroll
+        for (int m = 0; m < W; ++m) {
+            const int64_t s = t + m;
+            float gv = s < L ? Elem<T>::to_f(dr[s]) : 0.f;
+            if (kSilu) {
+                float y = bv;
+                #pragma unroll
+                for (int k = 0; k < W; ++k) y = fmaf(wv[k], xs[m + k], y);
+                gv *= dsilu_f(y);
+            }
+            gs[m] = gv;
+        }
+        float dw[W], db = 0.f;
+        #pragma unroll
+        for (int k = 0; k < W; ++k) dw[k] = 0.f;
+        if (t < L) {
+            float acc = 0.f;
+            #pragma unroll
+            for (int k = 0; k < W; ++k) acc = fmaf(wv[k], gs[W - 1 - k], acc);
+            dxr[t] = Elem<T>::from_f(acc);
+            db = gs[0];
+            #pragma unroll
+            for (int k = 0; k < W; ++k) dw[k] = xs[k] * gs[0];
+        }
+        #pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            #pragma unroll
+            for (int k = 0; k < W; ++k) dw[k] += __shfl_xor_sync(kFullMask, dw[k], off);
+            db += __shfl_xor_sync(kFullMask, db, off);
+        }
+        __syncthreads();   // previous tile's readers are done with `red`
+        if (lane == 0) {
+            #pragma unroll
+            for (int k = 0; k < W; ++k) red[wid][k] = dw[k];
+            red[wid][W] = db;
+        }
+        __syncthreads();
+        if (threadIdx.x <= W) {
+            float s = 0.f;
+            #pragma unroll
+            for (int w8 = 0; w8 < 8; ++w8) s += red[w8][threadIdx.x];
+            a.ws[(uint64_t)tile * (W + 1) + threadIdx.x] = s;
+        }
+    }
+}
+
+struct CfPlan {
+    bool vec;
+    uint64_t vpr, upr, n_units;
+};
+
+static CfPlan plan_channel_first(const cc1d_bwd_params &p) {
+    constexpr int kVecs = 4;
+    const int V = vec_elems(p.itype);
+    const int64_t x_bs = p.batch > 1 ? p.x_batch_stride : 0, x_cs = p.dim > 1 ? p.x_c_stride : 0;
+    const int64_t d_bs = p.batch > 1 ? p.dout_batch_stride : 0, d_cs = p.dim > 1 ? p.dout_c_stride : 0;
+    const int64_t o_bs = p.batch > 1 ? p.dx_batch_stride : 0, o_cs = p.dim > 1 ? p.dx_c_stride : 0;
+    CfPlan pl;
+    pl.vec = is_aligned16(p.x) && is_aligned16(p.dout) && is_aligned16(p.dx) && x_bs % V == 0 && x_cs % V == 0 &&
+             d_bs % V == 0 && d_cs % V == 0 && o_bs % V == 0 && o_cs % V == 0;
+    const uint64_t rows = (uint64_t)p.batch * (uint64_t)p.dim;
+    if (pl.vec) {
+        pl.vpr = ((uint64_t)p.seqlen + V - 1) / V;
+        pl.upr = (pl.vpr + 32 * kVecs - 1) / (32 * kVecs);
+    } else {
+        pl.vpr = ((uint64_t)p.seqlen + 255) / 256;
+        pl.upr = pl.vpr;
+    }
+    pl.n_units = rows * pl.upr;
+    return pl;
+}
+
+size_t bwd_workspace_bytes_channel_first(const cc1d_bwd_params &p) {
+    // Alignment of the data pointers decides vector vs scalar tiling; size for the larger of
+    // the two so that the answer does not depend on pointers the caller has not allocated yet.
+    const int V = vec_elems(p.itype);
+    const uint64_t rows = (uint64_t)p.batch * (uint64_t)p.dim;
+    const uint64_t vpr = ((uint64_t)p.seqlen + V - 1) / V;
+    const uint64_t upr_vec = (vpr + 127) / 128;
+    const uint64_t upr_sc = ((uint64_t)p.seqlen + 255) / 256;
+    const uint64_t upr = upr_vec > upr_sc ? upr_vec : upr_sc;
+    return (size_t)(rows * upr * (uint64_t)(p.width + 1) * sizeof(float));
+}
+
+int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream) {
+    const uint64_t rows = (uint64_t)p.batch * (uint64_t)p.dim;
+    if (p.seqlen >= (1ll << 31) || p.dim >= (1ll << 31)) return CC1D_ERR_TOO_LARGE;
+    const CfPlan pl = plan_channel_first(p);
+    if (pl.n_units >= (1ull << 32)) return CC1D_ERR_TOO_LARGE;
+    if (pl.n_units * (uint64_t)(p.width + 1) * sizeof(float) > p.workspace_bytes) return CC1D_ERR_WORKSPACE;
+
+    BwdCfArgs a;
+    a.x = p.x; a.dout = p.dout; a.dx = p.dx; a.weight = p.weight; a.bias = p.bias;
+    a.ws = reinterpret_cast<float *>(p.workspace);
+    a.x_bs = p.batch > 1 ? p.x_batch_stride : 0; a.x_cs = p.dim > 1 ? p.x_c_stride : 0;
+    a.d_bs = p.batch > 1 ? p.dout_batch_stride : 0; a.d_cs = p.dim > 1 ? p.dout_c_stride : 0;
+    a.o_bs = p.batch > 1 ? p.dx_batch_stride : 0; a.o_cs = p.dim > 1 ? p.dx_c_stride : 0;
+    a.w_cs = p.weight_c_stride; a.w_ws = p.weight_width_stride;
+    a.dim = (uint32_t)p.dim; a.seqlen = (uint32_t)p.seqlen; a.wtype = p.wtype;
+    a.vpr = (uint32_t)pl.vpr; a.upr = (uint32_t)pl.upr; a.n_units = (uint32_t)pl.n_units;
+    const int sms = num_sms();
+    if (rows > 0 && p.seqlen > 0) {
+        if (pl.vec) {
+            const uint64_t ctas = (pl.n_units + 7) / 8;
+            const unsigned grid = (unsigned)(ctas < (uint64_t)sms * 8 ? ctas : (uint64_t)sms * 8);
+            CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
+                bwd_cf_vec_kernel<T, W, kSilu, 4><<<grid, 256, 0, stream>>>(a);
+            });););
+        } else {
+            const unsigned grid = (unsigned)(pl.n_units < (uint64_t)sms * 16 ? pl.n_units : (uint64_t)sms * 16);
+            CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
+                bwd_cf_scalar_kernel<T, W, kSilu><<<grid, 256, 0, stream>>>(a);
+            });););
+        }
+        if (check_launch() != CC1D_OK) return CC1D_ERR_LAUNCH;
+    }
+    ReduceArgs r;
+    r.ws = a.ws; r.dweight = p.dweight; r.dbias = p.dbias;
+    r.dw_cs = p.dweight_c_stride; r.dw_ws = p.dweight_width_stride;
+    r.dim = p.dim;
+    r.n_outer = (rows > 0 && p.seqlen > 0) ? p.batch : 0;
+    r.outer_stride = (int64_t)p.dim * (int64_t)pl.upr * (p.width + 1);
+    r.n_inner = (int64_t)pl.upr; r.inner_stride = p.width + 1;
+    r.chan_stride = (int64_t)pl.upr * (p.width + 1);
+    r.accumulate = p.accumulate;
+    if (p.dim == 0) return CC1D_OK;
+    return launch_reduce(r, p.width, stream);
+}
+
+// ======================================================================================
+// channel-last
+// ======================================================================================
+struct BwdClArgs {
+    const void *x;
+    const void *dout;
+    void *dx;
+    const void *weight;
+    const void *bias;
+    const int32_t *seq_idx;
+    const void *init;
+    const void *dfin;
+    void *dinit;
+    float *ws;
+    int64_t x_bs, x_ls, d_bs, d_ls, o_bs, o_ls, w_cs, w_ws, i_bs, i_ls, df_bs, df_cs, df_ls, di_bs, di_ls;
+    int64_t dim, seqlen;
+    int wtype;
+    int tpt;
+    uint32_t ncols, ncolblk, ngroups;
+};
+
+constexpr int kBwdClRows = 8;
+constexpr int kBwdClUnroll = 4;
+
+template <typename T, int W, bool kSilu, bool kSeqIdx>
+__global__ void __launch_bounds__(32 * kBwdClRows) bwd_cl_kernel(const BwdClArgs a) {
+    constexpr int C = Elem<T>::kVec;
+    constexpr int kAcc = (W + 1) * C;                    // fp32 partial sums per thread
+    __shared__ __align__(16) float s_w[(W + 1) * 32 * C];
+    __shared__ __align__(16) float s_red[(kBwdClRows - 1) * 32 * kAcc];
+
+    const uint32_t cb = blockIdx.x % a.ncolblk;
+    const uint32_t rest = blockIdx.x / a.ncolblk;
+    const uint32_t grp = rest % a.ngroups;
+    const uint32_t b = rest / a.ngroups;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+
+    stage_weights<W>(s_w, 32 * C, (int64_t)cb * 32 * C, a.dim, a.weight, a.w_cs, a.w_ws, a.bias,
+                     a.wtype, threadIdx.x, 32 * kBwdClRows);
+    __syncthreads();
+
+    const uint32_t col = cb * 32 + tx;
+    const int64_t L = a.seqlen;
+    const int64_t t0 = ((int64_t)grp * kBwdClRows + ty) * a.tpt;
+    const bool active = col < a.ncols && t0 < L;
+
+    float dw[C][W + 1];   // [.][W] is dbias
+    #pragma unroll
+    for (int c = 0; c < C; ++c) {
+        #pragma unroll
+        for (int k = 0; k <= W; ++k) dw[c][k] = 0.f;
+    }
+
+    if (active) {
+        const int64_t t1 = t0 + a.tpt < L ? t0 + a.tpt : L;
+        const int64_t s_end = t1 + (W - 1);
+        float wv[W][C], bv[C];
+        #pragma unroll
+        for (int k = 0; k < W; ++k) {
+            #pragma unroll
+            for (int c = 0; c < C; ++c) wv[k][c] = s_w[k * 32 * C + tx * C + c];
+        }
+        #pragma unroll
+        for (int c = 0; c < C; ++c) bv[c] = s_w[W * 32 * C + tx * C + c];
+
+        const T *__restrict__ xp = reinterpret_cast<const T *>(a.x) + b * a.x_bs + (int64_t)col * C;
+        const T *__restrict__ dp = reinterpret_cast<const T *>(a.dout) + b * a.d_bs + (int64_t)col * C;
+        T *__restrict__ op = reinterpret_cast<T *>(a.dx) + b * a.o_bs + (int64_t)col * C;
+        const int32_t *__restrict__ sp = kSeqIdx ? a.seq_idx + (int64_t)b * L : nullptr;
+
+        // x and g at the width-1 positions before the current one; g before t0 is never used
+        float xwin[W - 1][C], gwin[W - 1][C];
+        int swin[W - 1];
+        #pragma unroll
+        for (int k = 0; k < W - 1; ++k) {
+            const int64_t p = t0 - (W - 1) + k;
+            uint4 r = make_uint4(0, 0, 0, 0);
+            swin[k] = -1;
+            if (p >= 0) {
+                r = ld_cached(xp + p * a.x_ls);
+                if (kSeqIdx) swin[k] = sp[p];
+            } else if (a.init != nullptr) {
+                r = ld_cached(reinterpret_cast<const T *>(a.init) + b * a.i_bs + (p + (W - 1)) * a.i_ls + (int64_t)col * C);
+            }
+            unpack<T>(r, xwin[k]);
+            #pragma unroll
+            for (int c = 0; c < C; ++c) gwin[k][c] = 0.f;
+        }
+
+        for (int64_t s = t0; s < s_end; s += kBwdClUnroll) {
+            uint4 xr[kBwdClUnroll], dr[kBwdClUnroll];
+            int sid[kBwdClUnroll];
+            #pragma unroll
+            for (int u = 0; u < kBwdClUnroll; ++u) {
+                const int64_t pos = s + u;
+                xr[u] = make_uint4(0, 0, 0, 0);
+                dr[u] = make_uint4(0, 0, 0, 0);
+                sid[u] = -2;   // beyond the sequence: matches nothing
+                if (pos < s_end && pos < L) {
+                    if (kSilu || pos < t1) xr[u] = ld_stream(xp + pos * a.x_ls);
+                    dr[u] = ld_stream(dp + pos * a.d_ls);
+                    if (kSeqIdx) sid[u] = sp[pos];
+                }
+            }
+            #pragma unroll
+            for (int u = 0; u < kBwdClUnroll; ++u) {
+                const int64_t pos = s + u;
+                if (pos < s_end) {
+                    float xc[C], gc[C];
+                    unpack<T>(xr[u], xc);
+                    unpack<T>(dr[u], gc);   // dout, turned into g below
+                    #pragma unroll
+                    for (int c = 0; c < C; ++c) {
+                        if (kSilu) {
+                            float y = bv[c];
+                            #pragma unroll
+                            for (int k = 0; k < W - 1; ++k) {
+                                if (!kSeqIdx || swin[k] == sid[u]) y = fmaf(wv[k][c], xwin[k][c], y);
+                            }
+                            y = fmaf(wv[W - 1][c], xc[c], y);
+                            gc[c] *= dsilu_f(y);
+                        }
+                        if (kSeqIdx && sid[u] < 0) gc[c] = 0.f;   // padded token: out == 0 identically
+                    }
+                    if (pos < t1) {
+                        #pragma unroll
+                        for (int c = 0; c < C; ++c) {
+                            dw[c][W] += gc[c];
+                            #pragma unroll
+                            for (int k = 0; k < W - 1; ++k) {
+                                if (!kSeqIdx || swin[k] == sid[u]) dw[c][k] = fmaf(xwin[k][c], gc[c], dw[c][k]);
+                            }
+                            dw[c][W - 1] = fmaf(xc[c], gc[c], dw[c][W - 1]);
+                        }
+                    }
+                    // gradient w.r.t. the input at q = pos-(W-1): taps g[q .. q+W-1]
+                    const int64_t q = pos - (W - 1);
+                    const bool to_dx = q >= t0;                                   // q < t1 holds
+                    const bool to_dinit = q < 0 && a.dinit != nullptr;           // only when t0 == 0
+                    if (to_dx || to_dinit) {
+                        float o[C];
+                        #pragma unroll
+                        for (int c = 0; c < C; ++c) {
+                            float acc = 0.f;
+                            #pragma unroll
+                            for (int m = 0; m < W - 1; ++m) {
+                                if (!kSeqIdx || swin[m] == swin[0]) acc = fmaf(wv[W - 1 - m][c], gwin[m][c], acc);
+                            }
+                            if (!kSeqIdx || sid[u] == swin[0]) acc = fmaf(wv[0][c], gc[c], acc);
+                            o[c] = acc;
+                        }
+                        if (a.dfin != nullptr && q >= L - (W - 1)) {
+                            const T *df = reinterpret_cast<const T *>(a.dfin) + b * a.df_bs +
+                                          (q - (L - (W - 1))) * a.df_ls + (int64_t)col * C * a.df_cs;
+                            #pragma unroll
+                            for (int c = 0; c < C; ++c) o[c] += Elem<T>::to_f(df[c * a.df_cs]);
+                        }
+                        if (to_dx) {
+                            st_stream(op + q * a.o_ls, pack<T>(o));
+                        } else {
+                            T *di = reinterpret_cast<T *>(a.dinit) + b * a.di_bs + (q + (W - 1)) * a.di_ls + (int64_t)col * C;
+                            *reinterpret_cast<uint4 *>(di) = pack<T>(o);
+                        }
+                    }
+                    #pragma unroll
+                    for (int k = 0; k < W - 2; ++k) {
+                        #pragma unroll
+                        for (int c = 0; c < C; ++c) { xwin[k][c] = xwin[k + 1][c]; gwin[k][c] = gwin[k + 1][c]; }
+                        swin[k] = swin[k + 1];
+                    }
+                    #pragma unroll
+                    for (int c = 0; c < C; ++c) { xwin[W - 2][c] = xc[c]; gwin[W - 2][c] = gc[c]; }
+                    swin[W - 2] = sid[u];
+                }
+            }
+        }
+    }
+
+    // fixed-order sum over the CTA's token chunks: rows 1..7 park their sums, row 0 adds them
+    // in ascending row order and writes the CTA's partial row
+    if (ty > 0) {
+        float *r = s_red + ((ty - 1) * 32 + tx) * kAcc;
+        #pragma unroll
+        for (int c = 0; c < C; ++c) {
+            #pragma unroll
+            for (int k = 0; k <= W; ++k) r[c * (W + 1) + k] = dw[c][k];
+        }
+    }
+    __syncthreads();
+    if (ty == 0 && col < a.ncols) {
+        #pragma unroll 1
+        for (int y = 1; y < kBwdClRows; ++y) {
+            const float *r = s_red + ((y - 1) * 32 + tx) * kAcc;
+            #pragma unroll
+            for (int c = 0; c < C; ++c) {
+                #pragma unroll
+                for (int k = 0; k <= W; ++k) dw[c][k] += r[c * (W + 1) + k];
+            }
+        }
+        float *p = a.ws + (((uint64_t)b * a.ngroups + grp) * (uint64_t)a.dim + (uint64_t)col * C) * (W + 1);
+        #pragma unroll
+        for (int c = 0; c < C; ++c) {
+            #pragma unroll
+            for (int k = 0; k <= W; ++k) p[c * (W + 1) + k] = dw[c][k];
+        }
+    }
+}
+
+int pick_tokens_per_thread(int64_t batch, int64_t ncols, int64_t seqlen, int sms, int max_tpt);
+
+struct ClPlan {
+    int tpt;
+    uint32_t ncols, ncolblk, ngroups;
+};
+
+static ClPlan plan_channel_last(const cc1d_bwd_params &p) {
+    const int C = vec_elems(p.itype);
+    ClPlan pl;
+    const int64_t ncols = p.dim / C;
+    pl.tpt = pick_tokens_per_thread(p.batch, ncols, p.seqlen, kTilingSMs / 2, 128);
+    pl.ncols = (uint32_t)ncols;
+    pl.ncolblk = (uint32_t)((ncols + 31) / 32);
+    const int64_t chunks = (p.seqlen + pl.tpt - 1) / pl.tpt;
+    pl.ngroups = (uint32_t)((chunks + kBwdClRows - 1) / kBwdClRows);
+    return pl;
+}
+
+size_t bwd_workspace_bytes_channel_last(const cc1d_bwd_params &p) {
+    const ClPlan pl = plan_channel_last(p);
+    return (size_t)((uint64_t)p.batch * pl.ngroups * (uint64_t)p.dim * (uint64_t)(p.width + 1) * sizeof(float));
+}
+
+int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
+    const int C = vec_elems(p.itype);
+    if (!is_aligned16(p.x) || !is_aligned16(p.dout) || !is_aligned16(p.dx)) return CC1D_ERR_ALIGN;
+    if (p.initial_states && (!is_aligned16(p.initial_states) || p.initial_states_batch_stride % C ||
+                             p.initial_states_l_stride % C)) return CC1D_ERR_ALIGN;
+    if (p.dinitial_states && (!is_aligned16(p.dinitial_states) || p.dinitial_states_batch_stride % C ||
+                              p.dinitial_states_l_stride % C)) return CC1D_ERR_ALIGN;
+    const ClPlan pl = plan_channel_last(p);
+    const uint64_t ctas = (uint64_t)pl.ncolblk * pl.ngroups * (uint64_t)p.batch;
+    if (ctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
+    if (bwd_workspace_bytes_channel_last(p) > p.workspace_bytes) return CC1D_ERR_WORKSPACE;
+    if (!is_aligned16(p.workspace)) return CC1D_ERR_ALIGN;
+
+    BwdClArgs a;
+    a.x = p.x; a.dout = p.dout; a.dx = p.dx; a.weight = p.weight; a.bias = p.bias; a.seq_idx = p.seq_idx;
+    a.init = p.initial_states; a.dfin = p.dfinal_states; a.dinit = p.dinitial_states;
+    a.ws = reinterpret_cast<float *>(p.workspace);
+    a.x_bs = p.x_batch_stride; a.x_ls = p.x_l_stride; a.d_bs = p.dout_batch_stride; a.d_ls = p.dout_l_stride;
+    a.o_bs = p.dx_batch_stride; a.o_ls = p.dx_l_stride; a.w_cs = p.weight_c_stride; a.w_ws = p.weight_width_stride;
+    a.i_bs = p.initial_states_batch_stride; a.i_ls = p.initial_states_l_stride;
+    a.df_bs = p.dfinal_states_batch_stride; a.df_cs = p.dfinal_states_c_stride; a.df_ls = p.dfinal_states_l_stride;
+    a.di_bs = p.dinitial_states_batch_stride; a.di_ls = p.dinitial_states_l_stride;
+    a.dim = p.dim; a.seqlen = p.seqlen; a.wtype = p.wtype; a.tpt = pl.tpt;
+    a.ncols = pl.ncols; a.ncolblk = pl.ncolblk; a.ngroups = pl.ngroups;
+    if (ctas > 0) {
+        CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
+            CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
+                bwd_cl_kernel<T, W, kSilu, kSeqIdx><<<(unsigned)ctas, 32 * kBwdClRows, 0, stream>>>(a);
+            }););););
+        if (check_launch() != CC1D_OK) return CC1D_ERR_LAUNCH;
+    }
+    ReduceArgs r;
+    r.ws = a.ws; r.dweight = p.dweight; r.dbias = p.dbias;
+    r.dw_cs = p.dweight_c_stride; r.dw_ws = p.dweight_width_stride;
+    r.dim = p.dim;
+    r.n_outer = (int64_t)p.batch * pl.ngroups;
+    r.outer_stride = p.dim * (p.width + 1);
+    r.n_inner = 1; r.inner_stride = 0;
+    r.chan_stride = p.width + 1;
+    r.accumulate = p.accumulate;
+    if (p.dim == 0) return CC1D_OK;
+    if (p.seqlen == 0) r.n_outer = 0;
+    return launch_reduce(r, p.width, stream);
+}
+
+}  // namespace cc1d

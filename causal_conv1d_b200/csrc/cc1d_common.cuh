@@ -1,0 +1,133 @@
+// Shared device helpers for the sm_100a causal conv1d kernels: element traits, 16-byte
+// streaming loads/stores, fp32 conversion, SiLU, weight staging.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "cc1d.h"
+
+namespace cc1d {
+
+constexpr unsigned kFullMask = 0xffffffffu;
+
+// ---- element traits -----------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static constexpr int kVec = 4;   // elements per 16-byte vector
+    static __device__ __forceinline__ float to_f(float v) { return v; }
+    static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <> struct Elem<__half> {
+    static constexpr int kVec = 8;
+    static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static constexpr int kVec = 8;
+    static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+// ---- 16-byte global access ------------------------------------------------------------
+// Read-once input streams: non-coherent path, do not keep the line in L1.
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+    uint4 v;
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+// Data that another thread of the same launch may also read (halos): plain cached load.
+__device__ __forceinline__ uint4 ld_cached(const void *p) {
+    return *reinterpret_cast<const uint4 *>(p);
+}
+// Write-once output streams: evict-first.
+__device__ __forceinline__ void st_stream(void *p, const uint4 &v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};"
+                 :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// ---- 16-byte vector <-> fp32 ------------------------------------------------------------
+template <typename T> __device__ __forceinline__ void unpack(const uint4 &v, float *f);
+template <> __device__ __forceinline__ void unpack<float>(const uint4 &v, float *f) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+}
+template <> __device__ __forceinline__ void unpack<__nv_bfloat16>(const uint4 &v, float *f) {
+    const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(r[i] << 16);
+        f[2 * i + 1] = __uint_as_float(r[i] & 0xffff0000u);
+    }
+}
+template <> __device__ __forceinline__ void unpack<__half>(const uint4 &v, float *f) {
+    const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(&r[i]));
+        f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+}
+
+template <typename T> __device__ __forceinline__ uint4 pack(const float *f);
+template <> __device__ __forceinline__ uint4 pack<float>(const float *f) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]),
+                      __float_as_uint(f[2]), __float_as_uint(f[3]));
+}
+template <> __device__ __forceinline__ uint4 pack<__nv_bfloat16>(const float *f) {
+    uint32_t r[4];
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        r[i] = *reinterpret_cast<const uint32_t *>(&t);
+    }
+    return make_uint4(r[0], r[1], r[2], r[3]);
+}
+template <> __device__ __forceinline__ uint4 pack<__half>(const float *f) {
+    uint32_t r[4];
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+        r[i] = *reinterpret_cast<const uint32_t *>(&t);
+    }
+    return make_uint4(r[0], r[1], r[2], r[3]);
+}
+
+// ---- activation ---------------------------------------------------------------------------
+__device__ __forceinline__ float sigmoid_f(float y) { return __fdividef(1.f, 1.f + __expf(-y)); }
+__device__ __forceinline__ float silu_f(float y) { return __fdividef(y, 1.f + __expf(-y)); }
+// d silu(y) / dy
+__device__ __forceinline__ float dsilu_f(float y) {
+    const float s = sigmoid_f(y);
+    return s * (1.f + y * (1.f - s));
+}
+
+// ---- weights: dtype chosen at run time (they are a few KB, never on the critical stream) --
+__device__ __forceinline__ float load_w(const void *p, int64_t idx, int wtype) {
+    if (wtype == CC1D_F32) return reinterpret_cast<const float *>(p)[idx];
+    if (wtype == CC1D_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[idx]);
+    return __half2float(reinterpret_cast<const __half *>(p)[idx]);
+}
+
+// Stage weight taps and bias of `nch` consecutive channels starting at c0 into shared memory
+// as fp32: s_w[k * nch + c] for tap k < W, s_w[W * nch + c] = bias (0 without bias, 0 past dim).
+template <int W>
+__device__ __forceinline__ void stage_weights(float *s_w, int nch, int64_t c0, int64_t dim,
+                                              const void *weight, int64_t w_cs, int64_t w_ws,
+                                              const void *bias, int wtype, int tid, int nthreads) {
+    for (int i = tid; i < (W + 1) * nch; i += nthreads) {
+        const int k = i / nch;
+        const int64_t c = c0 + (i - k * nch);
+        float v = 0.f;
+        if (c < dim) {
+            if (k < W) v = load_w(weight, c * w_cs + k * w_ws, wtype);
+            else if (bias != nullptr) v = load_w(bias, c, wtype);
+        }
+        s_w[i] = v;
+    }
+}
+
+}  // namespace cc1d

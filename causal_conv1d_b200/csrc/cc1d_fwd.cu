@@ -1,0 +1,355 @@
+// Forward kernels (sm_100a).
+//
+// Channel-first (x[b, c, :] contiguous): the work is cut into warp units of 32 * kVecs
+// consecutive 16-byte vectors of one row.  A lane owns vector (j * 32 + lane); the
+// (width-1)-element halo comes from the neighbouring lane by warp shuffle, only lane 0 of a
+// unit's first vector re-reads one vector from global.  No shared memory, no barrier, every
+// x byte is requested from DRAM once.
+//
+// Channel-last (x[b, :, t] contiguous): a thread owns one 16-byte vector of channels and
+// slides down `tpt` consecutive tokens keeping the last width-1 vectors in registers; a
+// warp covers 512 contiguous bytes of one token.  seq_idx masking, initial_states (halo of
+// the first chunk) and final_states (the window left after the last token) ride along.
+//
+// Replaces csrc/causal_conv1d_fwd.cu:46-137 (channel-first) and :205-348 (channel-last)
+// of the reference.
+#include "cc1d_common.cuh"
+#include "cc1d_kernels.h"
+
+namespace cc1d {
+
+// ======================================================================================
+// channel-first
+// ======================================================================================
+struct FwdCfArgs {
+    const void *x;
+    void *out;
+    const void *weight;
+    const void *bias;
+    int64_t x_bs, x_cs, o_bs, o_cs, w_cs, w_ws;
+    uint32_t dim, seqlen;
+    int wtype;
+    uint32_t vpr;      // 16-byte vectors per row, the last one may be partial
+    uint32_t upr;      // warp units per row
+    uint32_t n_units;  // rows * upr
+};
+
+template <typename T, int W, bool kSilu, int kVecs>
+__global__ void __launch_bounds__(256) fwd_cf_vec_kernel(const FwdCfArgs a) {
+    constexpr int V = Elem<T>::kVec;
+    const int lane = threadIdx.x & 31;
+    const int src_lane = (lane + 31) & 31;
+    const uint32_t warps_per_cta = blockDim.x >> 5;
+    const uint32_t nwarps = gridDim.x * warps_per_cta;
+    const uint32_t L = a.seqlen;
+
+    for (uint32_t unit = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); unit < a.n_units; unit += nwarps) {
+        const uint32_t row = unit / a.upr;
+        const uint32_t seg = unit - row * a.upr;
+        const uint32_t b = row / a.dim;
+        const uint32_t c = row - b * a.dim;
+        const T *__restrict__ xr = reinterpret_cast<const T *>(a.x) + b * a.x_bs + c * a.x_cs;
+        T *__restrict__ outr = reinterpret_cast<T *>(a.out) + b * a.o_bs + c * a.o_cs;
+        const uint32_t v0 = seg * (32 * kVecs);
+
+        // issue every load of the unit before any use
+        uint4 raw[kVecs];
+        #pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const uint32_t v = v0 + j * 32 + lane;
+            raw[j] = make_uint4(0, 0, 0, 0);
+            if ((uint64_t)(v + 1) * V <= L) raw[j] = ld_stream(xr + (uint64_t)v * V);
+        }
+        uint4 halo0 = make_uint4(0, 0, 0, 0);
+        if (lane == 0 && v0 > 0) halo0 = ld_cached(xr + (uint64_t)(v0 - 1) * V);
+
+        float wv[W];
+        #pragma unroll
+        for (int k = 0; k < W; ++k) wv[k] = load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype);
+        const float bv = a.bias != nullptr ? load_w(a.bias, c, a.wtype) : 0.f;
+
+        #pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const uint32_t v = v0 + j * 32 + lane;
+            // previous vector: lane-1's raw[j]; for lane 0 it is lane 31's raw[j-1]
+            const uint4 &own = raw[j];
+            const uint4 &old = raw[j > 0 ? j - 1 : 0];
+            uint4 prev = make_uint4(0, 0, 0, 0);
+            if (V == 4) {
+                if (W >= 4) prev.y = __shfl_sync(kFullMask, lane == 31 ? old.y : own.y, src_lane);
+                if (W >= 3) prev.z = __shfl_sync(kFullMask, lane == 31 ? old.z : own.z, src_lane);
+            } else {
+                if (W >= 4) prev.z = __shfl_sync(kFullMask, lane == 31 ? old.z : own.z, src_lane);
+            }
+            prev.w = __shfl_sync(kFullMask, lane == 31 ? old.w : own.w, src_lane);
+            if (j == 0 && lane == 0) prev = halo0;
+
+            if (v >= a.vpr) continue;
+            const bool full = (uint64_t)(v + 1) * V <= L;
+            float xx[W - 1 + V];
+            {
+                float pf[V];
+                unpack<T>(prev, pf);
+                #pragma unroll
+                for (int k = 0; k < W - 1; ++k) xx[k] = pf[V - (W - 1) + k];
+            }
+            if (full) {
+                unpack<T>(own, xx + (W - 1));
+            } else {
+                #pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    const uint64_t t = (uint64_t)v * V + i;
+                    xx[W - 1 + i] = t < L ? Elem<T>::to_f(xr[t]) : 0.f;
+                }
+            }
+            float o[V];
+            #pragma unroll
+            for (int i = 0; i < V; ++i) {
+                float acc = bv;
+                #pragma unroll
+                for (int k = 0; k < W; ++k) acc = fmaf(wv[k], xx[i + k], acc);
+                o[i] = kSilu ? silu_f(acc) : acc;
+            }
+            if (full) {
+                st_stream(outr + (uint64_t)v * V, pack<T>(o));
+            } else {
+                #pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    const uint64_t t = (uint64_t)v * V + i;
+                    if (t < L) outr[t] = Elem<T>::from_f(o[i]);
+                }
+            }
+        }
+    }
+}
+
+// Any alignment / row stride: one output element per thread, lanes along seqlen.
+template <typename T, int W, bool kSilu>
+__global__ void __launch_bounds__(256) fwd_cf_scalar_kernel(const FwdCfArgs a) {
+    // here: vpr = 256-element tiles per row, n_units = rows * vpr
+    for (uint32_t tile = blockIdx.x; tile < a.n_units; tile += gridDim.x) {
+        const uint32_t row = tile / a.vpr;
+        const uint32_t t = (tile - row * a.vpr) * 256 + threadIdx.x;
+        if (t >= a.seqlen) continue;
+        const uint32_t b = row / a.dim;
+        const uint32_t c = row - b * a.dim;
+        const T *__restrict__ xr = reinterpret_cast<const T *>(a.x) + b * a.x_bs + c * a.x_cs;
+        T *__restrict__ outr = reinterpret_cast<T *>(a.out) + b * a.o_bs + c * a.o_cs;
+        float acc = a.bias != nullptr ? load_w(a.bias, c, a.wtype) : 0.f;
+        #pragma unroll
+        for (int k = 0; k < W; ++k) {
+            const int64_t p = (int64_t)t - (W - 1 - k);
+            if (p >= 0) acc = fmaf(load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype), Elem<T>::to_f(xr[p]), acc);
+        }
+        outr[t] = Elem<T>::from_f(kSilu ? silu_f(acc) : acc);
+    }
+}
+
+int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
+    const int V = vec_elems(p.itype);
+    const uint64_t rows = (uint64_t)p.batch * (uint64_t)p.dim;
+    if (rows == 0 || p.seqlen == 0) return CC1D_OK;
+    if (p.seqlen >= (1ll << 31) || p.dim >= (1ll << 31)) return CC1D_ERR_TOO_LARGE;
+
+    FwdCfArgs a;
+    a.x = p.x; a.out = p.out; a.weight = p.weight; a.bias = p.bias;
+    a.x_bs = p.batch > 1 ? p.x_batch_stride : 0; a.x_cs = p.dim > 1 ? p.x_c_stride : 0;
+    a.o_bs = p.batch > 1 ? p.out_batch_stride : 0; a.o_cs = p.dim > 1 ? p.out_c_stride : 0;
+    a.w_cs = p.weight_c_stride; a.w_ws = p.weight_width_stride;
+    a.dim = (uint32_t)p.dim; a.seqlen = (uint32_t)p.seqlen; a.wtype = p.wtype;
+
+    const bool vec_ok = is_aligned16(p.x) && is_aligned16(p.out) && a.x_bs % V == 0 && a.x_cs % V == 0 &&
+                        a.o_bs % V == 0 && a.o_cs % V == 0;
+    const int sms = num_sms();
+    if (vec_ok) {
+        constexpr int kVecs = 4;
+        const uint64_t vpr = ((uint64_t)p.seqlen + V - 1) / V;
+        const uint64_t upr = (vpr + 32 * kVecs - 1) / (32 * kVecs);
+        const uint64_t n_units = rows * upr;
+        if (n_units >= (1ull << 32)) return CC1D_ERR_TOO_LARGE;
+        a.vpr = (uint32_t)vpr; a.upr = (uint32_t)upr; a.n_units = (uint32_t)n_units;
+        const uint64_t ctas = (n_units + 7) / 8;
+        const unsigned grid = (unsigned)(ctas < (uint64_t)sms * 8 ? ctas : (uint64_t)sms * 8);
+        CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
+            fwd_cf_vec_kernel<T, W, kSilu, kVecs><<<grid, 256, 0, stream>>>(a);
+        });););
+    } else {
+        const uint64_t tpr = ((uint64_t)p.seqlen + 255) / 256;
+        const uint64_t n_tiles = rows * tpr;
+        if (n_tiles >= (1ull << 32)) return CC1D_ERR_TOO_LARGE;
+        a.vpr = (uint32_t)tpr; a.upr = 0; a.n_units = (uint32_t)n_tiles;
+        const unsigned grid = (unsigned)(n_tiles < (uint64_t)sms * 32 ? n_tiles : (uint64_t)sms * 32);
+        CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
+            fwd_cf_scalar_kernel<T, W, kSilu><<<grid, 256, 0, stream>>>(a);
+        });););
+    }
+    return check_launch();
+}
+
+// ======================================================================================
+// channel-last
+// ======================================================================================
+struct FwdClArgs {
+    const void *x;
+    void *out;
+    const void *weight;
+    const void *bias;
+    const int32_t *seq_idx;
+    const void *init;
+    void *fin;
+    int64_t x_bs, x_ls, o_bs, o_ls, w_cs, w_ws, i_bs, i_ls, f_bs, f_ls;
+    int64_t dim, seqlen;
+    int wtype;
+    int tpt;            // tokens per thread
+    uint32_t ncols;     // 16-byte channel vectors per token
+    uint32_t ncolblk;   // CTAs along channels (32 vectors each)
+    uint32_t ngroups;   // CTAs along seqlen per batch entry (kRows chunks each)
+};
+
+constexpr int kClRows = 8;    // token chunks per CTA (threadIdx.y)
+constexpr int kClUnroll = 4;  // independent 16-byte loads in flight per thread
+
+template <typename T, int W, bool kSilu, bool kSeqIdx>
+__global__ void __launch_bounds__(32 * kClRows) fwd_cl_kernel(const FwdClArgs a) {
+    constexpr int C = Elem<T>::kVec;  // channels per thread
+    __shared__ __align__(16) float s_w[(W + 1) * 32 * C];
+
+    const uint32_t cb = blockIdx.x % a.ncolblk;
+    const uint32_t rest = blockIdx.x / a.ncolblk;
+    const uint32_t grp = rest % a.ngroups;
+    const uint32_t b = rest / a.ngroups;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+
+    stage_weights<W>(s_w, 32 * C, (int64_t)cb * 32 * C, a.dim, a.weight, a.w_cs, a.w_ws, a.bias,
+                     a.wtype, threadIdx.x, 32 * kClRows);
+    __syncthreads();
+
+    const uint32_t col = cb * 32 + tx;
+    const int64_t t0 = ((int64_t)grp * kClRows + ty) * a.tpt;
+    if (col >= a.ncols || t0 >= a.seqlen) return;
+    const int64_t t1 = t0 + a.tpt < a.seqlen ? t0 + a.tpt : a.seqlen;
+
+    float wv[W][C], bv[C];
+    #pragma unroll
+    for (int k = 0; k < W; ++k) {
+        #pragma unroll
+        for (int c = 0; c < C; ++c) wv[k][c] = s_w[k * 32 * C + tx * C + c];
+    }
+    #pragma unroll
+    for (int c = 0; c < C; ++c) bv[c] = s_w[W * 32 * C + tx * C + c];
+
+    const T *__restrict__ xp = reinterpret_cast<const T *>(a.x) + b * a.x_bs + (int64_t)col * C;
+    T *__restrict__ op = reinterpret_cast<T *>(a.out) + b * a.o_bs + (int64_t)col * C;
+    const int32_t *__restrict__ sp = kSeqIdx ? a.seq_idx + (int64_t)b * a.seqlen : nullptr;
+
+    // window = the width-1 tokens before t0 (x, or initial_states, or zero)
+    float win[W - 1][C];
+    int sw[W - 1];
+    #pragma unroll
+    for (int k = 0; k < W - 1; ++k) {
+        const int64_t p = t0 - (W - 1) + k;
+        uint4 r = make_uint4(0, 0, 0, 0);
+        sw[k] = -1;
+        if (p >= 0) {
+            r = ld_cached(xp + p * a.x_ls);
+            if (kSeqIdx) sw[k] = sp[p];
+        } else if (a.init != nullptr) {
+            r = ld_cached(reinterpret_cast<const T *>(a.init) + b * a.i_bs + (p + (W - 1)) * a.i_ls + (int64_t)col * C);
+        }
+        unpack<T>(r, win[k]);
+    }
+
+    for (int64_t t = t0; t < t1; t += kClUnroll) {
+        uint4 raw[kClUnroll];
+        int sid[kClUnroll];
+        #pragma unroll
+        for (int u = 0; u < kClUnroll; ++u) {
+            raw[u] = make_uint4(0, 0, 0, 0);
+            sid[u] = 0;
+            if (t + u < t1) {
+                raw[u] = ld_stream(xp + (t + u) * a.x_ls);
+                if (kSeqIdx) sid[u] = sp[t + u];
+            }
+        }
+        #pragma unroll
+        for (int u = 0; u < kClUnroll; ++u) {
+            if (t + u < t1) {
+                float cur[C], o[C];
+                unpack<T>(raw[u], cur);
+                #pragma unroll
+                for (int c = 0; c < C; ++c) {
+                    float acc = bv[c];
+                    #pragma unroll
+                    for (int k = 0; k < W - 1; ++k) {
+                        if (!kSeqIdx || sw[k] == sid[u]) acc = fmaf(wv[k][c], win[k][c], acc);
+                    }
+                    acc = fmaf(wv[W - 1][c], cur[c], acc);
+                    if (kSilu) acc = silu_f(acc);
+                    // a padded token (seq_idx < 0) outputs exactly zero: no bias, no activation
+                    o[c] = (kSeqIdx && sid[u] < 0) ? 0.f : acc;
+                }
+                st_stream(op + (t + u) * a.o_ls, pack<T>(o));
+                #pragma unroll
+                for (int k = 0; k < W - 2; ++k) {
+                    #pragma unroll
+                    for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
+                    sw[k] = sw[k + 1];
+                }
+                #pragma unroll
+                for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
+                sw[W - 2] = sid[u];
+            }
+        }
+    }
+
+    // the thread that consumed the last token holds the last width-1 entries of [initial | x]
+    if (a.fin != nullptr && t1 == a.seqlen) {
+        T *fp = reinterpret_cast<T *>(a.fin) + b * a.f_bs + (int64_t)col * C;
+        #pragma unroll
+        for (int k = 0; k < W - 1; ++k) *reinterpret_cast<uint4 *>(fp + k * a.f_ls) = pack<T>(win[k]);
+    }
+}
+
+// Tokens per thread: long enough to amortise the (width-1)-token halo re-read, short enough
+// to fill the machine (~2 CTAs of 256 threads per SM and more).
+int pick_tokens_per_thread(int64_t batch, int64_t ncols, int64_t seqlen, int sms, int max_tpt) {
+    const double threads_wanted = (double)sms * 2048.0;
+    const double cols_total = (double)batch * (double)ncols;
+    int tpt = max_tpt;
+    while (tpt > 8 && cols_total * (double)((seqlen + tpt - 1) / tpt) < threads_wanted) tpt >>= 1;
+    return tpt;
+}
+
+int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream) {
+    if (p.batch == 0 || p.dim == 0 || p.seqlen == 0) return CC1D_OK;
+    const int C = vec_elems(p.itype);
+    if (!is_aligned16(p.x) || !is_aligned16(p.out)) return CC1D_ERR_ALIGN;
+    if (p.initial_states && (!is_aligned16(p.initial_states) || p.initial_states_batch_stride % C ||
+                             p.initial_states_l_stride % C)) return CC1D_ERR_ALIGN;
+    if (p.final_states && (!is_aligned16(p.final_states) || p.final_states_batch_stride % C ||
+                           p.final_states_l_stride % C)) return CC1D_ERR_ALIGN;
+    const int sms = num_sms();
+    FwdClArgs a;
+    a.x = p.x; a.out = p.out; a.weight = p.weight; a.bias = p.bias; a.seq_idx = p.seq_idx;
+    a.init = p.initial_states; a.fin = p.final_states;
+    a.x_bs = p.x_batch_stride; a.x_ls = p.x_l_stride; a.o_bs = p.out_batch_stride; a.o_ls = p.out_l_stride;
+    a.w_cs = p.weight_c_stride; a.w_ws = p.weight_width_stride;
+    a.i_bs = p.initial_states_batch_stride; a.i_ls = p.initial_states_l_stride;
+    a.f_bs = p.final_states_batch_stride; a.f_ls = p.final_states_l_stride;
+    a.dim = p.dim; a.seqlen = p.seqlen; a.wtype = p.wtype;
+    const int64_t ncols = p.dim / C;
+    a.tpt = pick_tokens_per_thread(p.batch, ncols, p.seqlen, sms, 64);
+    a.ncols = (uint32_t)ncols;
+    a.ncolblk = (uint32_t)((ncols + 31) / 32);
+    const int64_t chunks = (p.seqlen + a.tpt - 1) / a.tpt;
+    a.ngroups = (uint32_t)((chunks + kClRows - 1) / kClRows);
+    const uint64_t ctas = (uint64_t)a.ncolblk * a.ngroups * (uint64_t)p.batch;
+    if (ctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
+    CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
+        CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
+            fwd_cl_kernel<T, W, kSilu, kSeqIdx><<<(unsigned)ctas, 32 * kClRows, 0, stream>>>(a);
+        }););););
+    return check_launch();
+}
+
+}  // namespace cc1d

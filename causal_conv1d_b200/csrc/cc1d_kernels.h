@@ -1,0 +1,52 @@
+// Internal launch functions behind the C ABI (cc1d_api.cu validates, these dispatch on
+// dtype / width / flags and launch).  All return a cc1d_status.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "cc1d.h"
+
+namespace cc1d {
+
+// Number of SMs of the current device (cached per device; 148 on B200).
+int num_sms();
+
+inline bool is_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int elem_size(int dtype) { return dtype == CC1D_F32 ? 4 : 2; }
+inline int vec_elems(int dtype) { return 16 / elem_size(dtype); }
+
+int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream);
+int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream);
+
+size_t bwd_workspace_bytes_channel_first(const cc1d_bwd_params &p);
+size_t bwd_workspace_bytes_channel_last(const cc1d_bwd_params &p);
+int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream);
+int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream);
+
+int launch_update(const cc1d_update_params &p, cudaStream_t stream);
+int launch_varlen_states(const cc1d_varlen_states_params &p, cudaStream_t stream);
+
+inline int check_launch() { return cudaGetLastError() == cudaSuccess ? CC1D_OK : CC1D_ERR_LAUNCH; }
+
+}  // namespace cc1d
+
+// Dispatch helpers: run `...` (a generic lambda body) with T / W bound as types / constants.
+#define CC1D_DISPATCH_ITYPE(itype, ...)                                         \
+    do {                                                                        \
+        if ((itype) == CC1D_F32) { using T = float; __VA_ARGS__ }               \
+        else if ((itype) == CC1D_F16) { using T = __half; __VA_ARGS__ }         \
+        else { using T = __nv_bfloat16; __VA_ARGS__ }                           \
+    } while (0)
+
+#define CC1D_DISPATCH_WIDTH(width, ...)                                         \
+    do {                                                                        \
+        if ((width) == 2) { constexpr int W = 2; __VA_ARGS__ }                  \
+        else if ((width) == 3) { constexpr int W = 3; __VA_ARGS__ }             \
+        else { constexpr int W = 4; __VA_ARGS__ }                               \
+    } while (0)
+
+#define CC1D_DISPATCH_BOOL(cond, NAME, ...)                                     \
+    do {                                                                        \
+        if (cond) { constexpr bool NAME = true; __VA_ARGS__ }                   \
+        else { constexpr bool NAME = false; __VA_ARGS__ }                       \
+    } while (0)

@@ -1,0 +1,106 @@
+"""The C-ABI shared library without a GPU: it loads, exports every symbol the header
+declares, and rejects bad parameter blocks with the documented status before touching CUDA."""
+import ctypes
+
+import pytest
+
+import cabi
+
+FAKE = 0x1000  # never dereferenced: validation fails first
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import causal_conv1d_b200._build as b
+    b.build_kernels()
+    return cabi.load()
+
+
+def test_exports_every_declared_symbol(lib):
+    names = cabi.declared_symbols()
+    assert {"cc1d_fwd", "cc1d_bwd", "cc1d_bwd_workspace_bytes", "cc1d_update", "cc1d_varlen_states",
+            "cc1d_status_str", "cc1d_abi_version"} <= set(names)
+    for n in names:
+        assert hasattr(lib, n), f"libcc1d.so does not export {n}"
+    assert lib.cc1d_abi_version() >= 1
+
+
+def test_struct_sizes_match_header():
+    # all fields are 4- or 8-byte scalars laid out without surprises; spot-check total sizes
+    assert ctypes.sizeof(cabi.FwdParams) == 16 + 3 * 8 + 8 + 24 + 8 + 16 + 8 + 8 + 24 + 8 + 8 + 24 + 8 + 24
+    assert ctypes.sizeof(cabi.VarlenParams) == 8 + 4 * 8 + 8 + 16 + 8 + 8 + 24
+
+
+def _fwd(**kw):
+    p = cabi.FwdParams(itype=cabi.BF16, wtype=cabi.BF16, width=4, silu=1, batch=2, dim=64, seqlen=128,
+                       x=FAKE, x_batch_stride=64 * 128, x_c_stride=128, x_l_stride=1,
+                       weight=FAKE, weight_c_stride=4, weight_width_stride=1,
+                       out=FAKE, out_batch_stride=64 * 128, out_c_stride=128, out_l_stride=1)
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+@pytest.mark.parametrize("kw,code,text", [
+    (dict(width=5), 3, "width between 2 and 4"),
+    (dict(width=1), 3, "width between 2 and 4"),
+    (dict(itype=7), 2, "dtype"),
+    (dict(x=0), 1, "NULL"),
+    (dict(out=0), 1, "NULL"),
+    (dict(batch=-1), 4, "sizes"),
+    (dict(x_c_stride=3, x_l_stride=2), 5, "contiguous"),
+    (dict(dim=60, x_c_stride=1, x_l_stride=64), 6, "divisible by 8"),
+    (dict(x_c_stride=1, x_l_stride=68), 7, "multiples of 8"),
+    (dict(seq_idx=FAKE), 8, "channel last"),
+    (dict(x=FAKE + 1), 12, "aligned"),
+])
+def test_fwd_rejects(lib, kw, code, text):
+    p = _fwd(**kw)
+    rc = lib.cc1d_fwd(ctypes.byref(p), None)
+    assert rc == code
+    assert text in lib.cc1d_status_str(rc).decode()
+
+
+def test_update_rejects(lib):
+    p = cabi.UpdateParams(itype=cabi.F32, wtype=cabi.F32, width=4, silu=0, batch=2, dim=8, seqlen=1,
+                          x=FAKE, weight=FAKE, out=FAKE, conv_state=FAKE, conv_state_len=2)
+    assert lib.cc1d_update(ctypes.byref(p), None) == 10   # state_len < width - 1
+    p.conv_state_len = 3
+    p.conv_state = 0
+    assert lib.cc1d_update(ctypes.byref(p), None) == 1
+    assert lib.cc1d_update(None, None) == 1
+
+
+def test_bwd_workspace_and_rejects(lib):
+    p = cabi.BwdParams(itype=cabi.BF16, wtype=cabi.F32, width=4, silu=1, batch=8, dim=5120, seqlen=2048,
+                       x=FAKE, x_batch_stride=5120 * 2048, x_c_stride=2048, x_l_stride=1,
+                       weight=FAKE, weight_c_stride=4, weight_width_stride=1,
+                       dout=FAKE, dout_batch_stride=5120 * 2048, dout_c_stride=2048, dout_l_stride=1,
+                       dx=FAKE, dx_batch_stride=5120 * 2048, dx_c_stride=2048, dx_l_stride=1,
+                       dweight=FAKE, dweight_c_stride=4, dweight_width_stride=1)
+    n = lib.cc1d_bwd_workspace_bytes(ctypes.byref(p))
+    # one fp32 row of width+1 per (batch, channel, 256-element tile): 8 * 5120 * 8 * 5 * 4 bytes
+    assert n == 8 * 5120 * 8 * 5 * 4
+    assert lib.cc1d_bwd(ctypes.byref(p), None) == 11          # workspace missing
+    p.workspace, p.workspace_bytes = FAKE, n - 1
+    assert lib.cc1d_bwd(ctypes.byref(p), None) == 11          # workspace too small
+    p.bias = FAKE                                             # bias without dbias
+    assert lib.cc1d_bwd(ctypes.byref(p), None) == 1
+    p.width = 9
+    assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(p)) == 0
+    # channel-last problem: partial rows per (batch, 8-chunk group)
+    q = cabi.BwdParams(itype=cabi.BF16, wtype=cabi.BF16, width=4, silu=1, batch=1, dim=5376, seqlen=32768,
+                       x=FAKE, x_batch_stride=5376 * 32768, x_c_stride=1, x_l_stride=5376)
+    assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(q)) == 32 * 5376 * 5 * 4
+
+
+def test_varlen_rejects(lib):
+    p = cabi.VarlenParams(itype=9, total_tokens=4, dim=8, batch=1, state_len=2, x=FAKE, cu_seqlens=FAKE, states=FAKE)
+    assert lib.cc1d_varlen_states(ctypes.byref(p), None) == 2
+    p.itype, p.states = cabi.F16, 0
+    assert lib.cc1d_varlen_states(ctypes.byref(p), None) == 1
+
+
+def test_status_strings(lib):
+    assert lib.cc1d_status_str(0) == b"ok"
+    assert b"unknown" in lib.cc1d_status_str(999)

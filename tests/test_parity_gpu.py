@@ -1,0 +1,400 @@
+"""Parity of the CUDA path (Python API -> torch extension -> C ABI -> sm_100a kernels)
+against the golden fixtures and the CPU oracle.  The grids follow the reference's own test
+file (tests/test_causal_conv1d.py), thinned where the CPU oracle would take too long."""
+import itertools
+import zlib
+
+import pytest
+import torch
+
+import oracle
+from conftest import DT, TOL, assert_close, assert_close_sum, check, golden_names
+from torch_ref import conv_grads64
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _api():
+    import causal_conv1d_b200 as m
+    return m
+
+
+def _pick(key, n):
+    """Deterministic pseudo-random choice in range(n) from a test id."""
+    return zlib.crc32(repr(key).encode()) % n
+
+
+# Tolerance for fp32 sums of many terms (dweight/dbias): relative to max |ref|.
+SUM_TOL = {torch.float32: 2e-5, torch.float16: 3e-3, torch.bfloat16: 1e-2}
+
+
+# ------------------------------------------------------------------ golden fixtures
+@pytest.mark.parametrize("channel_last", [False, True])
+@pytest.mark.parametrize("case", golden_names("fwd_bwd"))
+def test_golden_fwd_bwd(golden, case, channel_last):
+    m = golden.meta[case]
+    if not channel_last and (m["init"] or m["final"]):
+        pytest.skip("states need channel-last")
+    it, wt = DT[m["itype"]], DT[m["wtype"]]
+    g = lambda k, dt: None if golden.get(case, k, dt) is None else golden.get(case, k, dt).to(DEV)
+    x, w, b = g("x", it), g("weight", wt), g("bias", wt)
+    B, D, L = x.shape
+    if channel_last:
+        if D % 8:
+            pytest.skip("channel-last needs dim % 8 == 0")
+        x = x.transpose(1, 2).contiguous().transpose(1, 2)
+    ini, dout, dfin = g("initial_states", it), g("dout", it), g("dfinal_states", it)
+    if ini is not None:
+        ini = ini.transpose(1, 2).contiguous().transpose(1, 2)
+    act = "silu" if m["silu"] else None
+    x.requires_grad_(); w.requires_grad_()
+    if b is not None: b.requires_grad_()
+    if ini is not None: ini.requires_grad_()
+    res = _api().causal_conv1d_fn(x, w, b, initial_states=ini, return_final_states=m["final"], activation=act)
+    out, fs = res if m["final"] else (res, None)
+    assert out.stride() == x.stride()
+    check(out, g("out", it), it, wt, "out vs golden")
+    if fs is not None:
+        assert torch.equal(fs, g("final_states", it)), "final_states must be bit-exact"
+        torch.autograd.backward([out, fs], [dout, dfin])
+    else:
+        out.backward(dout)
+    check(x.grad, g("dx", it), it, wt, "dx vs golden")
+    assert_close_sum(w.grad, g("dweight", wt), max(SUM_TOL[it], TOL[wt]), "dweight vs golden")
+    if b is not None:
+        assert_close_sum(b.grad, g("dbias", wt), max(SUM_TOL[it], TOL[wt]), "dbias vs golden")
+    if ini is not None:
+        check(ini.grad, g("dinitial_states", it), it, wt, "dinitial_states vs golden")
+    # tight gate against the float64 oracle, one rounding to the I/O dtype
+    xo, wo, bo = x.detach(), w.detach(), None if b is None else b.detach()
+    o = oracle.fwd(xo, wo, bo, initial_states=ini, return_final_states=m["final"], activation=act)
+    o = o[0] if m["final"] else o
+    assert_close(out, o.to(it), TOL[it], "out vs oracle")
+    gr = oracle.bwd(xo, wo, bo, dout, initial_states=ini, dfinal_states=dfin, activation=act)
+    assert_close(x.grad, gr["dx"].to(it), TOL[it], "dx vs oracle")
+    assert_close_sum(w.grad, gr["dweight"].to(wt), max(SUM_TOL[it], TOL[wt]), "dweight vs oracle")
+
+
+@pytest.mark.parametrize("case", golden_names("seq_idx"))
+def test_golden_seq_idx(golden, case):
+    m = golden.meta[case]
+    it = DT[m["itype"]]
+    g = lambda k, dt=None: None if golden.get(case, k, dt) is None else golden.get(case, k, dt).to(DEV)
+    x = g("x", it).transpose(1, 2).contiguous().transpose(1, 2).requires_grad_()
+    w, b, sidx, dout = g("weight").requires_grad_(), g("bias"), g("seq_idx"), g("dout", it)
+    if b is not None: b.requires_grad_()
+    out = _api().causal_conv1d_fn(x, w, b, seq_idx=sidx, activation="silu" if m["silu"] else None)
+    assert_close(out, g("out", it), TOL[it], "out")
+    if m["padded"]:
+        assert (out.detach()[(sidx < 0)[:, None, :].expand_as(out)] == 0).all(), "padded tokens must be exactly 0"
+    out.backward(dout)
+    assert_close(x.grad, g("dx", it), TOL[it], "dx")
+    assert_close_sum(w.grad, g("dweight"), SUM_TOL[it], "dweight")
+    if b is not None:
+        assert_close_sum(b.grad, g("dbias"), SUM_TOL[it], "dbias")
+
+
+@pytest.mark.parametrize("state_layout", ["channel_last", "channel_first"])
+@pytest.mark.parametrize("case", golden_names("update"))
+def test_golden_update(golden, case, state_layout):
+    m = golden.meta[case]
+    it, wt = DT[m["itype"]], DT[m["wtype"]]
+    g = lambda k, dt=None: None if golden.get(case, k, dt) is None else golden.get(case, k, dt).to(DEV)
+    x, st = g("x", it), g("conv_state", it)
+    if state_layout == "channel_last":
+        x = x.transpose(1, 2).contiguous().transpose(1, 2)
+        st = st.transpose(1, 2).contiguous().transpose(1, 2)
+    out = _api().causal_conv1d_update(x, st, g("weight", wt), g("bias", wt),
+                                      activation="silu" if m["silu"] else None, cache_seqlens=g("cache_seqlens"))
+    assert torch.equal(st, g("conv_state_out", it)), "conv_state must be bit-exact"
+    check(out, g("out", it), it, wt, "out")
+
+
+@pytest.mark.parametrize("case", golden_names("varlen_states"))
+def test_golden_varlen_states(golden, case):
+    m = golden.meta[case]
+    it = DT[m["itype"]]
+    x, cu = golden.get(case, "x", it).to(DEV), golden.get(case, "cu_seqlens").to(DEV)
+    from causal_conv1d_b200.causal_conv1d_varlen import causal_conv1d_varlen_states
+    st = causal_conv1d_varlen_states(x, cu, m["state_len"])
+    assert st.stride(1) == 1
+    assert torch.equal(st, golden.get(case, "states", it).to(DEV))
+    st32 = causal_conv1d_varlen_states(x, cu.int(), m["state_len"])
+    assert torch.equal(st32, st)
+
+
+# ------------------------------------------------------------------ reference-style grids
+SEQLENS = [1, 2, 8, 16, 32, 64, 128, 129, 130, 151, 256, 372, 512, 784, 1024, 1134, 2048, 4096]
+
+
+def _make_x(batch, dim, seqlen, itype, channel_last, pad=64):
+    """Non-contiguous slice of a wider tensor, as in tests/test_causal_conv1d.py:84-88."""
+    if not channel_last:
+        return torch.randn(batch, pad + dim + 64, seqlen, device=DEV, dtype=itype)[:, pad:pad + dim, :]
+    return torch.randn(batch, seqlen, pad + dim + 64, device=DEV, dtype=itype)[:, :, pad:pad + dim].transpose(1, 2)
+
+
+def _run_fwd_bwd(dim, seqlen, width, has_bias, silu, itype, channel_last, init, final, use_cpu_oracle):
+    torch.manual_seed(0)
+    batch = 2
+    x = _make_x(batch, dim, seqlen, itype, channel_last).requires_grad_()
+    weight = torch.randn(dim, width, device=DEV, dtype=torch.float32, requires_grad=True)
+    bias = torch.randn(dim, device=DEV, dtype=torch.float32, requires_grad=True) if has_bias else None
+    ini = (torch.randn(batch, width - 1, dim, device=DEV, dtype=itype).transpose(1, 2).requires_grad_()
+           if init else None)
+    act = "silu" if silu else None
+    res = _api().causal_conv1d_fn(x, weight, bias, initial_states=ini, return_final_states=final, activation=act)
+    out, fs = res if final else (res, None)
+    dout = torch.randn_like(out)
+    dfin = torch.randn(batch, width - 1, dim, device=DEV, dtype=itype).transpose(1, 2) if final else None
+    if final:
+        torch.autograd.backward([out, fs], [dout, dfin])
+    else:
+        out.backward(dout)
+    if use_cpu_oracle:
+        o = oracle.fwd(x, weight, bias, initial_states=ini, return_final_states=final, activation=act)
+        o_out, o_fs = o if final else (o, None)
+        r = oracle.bwd(x, weight, bias, dout, initial_states=ini, dfinal_states=dfin, activation=act)
+        r["out"], r["final_states"] = o_out, o_fs
+    else:
+        r = conv_grads64(x.detach(), weight.detach(), None if bias is None else bias.detach(), dout,
+                         None, None if ini is None else ini.detach(), dfin, act)
+        if final is False:
+            r["final_states"] = None
+    assert_close(out, r["out"].to(itype), TOL[itype], "out")
+    if final:
+        assert torch.equal(fs.cpu(), r["final_states"].to(itype).cpu()), "final_states must be bit-exact"
+    assert_close(x.grad, r["dx"].to(itype), TOL[itype], "dx")
+    assert_close_sum(weight.grad, r["dweight"], SUM_TOL[itype], "dweight")
+    if has_bias:
+        assert_close_sum(bias.grad, r["dbias"], SUM_TOL[itype], "dbias")
+    if init:
+        assert_close(ini.grad, r["dinitial_states"].to(itype), TOL[itype], "dinitial_states")
+
+
+@pytest.mark.parametrize("channel_last", [False, True])
+@pytest.mark.parametrize("itype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("width", [2, 3, 4])
+@pytest.mark.parametrize("seqlen", SEQLENS)
+def test_causal_conv1d_small_dim(seqlen, width, itype, channel_last):
+    """dim 64, every seqlen of the reference grid; bias / SiLU / states chosen per case."""
+    key = (seqlen, width, str(itype), channel_last)
+    has_bias, silu = bool(_pick(key + ("b",), 2)), bool(_pick(key + ("s",), 2))
+    init = final = False
+    if channel_last:
+        init, final = bool(_pick(key + ("i",), 2)), bool(_pick(key + ("f",), 2))
+    _run_fwd_bwd(64, seqlen, width, has_bias, silu, itype, channel_last, init, final, use_cpu_oracle=True)
+
+
+@pytest.mark.parametrize("channel_last", [False, True])
+@pytest.mark.parametrize("itype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("width", [2, 3, 4])
+@pytest.mark.parametrize("seqlen", [1, 2, 129, 151, 512, 1134, 4096])
+def test_causal_conv1d_wide_dim(seqlen, width, itype, channel_last):
+    """dim 4096 + 32 as in the reference grid, checked against the float64 PyTorch statement."""
+    key = (seqlen, width, str(itype), channel_last, "wide")
+    has_bias, silu = bool(_pick(key + ("b",), 2)), bool(_pick(key + ("s",), 2))
+    init = final = False
+    if channel_last:
+        init, final = bool(_pick(key + ("i",), 2)), bool(_pick(key + ("f",), 2))
+    _run_fwd_bwd(4096 + 32, seqlen, width, has_bias, silu, itype, channel_last, init, final, use_cpu_oracle=False)
+
+
+@pytest.mark.parametrize("silu,has_bias,init,final", list(itertools.product([False, True], repeat=4)))
+@pytest.mark.parametrize("width", [2, 3, 4])
+def test_causal_conv1d_all_flag_combos(width, silu, has_bias, init, final):
+    """Every bias x SiLU x initial_states x return_final_states combination, channel-last bf16/fp32."""
+    for itype, seqlen in ((torch.bfloat16, 151), (torch.float32, 2), (torch.float16, 1)):
+        _run_fwd_bwd(72, seqlen, width, has_bias, silu, itype, True, init, final, use_cpu_oracle=True)
+
+
+def _update_inputs(dim, width, seqlen, itype, entries, batch=64, state_layout="channel_last"):
+    torch.manual_seed(0)
+    x = torch.randn(batch, seqlen, dim, device=DEV, dtype=itype).transpose(-1, -2)
+    state_len = int(torch.randint(width - 1, width + 10, (1,)).item())
+    if state_layout == "channel_last":
+        st = torch.randn(entries, state_len, dim, device=DEV, dtype=itype).transpose(-1, -2)
+    else:
+        st = torch.randn(entries, dim, state_len, device=DEV, dtype=itype)
+    weight = torch.randn(dim, width, device=DEV, dtype=torch.float32)
+    return x, st, weight
+
+
+@pytest.mark.parametrize("state_layout", ["channel_last", "channel_first"])
+@pytest.mark.parametrize("itype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("has_cache_seqlens", [False, True])
+@pytest.mark.parametrize("seqlen", [1, 4, 5])
+@pytest.mark.parametrize("width", [2, 3, 4])
+@pytest.mark.parametrize("dim", [2048, 2048 + 16, 4096])
+def test_causal_conv1d_update(dim, width, seqlen, has_cache_seqlens, itype, state_layout):
+    key = (dim, width, seqlen, has_cache_seqlens, str(itype), state_layout)
+    has_bias, silu = bool(_pick(key + ("b",), 2)), bool(_pick(key + ("s",), 2))
+    x, st, weight = _update_inputs(dim, width, seqlen, itype, 64, state_layout=state_layout)
+    bias = torch.randn(dim, device=DEV, dtype=torch.float32) if has_bias else None
+    cache = torch.randint(0, 1024, (64,), dtype=torch.int32, device=DEV) if has_cache_seqlens else None
+    if has_cache_seqlens and seqlen > st.shape[-1]:
+        pytest.skip("circular write longer than the buffer is order-dependent in the reference oracle")
+    act = "silu" if silu else None
+    o_out, o_st = oracle.update(x, st, weight, bias, activation=act, cache_seqlens=cache)
+    out = _api().causal_conv1d_update(x, st, weight, bias, activation=act, cache_seqlens=cache)
+    assert torch.equal(st.cpu(), o_st.to(itype)), "conv_state must be bit-exact"
+    assert_close(out, o_out.to(itype), TOL[itype], "out")
+    # 2-D x (batch, dim) path
+    if seqlen == 1:
+        x2, st2, _ = _update_inputs(dim, width, 1, itype, 64, state_layout=state_layout)
+        out2 = _api().causal_conv1d_update(x2.squeeze(-1), st2, weight, bias, activation=act, cache_seqlens=cache)
+        assert out2.shape == (64, dim)
+        assert torch.equal(out2, out.squeeze(-1)) and torch.equal(st2, st)
+
+
+@pytest.mark.parametrize("itype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("has_cache_seqlens", [False, True])
+@pytest.mark.parametrize("seqlen", [1, 4, 5])
+@pytest.mark.parametrize("width", [2, 3, 4])
+@pytest.mark.parametrize("dim", [2048 + 16, 4096])
+def test_causal_conv1d_update_with_batch_gather(dim, width, seqlen, has_cache_seqlens, itype):
+    batch = 64
+    x, st, weight = _update_inputs(dim, width, seqlen, itype, 10 * batch)
+    bias = torch.randn(dim, device=DEV, dtype=torch.float32)
+    idx = torch.randperm(10 * batch)[:batch].to(dtype=torch.int32, device=DEV)
+    cache = torch.randint(0, 1024, (batch,), dtype=torch.int32, device=DEV) if has_cache_seqlens else None
+    if has_cache_seqlens and seqlen > st.shape[-1]:
+        pytest.skip("circular write longer than the buffer is order-dependent in the reference oracle")
+    o_out, o_st = oracle.update(x, st, weight, bias, activation="silu", cache_seqlens=cache, conv_state_indices=idx)
+    out = _api().causal_conv1d_update(x, st, weight, bias, activation="silu", cache_seqlens=cache,
+                                      conv_state_indices=idx)
+    assert torch.equal(st.cpu(), o_st.to(itype)), "pool must be bit-exact (gathered rows updated, others untouched)"
+    assert_close(out, o_out.to(itype), TOL[itype], "out")
+
+
+@pytest.mark.parametrize("state_layout", ["channel_last", "channel_first"])
+@pytest.mark.parametrize("itype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("seqlen", [1, 4, 5])
+@pytest.mark.parametrize("width", [2, 3, 4])
+def test_causal_conv1d_update_with_padding(width, seqlen, itype, state_layout):
+    batch, dim = 64, 2048 + 16
+    x, st, weight = _update_inputs(dim, width, seqlen, itype, 10 * batch, state_layout=state_layout)
+    bias = torch.randn(dim, device=DEV, dtype=torch.float32)
+    valid = torch.randperm(10 * batch)[:batch // 2].to(DEV)
+    idx = torch.cat([valid, torch.full((batch - batch // 2,), -1, device=DEV)])[torch.randperm(batch, device=DEV)].int()
+    before = st.clone()
+    o_out, o_st = oracle.update(x, st, weight, bias, activation="silu", conv_state_indices=idx)
+    out = _api().causal_conv1d_update(x, st, weight, bias, activation="silu", conv_state_indices=idx)
+    assert torch.all(out[idx < 0] == 0), "padded rows must output exactly zero"
+    assert torch.equal(st.cpu(), o_st.to(itype))
+    untouched = torch.ones(10 * batch, dtype=torch.bool, device=DEV)
+    untouched[valid] = False
+    assert torch.equal(st[untouched], before[untouched])
+    assert_close(out, o_out.to(itype), TOL[itype], "out")
+
+
+@pytest.mark.parametrize("itype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("dim", [2048, 2048 + 16, 4096, 100])
+def test_causal_conv1d_get_states(dim, itype):
+    from causal_conv1d_b200.causal_conv1d_varlen import causal_conv1d_varlen_states
+    torch.manual_seed(0)
+    seqlens = torch.randint(1, 32, (100,), device=DEV)
+    total = int(seqlens.sum())
+    x = torch.randn(total, dim, device=DEV, dtype=itype)
+    cu = torch.nn.functional.pad(seqlens.cumsum(0), (1, 0))   # int64
+    st = causal_conv1d_varlen_states(x, cu, 20)
+    assert torch.equal(st.cpu(), oracle.varlen_states(x, cu, 20).to(itype))
+
+
+@pytest.mark.parametrize("itype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("width", [2, 3, 4])
+@pytest.mark.parametrize("seqlen", [8, 16, 32, 64, 128, 151, 256, 372, 512, 784, 1024, 1134, 2048, 4096])
+@pytest.mark.parametrize("dim", [64, 4096 + 32])
+def test_causal_conv1d_varlen(dim, seqlen, width, itype):
+    """seq_idx fwd + bwd (tests/test_causal_conv1d.py:401-472), random sub-sequence splits,
+    half of the cases with a padded (-1) tail (:474-557)."""
+    key = (dim, seqlen, width, str(itype))
+    if dim > 64 and _pick(key, 3):
+        pytest.skip("thinned")
+    has_bias, silu, padded = bool(_pick(key + ("b",), 2)), bool(_pick(key + ("s",), 2)), bool(_pick(key + ("p",), 2))
+    torch.manual_seed(seqlen + dim + width)
+    batch = 3
+    rows = []
+    for b in range(batch):
+        true_len = int(torch.randint(seqlen // 2, seqlen, (1,))) if padded else seqlen
+        nsplits = int(torch.randint(1, 5, (1,)))
+        eos = torch.randperm(true_len - 1)[:nsplits].sort().values if true_len > 1 else torch.tensor([], dtype=torch.long)
+        bounds = torch.cat([torch.tensor([-1]), eos, torch.tensor([true_len - 1])])
+        lens = torch.diff(bounds).tolist()
+        ids = torch.cat([torch.full((int(s),), i + 7 * b, dtype=torch.int32) for i, s in enumerate(lens)])
+        rows.append(torch.cat([ids, torch.full((seqlen - true_len,), -1, dtype=torch.int32)]))
+    sidx = torch.stack(rows).to(DEV)
+    x = _make_x(batch, dim, seqlen, itype, True).requires_grad_()
+    weight = torch.randn(dim, width, device=DEV, dtype=torch.float32, requires_grad=True)
+    bias = torch.randn(dim, device=DEV, dtype=torch.float32, requires_grad=True) if has_bias else None
+    act = "silu" if silu else None
+    out = _api().causal_conv1d_fn(x, weight, bias, seq_idx=sidx, activation=act)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    r = conv_grads64(x.detach(), weight.detach(), None if bias is None else bias.detach(), dout, sidx, None, None, act)
+    assert_close(out, r["out"].to(itype), TOL[itype], "out")
+    assert (out.detach()[(sidx < 0)[:, None, :].expand_as(out)] == 0).all()
+    assert_close(x.grad, r["dx"].to(itype), TOL[itype], "dx")
+    assert_close_sum(weight.grad, r["dweight"], SUM_TOL[itype], "dweight")
+    if has_bias:
+        assert_close_sum(bias.grad, r["dbias"], SUM_TOL[itype], "dbias")
+    if dim == 64:   # and the CPU oracle on the small ones
+        o = oracle.fwd(x, weight, bias, seq_idx=sidx, activation=act)
+        assert_close(out, o.to(itype), TOL[itype], "out vs oracle")
+
+
+@pytest.mark.parametrize("channel_last", [False, True])
+def test_bwd_bitwise_reproducible(channel_last):
+    """10 backward runs give identical bits (the reference only promises this in its
+    deterministic mode, tests/test_causal_conv1d.py:560-575)."""
+    torch.manual_seed(123)
+    batch, dim, seqlen, width = 4, 1024, 2048, 4
+    if channel_last:
+        x = torch.randn(batch, seqlen, dim, device=DEV, dtype=torch.bfloat16).transpose(1, 2).requires_grad_()
+    else:
+        x = torch.randn(batch, dim, seqlen, device=DEV, dtype=torch.bfloat16).requires_grad_()
+    w = torch.randn(dim, width, device=DEV, requires_grad=True)
+    b = torch.randn(dim, device=DEV, requires_grad=True)
+    g = torch.randn_like(x)
+    ref = None
+    for _ in range(10):
+        x.grad = w.grad = b.grad = None
+        _api().causal_conv1d_fn(x, w, b, activation="silu").backward(g)
+        cur = (x.grad.clone(), w.grad.clone(), b.grad.clone())
+        if ref is None:
+            ref = cur
+        else:
+            assert all(torch.equal(a, c) for a, c in zip(ref, cur))
+
+
+def test_weight_dtypes_and_strides():
+    """16-bit weights (the dtype the reference tests never exercise) and a strided weight view."""
+    torch.manual_seed(5)
+    for itype, wtype in ((torch.bfloat16, torch.bfloat16), (torch.float16, torch.float16), (torch.float32, torch.bfloat16)):
+        x = torch.randn(2, 40, 100, device=DEV, dtype=itype)
+        wfull = torch.randn(40, 8, device=DEV).to(wtype)
+        w = wfull[:, 1:8:2]   # (40, 4), strides (8, 2)
+        b = torch.randn(40, device=DEV).to(wtype)
+        out = _api().causal_conv1d_fn(x, w, b, activation="silu")
+        assert_close(out, oracle.fwd(x, w, b, activation="silu").to(itype), TOL[itype], "out")
+
+
+def test_errors():
+    api = _api()
+    x = torch.randn(2, 16, 32, device=DEV)
+    with pytest.raises(RuntimeError, match="width between 2 and 4"):
+        api.causal_conv1d_fn(x, torch.randn(16, 5, device=DEV))
+    with pytest.raises(NotImplementedError):
+        api.causal_conv1d_fn(x, torch.randn(16, 4, device=DEV), activation="relu")
+    with pytest.raises(RuntimeError, match="divisible by 8"):
+        api.causal_conv1d_fn(torch.randn(2, 32, 12, device=DEV).transpose(1, 2), torch.randn(12, 4, device=DEV))
+    with pytest.raises(RuntimeError, match="channel last"):
+        api.causal_conv1d_fn(x, torch.randn(16, 4, device=DEV), seq_idx=torch.zeros(2, 32, dtype=torch.int32, device=DEV))
+    with pytest.raises(AssertionError):
+        api.causal_conv1d_fn(x, torch.randn(16, 4, device=DEV), return_final_states=True)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        api.causal_conv1d_fn(x.cpu(), torch.randn(16, 4))
+    with pytest.raises(RuntimeError, match="width - 1"):
+        api.causal_conv1d_update(torch.randn(2, 16, device=DEV), torch.randn(2, 16, 2, device=DEV), torch.randn(16, 4, device=DEV))

@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Benchmark of the causal depthwise conv1d hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Workload (N = 1): the Mamba-1 2.8B-shape prefill, forward + backward, bf16:
+x (8, 5120, 2048) channel-first, weight (5120, 4) / bias bf16, SiLU.  One step = one forward
+plus one backward over one batch.  At N > 1 every rank runs the same per-GPU batch (weak
+scaling) and each step ends with the single all-reduce of the packed fp32 dweight/dbias.
+
+Prints ONE JSON line (rank 0).  `value` is whole-job algorithmic GB/s with inputs resident
+in HBM; `e2e` is the same metric through the public Python API with pinned HOST buffers,
+copies inside the timed region.  `--impl reference` times the CPU port of the reference's
+algorithm (oracle/) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# ---- workload: BASELINE config "Mamba-1 2.8B-shape prefill, fwd+bwd" ---------------------
+BATCH_PER_GPU, DIM, SEQLEN, WIDTH = 8, 5120, 2048, 4
+ELEM = 2  # bf16
+METRIC = "fwd+bwd algorithmic HBM GB/s, Mamba-1 2.8B prefill shape (8,5120,2048) bf16 width 4 SiLU"
+UNIT = "GB/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per launch of the backward kernel from the ncu capture summarised in
+# profiles/ (None until captured).
+BWD_KERNEL_DRAM_TRAFFIC_BYTES = None
+
+
+def algorithmic_bytes(batch):
+    n = batch * DIM * SEQLEN
+    w = (WIDTH + 1) * DIM
+    fwd = 2 * n * ELEM + w * ELEM                 # x + out, weights + bias
+    bwd = 3 * n * ELEM + w * ELEM + w * 4         # x, dout, dx, weights, fp32 grads
+    return fwd, bwd
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback (earlier pool measurement)"
+
+
+# ---- clocks ---------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs (NVML,
+    read-only)."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, torch_device_index, period=0.02):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.period, self._stop, self._thread, self.ok = period, threading.Event(), None, False
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(torch_device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self.nv, self.h = pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception as e:  # noqa: BLE001
+            self.err = repr(e)
+
+    def _read_reasons(self):
+        for name in ("nvmlDeviceGetCurrentClocksEventReasons", "nvmlDeviceGetCurrentClocksThrottleReasons"):
+            fn = getattr(self.nv, name, None)
+            if fn is not None:
+                return int(fn(self.h))
+        return 0
+
+    def _loop(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM)))
+                bits = self._read_reasons()
+                for bit, name in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.ok:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.ok or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "note": "no NVML samples"}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ---- CPU port (oracle) timing -------------------------------------------------------------------
+def cpu_port_inputs(batch, dim, seqlen, seed=1):
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((batch, dim, seqlen), dtype=np.float32)
+    dout = rng.standard_normal((batch, dim, seqlen), dtype=np.float32)
+    w = (rng.random((dim, WIDTH), dtype=np.float32) - 0.5)
+    b = (rng.random((dim,), dtype=np.float32) - 0.5)
+    out, dx = np.empty_like(x), np.empty_like(x)
+    dw, db = np.empty_like(w), np.empty_like(b)
+    return x, dout, w, b, out, dx, dw, db
+
+
+def cpu_port_step(buf):
+    import oracle
+    x, dout, w, b, out, dx, dw, db = buf
+    t = oracle.fwd_f32_timed(x, w, b, out, WIDTH, True)
+    t += oracle.bwd_f32_timed(x, w, b, dout, dx, dw, db, WIDTH, True)
+    return t
+
+
+def cpu_baseline(target_seconds=12.0):
+    """The CPU port on a bounded sample: one batch row of the workload, repeated."""
+    import oracle
+    oracle.build()
+    buf = cpu_port_inputs(1, DIM, SEQLEN)
+    cpu_port_step(buf)  # warm-up
+    n, total = 0, 0.0
+    while total < target_seconds and n < 200:
+        total += cpu_port_step(buf)
+        n += 1
+    fwd, bwd = algorithmic_bytes(1)
+    return {"value": round((fwd + bwd) * n / total / 1e9, 3), "unit": UNIT, "cores": oracle.max_threads(),
+            "kind": "port", "sample": f"1 of {BATCH_PER_GPU} batch rows (1,{DIM},{SEQLEN}), fwd+bwd in fp32, "
+                                      f"{n} repeats, {total:.1f} s; OpenMP over rows"}
+
+
+def run_reference(args):
+    """--impl reference: the CPU port of the reference's algorithm on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    cores = oracle.max_threads()
+    # size the per-step sample so that the whole run stays within ~2.5 minutes
+    probe = cpu_port_inputs(1, 256, SEQLEN)
+    cpu_port_step(probe)
+    t_probe = min(cpu_port_step(probe) for _ in range(3))
+    per_channel = t_probe / 256
+    budget = 150.0 / max(1, args.steps + args.warmup)
+    dim = int(max(64, min(DIM, budget / per_channel)))
+    dim -= dim % 8
+    buf = cpu_port_inputs(1, dim, SEQLEN)
+    for _ in range(args.warmup):
+        cpu_port_step(buf)
+    total = 0.0
+    for _ in range(args.steps):
+        total += cpu_port_step(buf)
+    n = dim * SEQLEN
+    step_bytes = 5 * n * ELEM + (WIDTH + 1) * dim * (2 * ELEM + 4)
+    value = step_bytes * args.steps / total / 1e9
+    sample = f"(1,{dim},{SEQLEN}) slice of the (8,{DIM},{SEQLEN}) batch per step, fp32 arithmetic, fwd+bwd"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(total / args.steps * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {
+        "workload": "C2 Mamba-1 2.8B-shape prefill fwd+bwd: x (8,5120,2048) bf16 channel-first per GPU, "
+                    "weight (5120,4)+bias bf16, SiLU, dout N(0,1), seed 1",
+        "batch_per_gpu": BATCH_PER_GPU, "global_batch": BATCH_PER_GPU * n_gpus, "dim": DIM, "seq_len": SEQLEN,
+        "width": WIDTH, "activation": "silu",
+        "parallelism": f"batch-sharded dp{n_gpus}, one NCCL all-reduce of packed fp32 dweight|dbias per step"
+                       if n_gpus > 1 else "single GPU",
+        "l2": "inputs larger than L2: 3 rotating buffer sets of 671 MB (x, dout, out, dx) per GPU",
+    }
+
+
+# ---- the B200 arm -------------------------------------------------------------------------------
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    from causal_conv1d_b200 import causal_conv1d_fn
+    from causal_conv1d_b200._ext import ext
+    from causal_conv1d_b200.distributed import packed_grad_buffer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+        args.gpus = world
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path in causal_conv1d_b200")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, K, Wm = BATCH_PER_GPU, args.steps, args.warmup
+    torch.manual_seed(1 + rank)
+    nsets = 3
+    sets = []
+    for _ in range(nsets):
+        x = torch.randn(B, DIM, SEQLEN, device=dev, dtype=torch.bfloat16)
+        dout = torch.randn(B, DIM, SEQLEN, device=dev, dtype=torch.bfloat16)
+        sets.append((x, dout, torch.empty_like(x), torch.empty_like(x)))
+    gen = torch.Generator(device="cpu").manual_seed(1)
+    weight = (torch.rand(DIM, WIDTH, generator=gen) - 0.5).to(device=dev, dtype=torch.bfloat16)
+    bias = (torch.rand(DIM, generator=gen) - 0.5).to(device=dev, dtype=torch.bfloat16)
+    packed, dweight, dbias = packed_grad_buffer(DIM, WIDTH, True, dev)
+
+    def step(i, evs=None):
+        x, dout, out, dx = sets[i % nsets]
+        if evs is not None:
+            evs[0].record()
+        ext.causal_conv1d_fwd(x, weight, bias, None, None, out, None, True)
+        if evs is not None:
+            evs[1].record()
+        ext.causal_conv1d_bwd(x, weight, bias, dout, None, None, None, dx, dweight, dbias, None, True, False)
+        if evs is not None:
+            evs[2].record()
+        if world > 1:
+            dist.all_reduce(packed)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(Wm, 3)):
+        step(i)
+    barrier()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        start.record()
+        for i in range(K):
+            step(i, evs[i])
+        end.record()
+        barrier()
+    total_ms = start.elapsed_time(end)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / K
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / K
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / K
+    fwd_b, bwd_b = algorithmic_bytes(B)
+    value = (fwd_b + bwd_b) * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: public API, pinned host buffers, copies inside the timed region -------------
+    k_e2e = max(3, min(K, 12))
+    hx = torch.randn(B, DIM, SEQLEN, dtype=torch.bfloat16).pin_memory()
+    hdout = torch.randn(B, DIM, SEQLEN, dtype=torch.bfloat16).pin_memory()
+    hout, hdx = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
+    hdw = torch.empty(DIM, WIDTH, dtype=torch.bfloat16).pin_memory()
+    hdb = torch.empty(DIM, dtype=torch.bfloat16).pin_memory()
+    wp, bp = weight.clone().requires_grad_(), bias.clone().requires_grad_()
+
+    def e2e_step():
+        xd = hx.to(dev, non_blocking=True).requires_grad_()
+        dd = hdout.to(dev, non_blocking=True)
+        wp.grad = bp.grad = None
+        out = causal_conv1d_fn(xd, wp, bp, activation="silu")
+        out.backward(dd)
+        if world > 1:
+            dist.all_reduce(wp.grad)
+            dist.all_reduce(bp.grad)
+        hout.copy_(out.detach(), non_blocking=True)
+        hdx.copy_(xd.grad, non_blocking=True)
+        hdw.copy_(wp.grad, non_blocking=True)
+        hdb.copy_(bp.grad, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(k_e2e):
+        e2e_step()
+    e2.record()
+    barrier()
+    e2e_ms = s2.elapsed_time(e2)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = (fwd_b + bwd_b) * world / (e2e_ms / k_e2e * 1e-3) / 1e9
+    h2d = hx.numel() * ELEM + hdout.numel() * ELEM
+    d2h = hout.numel() * ELEM + hdx.numel() * ELEM + hdw.numel() * ELEM + hdb.numel() * ELEM
+
+    if rank == 0:
+        peak, peak_src = measured_peak()
+        bwd_gbs = bwd_b / (bwd_ms * 1e-3) / 1e9
+        fwd_gbs = fwd_b / (fwd_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(Wm, 3),
+            "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "clocks": clocks.summary(),
+            "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": k_e2e, "api": "causal_conv1d_fn + autograd backward, pinned host tensors"},
+            "gpu_launches": 3 * K,
+            "roofline": {"bound": "hbm", "kernel": "bwd_cf_vec_kernel (+ reduce_partials_kernel, same launch pair)",
+                         "achieved": round(bwd_gbs, 1), "peak": peak, "unit": UNIT, "frac": round(bwd_gbs / peak, 4),
+                         "traffic": BWD_KERNEL_DRAM_TRAFFIC_BYTES, "peak_source": peak_src,
+                         "algorithmic_bytes_per_launch": bwd_b, "avg_launch_ms": round(bwd_ms, 5),
+                         "frac_of_nominal_8TBs": round(bwd_gbs / NOMINAL_HBM_GBS, 4)},
+            "kernels": {"fwd_cf_vec_kernel": {"gbs": round(fwd_gbs, 1), "ms": round(fwd_ms, 5), "frac": round(fwd_gbs / peak, 4)},
+                        "bwd": {"gbs": round(bwd_gbs, 1), "ms": round(bwd_ms, 5), "frac": round(bwd_gbs / peak, 4)}},
+            "tokens_per_s": round(B * world * SEQLEN / (ms_per_step * 1e-3), 1),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the ~12 s CPU-port timing")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -40,15 +40,16 @@ int check_conv_common(int itype, int wtype, int width, int64_t batch, int64_t di
     *channel_last = x_cs == 1 && x_ls > 1;
     if (*channel_last) {
         if (dim % 8 != 0) return CC1D_ERR_CL_DIM;
-        if (x_ls % 8 != 0 || x_bs % 8 != 0) return CC1D_ERR_CL_STRIDE;
+        if (x_ls % 8 != 0 || (batch > 1 && x_bs % 8 != 0)) return CC1D_ERR_CL_STRIDE;
     }
     return CC1D_OK;
 }
 
-int check_same_layout(bool channel_last, int64_t bs, int64_t cs, int64_t ls, int64_t seqlen, int64_t dim) {
+int check_same_layout(bool channel_last, int64_t bs, int64_t cs, int64_t ls, int64_t seqlen, int64_t dim,
+                      int64_t batch) {
     if (channel_last) {
         if (cs != 1 && dim > 1) return CC1D_ERR_STRIDE;
-        if (ls % 8 != 0 || bs % 8 != 0) return CC1D_ERR_CL_STRIDE;
+        if ((seqlen > 1 && ls % 8 != 0) || (batch > 1 && bs % 8 != 0)) return CC1D_ERR_CL_STRIDE;
     } else {
         if (ls != 1 && seqlen > 1) return CC1D_ERR_STRIDE;
     }
@@ -93,13 +94,17 @@ int cc1d_fwd(const cc1d_fwd_params *p, cc1d_stream_t stream) {
     if (rc != CC1D_OK) return rc;
     if (p->out == nullptr) return CC1D_ERR_NULL;
     if (!elem_aligned(p->out, p->itype)) return CC1D_ERR_ALIGN;
-    rc = check_same_layout(cl, p->out_batch_stride, p->out_c_stride, p->out_l_stride, p->seqlen, p->dim);
+    rc = check_same_layout(cl, p->out_batch_stride, p->out_c_stride, p->out_l_stride, p->seqlen, p->dim, p->batch);
     if (rc != CC1D_OK) return rc;
     if (!cl && (p->seq_idx || p->initial_states || p->final_states)) return CC1D_ERR_LAYOUT;
     if (p->initial_states && p->initial_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
     if (p->final_states && p->final_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    return cl ? launch_fwd_channel_last(*p, s) : launch_fwd_channel_first(*p, s);
+    // strides of extent-1 dimensions carry no information (PyTorch leaves them arbitrary)
+    cc1d_fwd_params q = *p;
+    if (q.batch <= 1) q.x_batch_stride = q.out_batch_stride = q.initial_states_batch_stride = q.final_states_batch_stride = 0;
+    if (q.width == 2) q.initial_states_l_stride = q.final_states_l_stride = 0;
+    return cl ? launch_fwd_channel_last(q, s) : launch_fwd_channel_first(q, s);
 }
 
 static int check_bwd(const cc1d_bwd_params *p, bool *cl) {
@@ -111,9 +116,9 @@ static int check_bwd(const cc1d_bwd_params *p, bool *cl) {
     if ((p->bias == nullptr) != (p->dbias == nullptr)) return CC1D_ERR_NULL;
     if (!elem_aligned(p->dout, p->itype) || !elem_aligned(p->dx, p->itype) ||
         !elem_aligned(p->dweight, CC1D_F32) || !elem_aligned(p->dbias, CC1D_F32)) return CC1D_ERR_ALIGN;
-    rc = check_same_layout(*cl, p->dout_batch_stride, p->dout_c_stride, p->dout_l_stride, p->seqlen, p->dim);
+    rc = check_same_layout(*cl, p->dout_batch_stride, p->dout_c_stride, p->dout_l_stride, p->seqlen, p->dim, p->batch);
     if (rc != CC1D_OK) return rc;
-    rc = check_same_layout(*cl, p->dx_batch_stride, p->dx_c_stride, p->dx_l_stride, p->seqlen, p->dim);
+    rc = check_same_layout(*cl, p->dx_batch_stride, p->dx_c_stride, p->dx_l_stride, p->seqlen, p->dim, p->batch);
     if (rc != CC1D_OK) return rc;
     if (!*cl && (p->seq_idx || p->initial_states || p->dfinal_states || p->dinitial_states)) return CC1D_ERR_LAYOUT;
     if (p->initial_states && p->initial_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
@@ -135,7 +140,13 @@ int cc1d_bwd(const cc1d_bwd_params *p, cc1d_stream_t stream) {
     if (rc != CC1D_OK) return rc;
     if (p->workspace == nullptr || p->workspace_bytes < cc1d_bwd_workspace_bytes(p)) return CC1D_ERR_WORKSPACE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    return cl ? launch_bwd_channel_last(*p, s) : launch_bwd_channel_first(*p, s);
+    cc1d_bwd_params q = *p;
+    if (q.batch <= 1) {
+        q.x_batch_stride = q.dout_batch_stride = q.dx_batch_stride = 0;
+        q.initial_states_batch_stride = q.dfinal_states_batch_stride = q.dinitial_states_batch_stride = 0;
+    }
+    if (q.width == 2) q.initial_states_l_stride = q.dfinal_states_l_stride = q.dinitial_states_l_stride = 0;
+    return cl ? launch_bwd_channel_last(q, s) : launch_bwd_channel_first(q, s);
 }
 
 int cc1d_update(const cc1d_update_params *p, cc1d_stream_t stream) {

@@ -44,7 +44,10 @@ def test_golden_fwd_bwd(golden, case, channel_last):
     if channel_last:
         if D % 8:
             pytest.skip("channel-last needs dim % 8 == 0")
-        x = x.transpose(1, 2).contiguous().transpose(1, 2)
+        # a slice of a wider token-major buffer, so that stride(2) > 1 even when seqlen == 1
+        buf = torch.empty(B, L, D + 8, device=DEV, dtype=it)
+        buf[:, :, :D] = x.transpose(1, 2)
+        x = buf[:, :, :D].transpose(1, 2)
     ini, dout, dfin = g("initial_states", it), g("dout", it), g("dfinal_states", it)
     if ini is not None:
         ini = ini.transpose(1, 2).contiguous().transpose(1, 2)

@@ -226,7 +226,7 @@ def run_b200(args):
 
     B, K, Wm = BATCH_PER_GPU, args.steps, args.warmup
     torch.manual_seed(1 + rank)
-    nsets = 3
+    nsets = max(1, args.buffer_sets)
     sets = []
     for _ in range(nsets):
         x = torch.randn(B, DIM, SEQLEN, device=dev, dtype=torch.bfloat16)
@@ -278,6 +278,13 @@ def run_b200(args):
     value = (fwd_b + bwd_b) * world / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end: public API, pinned host buffers, copies inside the timed region -------------
+    if args.skip_e2e:
+        if rank == 0:
+            print(json.dumps({"partial": True, "ms_per_step": ms_per_step, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+                              "value": value}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     k_e2e = max(3, min(K, 12))
     hx = torch.randn(B, DIM, SEQLEN, dtype=torch.bfloat16).pin_memory()
     hdout = torch.randn(B, DIM, SEQLEN, dtype=torch.bfloat16).pin_memory()
@@ -353,6 +360,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the ~12 s CPU-port timing")
+    ap.add_argument("--buffer-sets", type=int, default=3, help="rotating input/output sets (profiling: 1)")
+    ap.add_argument("--skip-e2e", action="store_true", help="kernel loop only (for ncu captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -33,6 +33,7 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
+    "--use_fast_math",   # flush-to-zero special-function paths; state copies never go through arithmetic
     "-Xptxas", "-v",
 ]
 

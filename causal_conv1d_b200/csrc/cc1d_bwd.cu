@@ -85,55 +85,19 @@ struct BwdCfArgs {
     uint32_t vpr, upr, n_units;
 };
 
-// Vector v of a row: a 16-byte load when it lies fully inside the row, element loads for the
-// ragged last vector, zeros beyond.
-template <typename T>
-__device__ __forceinline__ uint4 load_row_vec(const T *__restrict__ row, uint32_t v, uint32_t vpr, uint32_t L) {
-    constexpr int V = Elem<T>::kVec;
-    if ((uint64_t)(v + 1) * V <= L) return ld_stream(row + (uint64_t)v * V);
-    if (v >= vpr) return make_uint4(0, 0, 0, 0);
-    float f[V];
-    #pragma unroll
-    for (int i = 0; i < V; ++i) {
-        const uint64_t t = (uint64_t)v * V + i;
-        f[i] = t < L ? Elem<T>::to_f(row[t]) : 0.f;
-    }
-    return pack<T>(f);
+// g = dout * silu'(y) for one element; `y_or_h` is the pre-activation computed with the taps
+// scaled as the chosen SiLU form wants them (y, or y/2 for the tanh form).
+template <bool kSilu, bool kTanh>
+__device__ __forceinline__ float grad_through_act(float dout, float y_or_h) {
+    if (!kSilu) return dout;
+    return dout * (kTanh ? dsilu_half_arg(y_or_h) : dsilu_f(y_or_h));
 }
 
-template <typename T>
-__device__ __forceinline__ void store_row_vec(T *__restrict__ row, uint32_t v, uint32_t L, const float *f) {
-    constexpr int V = Elem<T>::kVec;
-    if ((uint64_t)(v + 1) * V <= L) {
-        st_stream(row + (uint64_t)v * V, pack<T>(f));
-    } else {
-        #pragma unroll
-        for (int i = 0; i < V; ++i) {
-            const uint64_t t = (uint64_t)v * V + i;
-            if (t < L) row[t] = Elem<T>::from_f(f[i]);
-        }
-    }
-}
-
-// Fetch the trailing width-1 elements' registers of the previous lane's vector (lane 0 gets
-// lane 31's `old`), see fwd_cf_vec_kernel.
-template <int V, int W>
-__device__ __forceinline__ uint4 prev_vector_tail(const uint4 &own, const uint4 &old, int lane) {
-    const int src_lane = (lane + 31) & 31;
-    uint4 prev = make_uint4(0, 0, 0, 0);
-    if (V == 4) {
-        if (W >= 4) prev.y = __shfl_sync(kFullMask, lane == 31 ? old.y : own.y, src_lane);
-        if (W >= 3) prev.z = __shfl_sync(kFullMask, lane == 31 ? old.z : own.z, src_lane);
-    } else {
-        if (W >= 4) prev.z = __shfl_sync(kFullMask, lane == 31 ? old.z : own.z, src_lane);
-    }
-    prev.w = __shfl_sync(kFullMask, lane == 31 ? old.w : own.w, src_lane);
-    return prev;
-}
-
-template <typename T, int W, bool kSilu, int kVecs>
+// kFull: seqlen is a multiple of the vector width and every unit has all 32 * kVecs vectors.
+template <typename T, int W, bool kSilu, bool kFull, int kVecs>
 __global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
     constexpr int V = Elem<T>::kVec;
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
     const int lane = threadIdx.x & 31;
     const uint32_t warps_per_cta = blockDim.x >> 5;
     const uint32_t nwarps = gridDim.x * warps_per_cta;
@@ -147,38 +111,39 @@ __global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
         const T *__restrict__ xr = reinterpret_cast<const T *>(a.x) + b * a.x_bs + c * a.x_cs;
         const T *__restrict__ dr = reinterpret_cast<const T *>(a.dout) + b * a.d_bs + c * a.d_cs;
         T *__restrict__ dxr = reinterpret_cast<T *>(a.dx) + b * a.o_bs + c * a.o_cs;
-        const uint32_t v0 = seg * (32 * kVecs);
+        const uint32_t e0 = (seg * (32 * kVecs) + lane) * V;
 
         uint4 xraw[kVecs], draw[kVecs];
         #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
-            const uint32_t v = v0 + j * 32 + lane;
-            xraw[j] = load_row_vec<T>(xr, v, a.vpr, L);
-            draw[j] = load_row_vec<T>(dr, v, a.vpr, L);
+            xraw[j] = load_row_vec<T, kFull>(xr, e0 + j * 32 * V, L);
+            draw[j] = load_row_vec<T, kFull>(dr, e0 + j * 32 * V, L);
         }
         // left halo of the unit (x only) and the first vector of the next unit (x and dout),
         // needed by lane 0 and lane 31 respectively
         uint4 halo0 = make_uint4(0, 0, 0, 0), xedge = make_uint4(0, 0, 0, 0), dedge = make_uint4(0, 0, 0, 0);
-        if (lane == 0 && v0 > 0) halo0 = ld_cached(xr + (uint64_t)(v0 - 1) * V);
-        if (lane == 31) {
-            const uint32_t vn = v0 + kVecs * 32;
-            if (vn < a.vpr) {
-                if (kSilu) xedge = load_row_vec<T>(xr, vn, a.vpr, L);
-                dedge = load_row_vec<T>(dr, vn, a.vpr, L);
-            }
+        if (lane == 0 && seg > 0) halo0 = ld_cached(xr + e0 - V);
+        if (lane == 31 && seg + 1 < a.upr) {
+            const uint32_t en = e0 + kVecs * 32 * V - 31 * V;   // first element of the next unit
+            if (kSilu) xedge = load_row_vec<T, false>(xr, en, L);
+            dedge = load_row_vec<T, false>(dr, en, L);
         }
 
-        float wv[W];
+        float wv[W], wy[W];   // taps, and taps scaled for the pre-activation recompute
+        const float pre = kTanh ? 0.5f : 1.f;
         #pragma unroll
-        for (int k = 0; k < W; ++k) wv[k] = load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype);
-        const float bv = a.bias != nullptr ? load_w(a.bias, c, a.wtype) : 0.f;
+        for (int k = 0; k < W; ++k) {
+            wv[k] = load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype);
+            wy[k] = pre * wv[k];
+        }
+        const float by = a.bias != nullptr ? pre * load_w(a.bias, c, a.wtype) : 0.f;
 
         float g[kVecs][V];
         float dw[W], db = 0.f;
         #pragma unroll
         for (int k = 0; k < W; ++k) dw[k] = 0.f;
 
-        // pass 1: g, dweight, dbias
+        // pass 1: g, dweight, dbias (elements past the row end have dout == 0, so g == 0)
         #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
             uint4 prev = prev_vector_tail<V, W>(xraw[j], xraw[j > 0 ? j - 1 : 0], lane);
@@ -195,10 +160,10 @@ __global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
             #pragma unroll
             for (int i = 0; i < V; ++i) {
                 if (kSilu) {
-                    float y = bv;
+                    float y = by;
                     #pragma unroll
-                    for (int k = 0; k < W; ++k) y = fmaf(wv[k], xx[i + k], y);
-                    g[j][i] *= dsilu_f(y);
+                    for (int k = 0; k < W; ++k) y = fmaf(wy[k], xx[i + k], y);
+                    g[j][i] = grad_through_act<kSilu, kTanh>(g[j][i], y);
                 }
                 db += g[j][i];
                 #pragma unroll
@@ -217,13 +182,10 @@ __global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
             for (int k = 0; k < W - 1; ++k) { xx[k] = xt[V - (W - 1) + k]; xx[W - 1 + k] = xn[k]; }
             #pragma unroll
             for (int i = 0; i < W - 1; ++i) {
-                ge[i] = dn[i];
-                if (kSilu) {
-                    float y = bv;
-                    #pragma unroll
-                    for (int k = 0; k < W; ++k) y = fmaf(wv[k], xx[i + k], y);
-                    ge[i] *= dsilu_f(y);
-                }
+                float y = by;
+                #pragma unroll
+                for (int k = 0; k < W; ++k) y = fmaf(wy[k], xx[i + k], y);
+                ge[i] = grad_through_act<kSilu, kTanh>(dn[i], y);
             }
         }
 
@@ -242,8 +204,8 @@ __global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
                 if (j == kVecs - 1 && lane == 31) r = ge[k];
                 gg[V + k] = r;
             }
-            const uint32_t v = v0 + j * 32 + lane;
-            if (v >= a.vpr) continue;
+            const uint32_t e = e0 + j * 32 * V;
+            if (!kFull && e >= L) continue;
             float o[V];
             #pragma unroll
             for (int i = 0; i < V; ++i) {
@@ -252,7 +214,7 @@ __global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
                 for (int k = 0; k < W; ++k) acc = fmaf(wv[k], gg[i + (W - 1 - k)], acc);
                 o[i] = acc;
             }
-            store_row_vec<T>(dxr, v, L, o);
+            store_row_vec<T, kFull>(dxr, e, L, o);
         }
 
         // warp tree (fixed order), one partial row per unit
@@ -384,7 +346,7 @@ size_t bwd_workspace_bytes_channel_first(const cc1d_bwd_params &p) {
 
 int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream) {
     const uint64_t rows = (uint64_t)p.batch * (uint64_t)p.dim;
-    if (p.seqlen >= (1ll << 31) || p.dim >= (1ll << 31)) return CC1D_ERR_TOO_LARGE;
+    if (p.seqlen >= (1ll << 31) - 4096 || p.dim >= (1ll << 31)) return CC1D_ERR_TOO_LARGE;
     const CfPlan pl = plan_channel_first(p);
     if (pl.n_units >= (1ull << 32)) return CC1D_ERR_TOO_LARGE;
     if (pl.n_units * (uint64_t)(p.width + 1) * sizeof(float) > p.workspace_bytes) return CC1D_ERR_WORKSPACE;
@@ -403,9 +365,11 @@ int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream) {
         if (pl.vec) {
             const uint64_t ctas = (pl.n_units + 7) / 8;
             const unsigned grid = (unsigned)(ctas < (uint64_t)sms * 8 ? ctas : (uint64_t)sms * 8);
-            CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
-                bwd_cf_vec_kernel<T, W, kSilu, 4><<<grid, 256, 0, stream>>>(a);
-            });););
+            const bool full = p.seqlen % vec_elems(p.itype) == 0 && pl.vpr % 128 == 0;
+            CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
+                CC1D_DISPATCH_BOOL(full, kFull, {
+                    bwd_cf_vec_kernel<T, W, kSilu, kFull, 4><<<grid, 256, 0, stream>>>(a);
+                }););););
         } else {
             const unsigned grid = (unsigned)(pl.n_units < (uint64_t)sms * 16 ? pl.n_units : (uint64_t)sms * 16);
             CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {

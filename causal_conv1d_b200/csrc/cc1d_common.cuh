@@ -97,12 +97,74 @@ template <> __device__ __forceinline__ uint4 pack<__half>(const float *f) {
 }
 
 // ---- activation ---------------------------------------------------------------------------
+// Two evaluations of SiLU.  "exact": sigmoid through ex2 + rcp (2 special-function ops per
+// element).  "tanh": sigmoid(y) = 0.5 * tanh(y/2) + 0.5 with the hardware tanh.approx (1
+// special-function op, absolute error ~2.5e-4 in sigmoid) — used for bf16 I/O only, whose
+// own rounding (2^-9 relative) dominates that error; fp32 and fp16 use the exact form.
+// The tanh forms take h = y/2, which callers get for free by halving weights and bias.
 __device__ __forceinline__ float sigmoid_f(float y) { return __fdividef(1.f, 1.f + __expf(-y)); }
 __device__ __forceinline__ float silu_f(float y) { return __fdividef(y, 1.f + __expf(-y)); }
 // d silu(y) / dy
 __device__ __forceinline__ float dsilu_f(float y) {
     const float s = sigmoid_f(y);
     return s * (1.f + y * (1.f - s));
+}
+__device__ __forceinline__ float tanh_approx(float x) {
+    float r;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+// silu(2h) = h + h * tanh(h)
+__device__ __forceinline__ float silu_half_arg(float h) { return fmaf(h, tanh_approx(h), h); }
+// silu'(2h) = 0.5 * (1 + t + h * (1 - t^2)),  t = tanh(h)
+__device__ __forceinline__ float dsilu_half_arg(float h) {
+    const float t = tanh_approx(h);
+    return fmaf(0.5f, fmaf(h, fmaf(-t, t, 1.f), t), 0.5f);
+}
+template <typename T> struct UseTanhSilu { static constexpr bool value = false; };
+template <> struct UseTanhSilu<__nv_bfloat16> { static constexpr bool value = true; };
+
+// ---- channel-first row access: 16-byte vectors of one (batch, channel) row -----------------
+// Vector at element offset e of a row of L elements: one 16-byte load when it lies fully
+// inside the row (always, when kFull), element loads for the ragged last vector, zeros beyond.
+template <typename T, bool kFull>
+__device__ __forceinline__ uint4 load_row_vec(const T *__restrict__ row, uint32_t e, uint32_t L) {
+    constexpr int V = Elem<T>::kVec;
+    if (kFull || e + V <= L) return ld_stream(row + e);
+    if (e >= L) return make_uint4(0, 0, 0, 0);
+    float f[V];
+    #pragma unroll
+    for (int i = 0; i < V; ++i) f[i] = e + i < L ? Elem<T>::to_f(row[e + i]) : 0.f;
+    return pack<T>(f);
+}
+
+template <typename T, bool kFull>
+__device__ __forceinline__ void store_row_vec(T *__restrict__ row, uint32_t e, uint32_t L, const float *f) {
+    constexpr int V = Elem<T>::kVec;
+    if (kFull || e + V <= L) {
+        st_stream(row + e, pack<T>(f));
+    } else {
+        #pragma unroll
+        for (int i = 0; i < V; ++i) {
+            if (e + i < L) row[e + i] = Elem<T>::from_f(f[i]);
+        }
+    }
+}
+
+// The registers of the previous lane's vector that hold its trailing width-1 elements; lane 0
+// receives lane 31's `old` instead (the vector that precedes lane 0's in memory).
+template <int V, int W>
+__device__ __forceinline__ uint4 prev_vector_tail(const uint4 &own, const uint4 &old, int lane) {
+    const int src_lane = (lane + 31) & 31;
+    uint4 prev = make_uint4(0, 0, 0, 0);
+    if (V == 4) {
+        if (W >= 4) prev.y = __shfl_sync(kFullMask, lane == 31 ? old.y : own.y, src_lane);
+        if (W >= 3) prev.z = __shfl_sync(kFullMask, lane == 31 ? old.z : own.z, src_lane);
+    } else {
+        if (W >= 4) prev.z = __shfl_sync(kFullMask, lane == 31 ? old.z : own.z, src_lane);
+    }
+    prev.w = __shfl_sync(kFullMask, lane == 31 ? old.w : own.w, src_lane);
+    return prev;
 }
 
 // ---- weights: dtype chosen at run time (they are a few KB, never on the critical stream) --

@@ -34,11 +34,13 @@ struct FwdCfArgs {
     uint32_t n_units;  // rows * upr
 };
 
-template <typename T, int W, bool kSilu, int kVecs>
+// kFull: seqlen is a multiple of the vector width and every unit has all 32 * kVecs vectors,
+// so no bounds check survives in the loop.
+template <typename T, int W, bool kSilu, bool kFull, int kVecs>
 __global__ void __launch_bounds__(256) fwd_cf_vec_kernel(const FwdCfArgs a) {
     constexpr int V = Elem<T>::kVec;
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
     const int lane = threadIdx.x & 31;
-    const int src_lane = (lane + 31) & 31;
     const uint32_t warps_per_cta = blockDim.x >> 5;
     const uint32_t nwarps = gridDim.x * warps_per_cta;
     const uint32_t L = a.seqlen;
@@ -50,42 +52,28 @@ __global__ void __launch_bounds__(256) fwd_cf_vec_kernel(const FwdCfArgs a) {
         const uint32_t c = row - b * a.dim;
         const T *__restrict__ xr = reinterpret_cast<const T *>(a.x) + b * a.x_bs + c * a.x_cs;
         T *__restrict__ outr = reinterpret_cast<T *>(a.out) + b * a.o_bs + c * a.o_cs;
-        const uint32_t v0 = seg * (32 * kVecs);
+        const uint32_t e0 = (seg * (32 * kVecs) + lane) * V;   // this lane's first element
 
         // issue every load of the unit before any use
         uint4 raw[kVecs];
         #pragma unroll
-        for (int j = 0; j < kVecs; ++j) {
-            const uint32_t v = v0 + j * 32 + lane;
-            raw[j] = make_uint4(0, 0, 0, 0);
-            if ((uint64_t)(v + 1) * V <= L) raw[j] = ld_stream(xr + (uint64_t)v * V);
-        }
+        for (int j = 0; j < kVecs; ++j) raw[j] = load_row_vec<T, kFull>(xr, e0 + j * 32 * V, L);
         uint4 halo0 = make_uint4(0, 0, 0, 0);
-        if (lane == 0 && v0 > 0) halo0 = ld_cached(xr + (uint64_t)(v0 - 1) * V);
+        if (lane == 0 && seg > 0) halo0 = ld_cached(xr + e0 - V);
 
+        // tanh form of SiLU works on y/2: fold the 1/2 into the taps
+        const float pre = kTanh ? 0.5f : 1.f;
         float wv[W];
         #pragma unroll
-        for (int k = 0; k < W; ++k) wv[k] = load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype);
-        const float bv = a.bias != nullptr ? load_w(a.bias, c, a.wtype) : 0.f;
+        for (int k = 0; k < W; ++k) wv[k] = pre * load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype);
+        const float bv = a.bias != nullptr ? pre * load_w(a.bias, c, a.wtype) : 0.f;
 
         #pragma unroll
         for (int j = 0; j < kVecs; ++j) {
-            const uint32_t v = v0 + j * 32 + lane;
-            // previous vector: lane-1's raw[j]; for lane 0 it is lane 31's raw[j-1]
-            const uint4 &own = raw[j];
-            const uint4 &old = raw[j > 0 ? j - 1 : 0];
-            uint4 prev = make_uint4(0, 0, 0, 0);
-            if (V == 4) {
-                if (W >= 4) prev.y = __shfl_sync(kFullMask, lane == 31 ? old.y : own.y, src_lane);
-                if (W >= 3) prev.z = __shfl_sync(kFullMask, lane == 31 ? old.z : own.z, src_lane);
-            } else {
-                if (W >= 4) prev.z = __shfl_sync(kFullMask, lane == 31 ? old.z : own.z, src_lane);
-            }
-            prev.w = __shfl_sync(kFullMask, lane == 31 ? old.w : own.w, src_lane);
+            uint4 prev = prev_vector_tail<V, W>(raw[j], raw[j > 0 ? j - 1 : 0], lane);
             if (j == 0 && lane == 0) prev = halo0;
-
-            if (v >= a.vpr) continue;
-            const bool full = (uint64_t)(v + 1) * V <= L;
+            const uint32_t e = e0 + j * 32 * V;
+            if (!kFull && e >= L) continue;
             float xx[W - 1 + V];
             {
                 float pf[V];
@@ -93,32 +81,16 @@ __global__ void __launch_bounds__(256) fwd_cf_vec_kernel(const FwdCfArgs a) {
                 #pragma unroll
                 for (int k = 0; k < W - 1; ++k) xx[k] = pf[V - (W - 1) + k];
             }
-            if (full) {
-                unpack<T>(own, xx + (W - 1));
-            } else {
-                #pragma unroll
-                for (int i = 0; i < V; ++i) {
-                    const uint64_t t = (uint64_t)v * V + i;
-                    xx[W - 1 + i] = t < L ? Elem<T>::to_f(xr[t]) : 0.f;
-                }
-            }
+            unpack<T>(raw[j], xx + (W - 1));
             float o[V];
             #pragma unroll
             for (int i = 0; i < V; ++i) {
                 float acc = bv;
                 #pragma unroll
                 for (int k = 0; k < W; ++k) acc = fmaf(wv[k], xx[i + k], acc);
-                o[i] = kSilu ? silu_f(acc) : acc;
+                o[i] = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
             }
-            if (full) {
-                st_stream(outr + (uint64_t)v * V, pack<T>(o));
-            } else {
-                #pragma unroll
-                for (int i = 0; i < V; ++i) {
-                    const uint64_t t = (uint64_t)v * V + i;
-                    if (t < L) outr[t] = Elem<T>::from_f(o[i]);
-                }
-            }
+            store_row_vec<T, kFull>(outr, e, L, o);
         }
     }
 }
@@ -149,7 +121,7 @@ int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
     const int V = vec_elems(p.itype);
     const uint64_t rows = (uint64_t)p.batch * (uint64_t)p.dim;
     if (rows == 0 || p.seqlen == 0) return CC1D_OK;
-    if (p.seqlen >= (1ll << 31) || p.dim >= (1ll << 31)) return CC1D_ERR_TOO_LARGE;
+    if (p.seqlen >= (1ll << 31) - 4096 || p.dim >= (1ll << 31)) return CC1D_ERR_TOO_LARGE;
 
     FwdCfArgs a;
     a.x = p.x; a.out = p.out; a.weight = p.weight; a.bias = p.bias;
@@ -170,9 +142,11 @@ int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
         a.vpr = (uint32_t)vpr; a.upr = (uint32_t)upr; a.n_units = (uint32_t)n_units;
         const uint64_t ctas = (n_units + 7) / 8;
         const unsigned grid = (unsigned)(ctas < (uint64_t)sms * 8 ? ctas : (uint64_t)sms * 8);
-        CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
-            fwd_cf_vec_kernel<T, W, kSilu, kVecs><<<grid, 256, 0, stream>>>(a);
-        });););
+        const bool full = p.seqlen % V == 0 && vpr % (32 * kVecs) == 0;
+        CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
+            CC1D_DISPATCH_BOOL(full, kFull, {
+                fwd_cf_vec_kernel<T, W, kSilu, kFull, kVecs><<<grid, 256, 0, stream>>>(a);
+            }););););
     } else {
         const uint64_t tpr = ((uint64_t)p.seqlen + 255) / 256;
         const uint64_t n_tiles = rows * tpr;

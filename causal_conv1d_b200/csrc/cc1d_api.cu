@@ -2,6 +2,10 @@
 // reference does with TORCH_CHECK in csrc/causal_conv1d.cpp) and hand-off to the launchers.
 #include <cuda_runtime.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "cc1d.h"
 #include "cc1d_kernels.h"
 
@@ -17,6 +21,22 @@ int num_sms() {
         cached[dev] = n;
     }
     return cached[dev];
+}
+
+int resident_ctas_per_sm(const void *kernel, int threads, size_t dyn_smem) {
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, int> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    const auto key = std::make_pair(kernel, threads);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, dyn_smem) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        n = 2;
+    }
+    cache[key] = n;
+    return n;
 }
 
 namespace {

@@ -360,20 +360,19 @@ int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream) {
     a.w_cs = p.weight_c_stride; a.w_ws = p.weight_width_stride;
     a.dim = (uint32_t)p.dim; a.seqlen = (uint32_t)p.seqlen; a.wtype = p.wtype;
     a.vpr = (uint32_t)pl.vpr; a.upr = (uint32_t)pl.upr; a.n_units = (uint32_t)pl.n_units;
-    const int sms = num_sms();
     if (rows > 0 && p.seqlen > 0) {
         if (pl.vec) {
             const uint64_t ctas = (pl.n_units + 7) / 8;
-            const unsigned grid = (unsigned)(ctas < (uint64_t)sms * 8 ? ctas : (uint64_t)sms * 8);
             const bool full = p.seqlen % vec_elems(p.itype) == 0 && pl.vpr % 128 == 0;
             CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
                 CC1D_DISPATCH_BOOL(full, kFull, {
-                    bwd_cf_vec_kernel<T, W, kSilu, kFull, 4><<<grid, 256, 0, stream>>>(a);
+                    auto kernel = bwd_cf_vec_kernel<T, W, kSilu, kFull, 4>;
+                    kernel<<<persistent_grid(kernel, 256, ctas), 256, 0, stream>>>(a);
                 }););););
         } else {
-            const unsigned grid = (unsigned)(pl.n_units < (uint64_t)sms * 16 ? pl.n_units : (uint64_t)sms * 16);
             CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
-                bwd_cf_scalar_kernel<T, W, kSilu><<<grid, 256, 0, stream>>>(a);
+                auto kernel = bwd_cf_scalar_kernel<T, W, kSilu>;
+                kernel<<<persistent_grid(kernel, 256, pl.n_units), 256, 0, stream>>>(a);
             });););
         }
         if (check_launch() != CC1D_OK) return CC1D_ERR_LAUNCH;

@@ -174,6 +174,48 @@ __device__ __forceinline__ float load_w(const void *p, int64_t idx, int wtype) {
     return __half2float(reinterpret_cast<const __half *>(p)[idx]);
 }
 
+// Taps and bias of C consecutive channels straight into registers: wv[k][c], bv[c].  When the
+// weight matrix is dense row-major (taps of a channel adjacent, channels adjacent) and 16-byte
+// aligned, C * W taps are fetched with 16-byte loads; any other stride pattern goes element
+// by element.  `scale` is folded into both (0.5 for the tanh form of SiLU).
+template <int W, int C>
+__device__ __forceinline__ void load_taps(float (&wv)[W][C], float (&bv)[C], const void *weight, int64_t w_cs,
+                                          int64_t w_ws, const void *bias, int wtype, int64_t c0, float scale) {
+    const bool dense = w_ws == 1 && w_cs == W;
+    if (dense && wtype != CC1D_F32 && (reinterpret_cast<uintptr_t>(weight) & 15) == 0 && (C * W) % 8 == 0) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(weight) + c0 * W);
+        float f[C * W];
+        #pragma unroll
+        for (int i = 0; i < C * W / 8; ++i) {
+            const uint4 v = __ldg(p + i);
+            if (wtype == CC1D_BF16) unpack<__nv_bfloat16>(v, f + 8 * i); else unpack<__half>(v, f + 8 * i);
+        }
+        #pragma unroll
+        for (int c = 0; c < C; ++c) {
+            #pragma unroll
+            for (int k = 0; k < W; ++k) wv[k][c] = scale * f[c * W + k];
+        }
+    } else if (dense && wtype == CC1D_F32 && (reinterpret_cast<uintptr_t>(weight) & 15) == 0 && (C * W) % 4 == 0) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(weight) + c0 * W);
+        float f[C * W];
+        #pragma unroll
+        for (int i = 0; i < C * W / 4; ++i) unpack<float>(__ldg(p + i), f + 4 * i);
+        #pragma unroll
+        for (int c = 0; c < C; ++c) {
+            #pragma unroll
+            for (int k = 0; k < W; ++k) wv[k][c] = scale * f[c * W + k];
+        }
+    } else {
+        #pragma unroll
+        for (int c = 0; c < C; ++c) {
+            #pragma unroll
+            for (int k = 0; k < W; ++k) wv[k][c] = scale * load_w(weight, (c0 + c) * w_cs + k * w_ws, wtype);
+        }
+    }
+    #pragma unroll
+    for (int c = 0; c < C; ++c) bv[c] = bias != nullptr ? scale * load_w(bias, c0 + c, wtype) : 0.f;
+}
+
 // Stage weight taps and bias of `nch` consecutive channels starting at c0 into shared memory
 // as fp32: s_w[k * nch + c] for tap k < W, s_w[W * nch + c] = bias (0 without bias, 0 past dim).
 template <int W>

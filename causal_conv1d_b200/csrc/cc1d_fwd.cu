@@ -132,7 +132,6 @@ int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
 
     const bool vec_ok = is_aligned16(p.x) && is_aligned16(p.out) && a.x_bs % V == 0 && a.x_cs % V == 0 &&
                         a.o_bs % V == 0 && a.o_cs % V == 0;
-    const int sms = num_sms();
     if (vec_ok) {
         constexpr int kVecs = 4;
         const uint64_t vpr = ((uint64_t)p.seqlen + V - 1) / V;
@@ -141,20 +140,20 @@ int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
         if (n_units >= (1ull << 32)) return CC1D_ERR_TOO_LARGE;
         a.vpr = (uint32_t)vpr; a.upr = (uint32_t)upr; a.n_units = (uint32_t)n_units;
         const uint64_t ctas = (n_units + 7) / 8;
-        const unsigned grid = (unsigned)(ctas < (uint64_t)sms * 8 ? ctas : (uint64_t)sms * 8);
         const bool full = p.seqlen % V == 0 && vpr % (32 * kVecs) == 0;
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
             CC1D_DISPATCH_BOOL(full, kFull, {
-                fwd_cf_vec_kernel<T, W, kSilu, kFull, kVecs><<<grid, 256, 0, stream>>>(a);
+                auto kernel = fwd_cf_vec_kernel<T, W, kSilu, kFull, kVecs>;
+                kernel<<<persistent_grid(kernel, 256, ctas), 256, 0, stream>>>(a);
             }););););
     } else {
         const uint64_t tpr = ((uint64_t)p.seqlen + 255) / 256;
         const uint64_t n_tiles = rows * tpr;
         if (n_tiles >= (1ull << 32)) return CC1D_ERR_TOO_LARGE;
         a.vpr = (uint32_t)tpr; a.upr = 0; a.n_units = (uint32_t)n_tiles;
-        const unsigned grid = (unsigned)(n_tiles < (uint64_t)sms * 32 ? n_tiles : (uint64_t)sms * 32);
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
-            fwd_cf_scalar_kernel<T, W, kSilu><<<grid, 256, 0, stream>>>(a);
+            auto kernel = fwd_cf_scalar_kernel<T, W, kSilu>;
+            kernel<<<persistent_grid(kernel, 256, n_tiles), 256, 0, stream>>>(a);
         });););
     }
     return check_launch();

@@ -26,6 +26,17 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream);
 int launch_update(const cc1d_update_params &p, cudaStream_t stream);
 int launch_varlen_states(const cc1d_varlen_states_params &p, cudaStream_t stream);
 
+// Resident CTAs per SM of a kernel (occupancy query, cached per kernel and block size):
+// persistent grid-stride kernels launch exactly sms * this many CTAs, so that no partial
+// second wave forms.
+int resident_ctas_per_sm(const void *kernel, int threads, size_t dyn_smem);
+
+template <typename K>
+inline unsigned persistent_grid(K kernel, int threads, uint64_t ctas_wanted) {
+    const uint64_t cap = (uint64_t)num_sms() * (uint64_t)resident_ctas_per_sm(reinterpret_cast<const void *>(kernel), threads, 0);
+    return (unsigned)(ctas_wanted < cap ? ctas_wanted : cap);
+}
+
 inline int check_launch() { return cudaGetLastError() == cudaSuccess ? CC1D_OK : CC1D_ERR_LAUNCH; }
 
 }  // namespace cc1d

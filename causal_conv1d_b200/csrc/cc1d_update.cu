@@ -3,8 +3,8 @@
 //
 // Vector path (x, out and conv_state all have channel stride 1): a thread owns one 16-byte
 // vector of channels of one batch entry; a warp touches 512 contiguous bytes per state row /
-// token.  The width-1 window is read once, the state shift is done in registers when
-// state_len == width-1 and as row copies otherwise.
+// token.  The width-1 window is read once; with state_len == width-1 the new state is the
+// window left in registers after the last token, otherwise rows are shifted by row copies.
 //
 // Generic path: any strides, one (batch, channel) pair per thread, scalar accesses.
 #include "cc1d_common.cuh"
@@ -27,124 +27,101 @@ struct UpdArgs {
     uint32_t ncols, ncolblk;
 };
 
-constexpr int kUpdRows = 4;     // batch entries per CTA (threadIdx.y)
-constexpr int kUpdUnroll = 4;   // tokens loaded together
-
+// One thread: one 16-byte vector of channels of one batch entry.  The kernel is kept small
+// and straight (a decode step is latency-bound: instruction fetch, one index -> state-row
+// dependent load chain, no barrier): every load that does not depend on the state row index
+// (taps, first token, cache_seqlens) is issued before the index arrives; later tokens are
+// prefetched one ahead in a rolled loop.
 template <typename T, int W, bool kSilu, bool kCirc>
-__global__ void __launch_bounds__(32 * kUpdRows) update_vec_kernel(const UpdArgs a) {
+__global__ void __launch_bounds__(128, 4) update_vec_kernel(const UpdArgs a) {
     constexpr int C = Elem<T>::kVec;
-    __shared__ __align__(16) float s_w[(W + 1) * 32 * C];
-
-    const uint32_t cb = blockIdx.x % a.ncolblk;
-    const uint32_t bg = blockIdx.x / a.ncolblk;
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int32_t b = (int32_t)bg * kUpdRows + ty;
-
-    // the state row index is the head of the dependent-load chain: fetch it first
-    int32_t coord = -1, cs = 0;
-    if (b < a.batch) {
-        coord = a.indices != nullptr ? a.indices[b] : b;
-        if (kCirc) cs = a.cache_seqlens[b];
-    }
-    stage_weights<W>(s_w, 32 * C, (int64_t)cb * 32 * C, a.dim, a.weight, a.w_cs, a.w_ws, a.bias,
-                     a.wtype, threadIdx.x, 32 * kUpdRows);
-    __syncthreads();
-
-    const uint32_t col = cb * 32 + tx;
-    if (col >= a.ncols || b >= a.batch) return;
-    const T *__restrict__ xp = reinterpret_cast<const T *>(a.x) + b * a.x_bs + (int64_t)col * C;
-    T *__restrict__ op = reinterpret_cast<T *>(a.out) + b * a.o_bs + (int64_t)col * C;
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    // flat thread index over (batch entry, channel vector), channel vectors fastest
+    const uint64_t gid = (uint64_t)blockIdx.x * 128 + threadIdx.x;
+    const int32_t b = (int32_t)(gid / a.ncols);
+    const uint32_t col = (uint32_t)(gid - (uint64_t)b * a.ncols);
+    if (b >= a.batch) return;
     const int L = a.seqlen, S = a.state_len;
 
-    if (coord < 0) {  // padded entry: zero output, state untouched
+    const int32_t coord = a.indices != nullptr ? __ldg(a.indices + b) : b;
+    const int32_t cs = kCirc ? __ldg(a.cache_seqlens + b) : 0;
+    const T *__restrict__ xp = reinterpret_cast<const T *>(a.x) + (int64_t)b * a.x_bs + (int64_t)col * C;
+    T *__restrict__ op = reinterpret_cast<T *>(a.out) + (int64_t)b * a.o_bs + (int64_t)col * C;
+    uint4 raw = ld_stream(xp);   // token 0
+    if (coord < 0) {             // padded entry: zero output, state untouched
         for (int i = 0; i < L; ++i) st_stream(op + i * a.o_ls, make_uint4(0, 0, 0, 0));
         return;
     }
     T *sp = reinterpret_cast<T *>(a.state) + coord * a.s_bs + (int64_t)col * C;
 
-    // window rows (the width-1 entries that precede x)
-    int widx[W - 1];
-    int wr = 0;  // circular: first row x is written to
+    // window rows: the width-1 entries that precede x
+    int wr = 0;   // circular: next row to write
+    uint4 winraw[W - 1];
     if (kCirc) {
-        wr = cs % S;  // cache_seqlens >= 0 by contract; a negative value is folded below
+        wr = cs % S;
         if (wr < 0) wr += S;
         int r = wr - (W - 1);
         if (r < 0) r += S;   // state_len >= width-1
         #pragma unroll
-        for (int k = 0; k < W - 1; ++k) { widx[k] = r; r = r + 1 >= S ? r + 1 - S : r + 1; }
+        for (int k = 0; k < W - 1; ++k) { winraw[k] = ld_cached(sp + r * a.s_ls); r = r + 1 >= S ? r + 1 - S : r + 1; }
     } else {
         #pragma unroll
-        for (int k = 0; k < W - 1; ++k) widx[k] = S - (W - 1) + k;
+        for (int k = 0; k < W - 1; ++k) winraw[k] = ld_cached(sp + (S - (W - 1) + k) * a.s_ls);
     }
-    uint4 wraw[W - 1];
-    #pragma unroll
-    for (int k = 0; k < W - 1; ++k) wraw[k] = ld_cached(sp + widx[k] * a.s_ls);
-
     float wv[W][C], bv[C];
-    #pragma unroll
-    for (int k = 0; k < W; ++k) {
-        #pragma unroll
-        for (int c = 0; c < C; ++c) wv[k][c] = s_w[k * 32 * C + tx * C + c];
-    }
-    #pragma unroll
-    for (int c = 0; c < C; ++c) bv[c] = s_w[W * 32 * C + tx * C + c];
+    load_taps<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, kTanh ? 0.5f : 1.f);
 
-    // linear mode with spare rows: shift the surviving rows down by L (ascending, in place)
-    const bool in_regs = !kCirc && S == W - 1;  // new state == final window
+    // linear mode with spare rows: shift the surviving rows down by L (ascending, in place;
+    // the window rows are already in registers).  With state_len == width-1 the new state is
+    // simply the window left after the last token.
+    const bool in_regs = !kCirc && S == W - 1;
     if (!kCirc && !in_regs) {
-        #pragma unroll 4
+        #pragma unroll 2
         for (int i = 0; i < S - L; ++i) {
             const uint4 v = ld_cached(sp + (i + L) * a.s_ls);
             *reinterpret_cast<uint4 *>(sp + i * a.s_ls) = v;
         }
     }
-
     float win[W - 1][C];
     #pragma unroll
-    for (int k = 0; k < W - 1; ++k) unpack<T>(wraw[k], win[k]);
+    for (int k = 0; k < W - 1; ++k) unpack<T>(winraw[k], win[k]);
 
-    for (int t = 0; t < L; t += kUpdUnroll) {
-        uint4 raw[kUpdUnroll];
+    #pragma unroll 1
+    for (int i = 0; i < L; ++i) {
+        uint4 next = make_uint4(0, 0, 0, 0);
+        if (i + 1 < L) next = ld_stream(xp + (i + 1) * a.x_ls);
+        if (kCirc) {
+            *reinterpret_cast<uint4 *>(sp + wr * a.s_ls) = raw;
+            wr = wr + 1 >= S ? 0 : wr + 1;
+        } else if (!in_regs) {
+            const int r = S - L + i;
+            if (r >= 0) *reinterpret_cast<uint4 *>(sp + r * a.s_ls) = raw;
+        }
+        float cur[C], o[C];
+        unpack<T>(raw, cur);
         #pragma unroll
-        for (int u = 0; u < kUpdUnroll; ++u) {
-            raw[u] = make_uint4(0, 0, 0, 0);
-            if (t + u < L) raw[u] = ld_stream(xp + (t + u) * a.x_ls);
+        for (int c = 0; c < C; ++c) {
+            float acc = bv[c];
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) acc = fmaf(wv[k][c], win[k][c], acc);
+            acc = fmaf(wv[W - 1][c], cur[c], acc);
+            o[c] = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
+        }
+        st_stream(op + i * a.o_ls, pack<T>(o));
+        #pragma unroll
+        for (int k = 0; k < W - 2; ++k) {
+            #pragma unroll
+            for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
+            winraw[k] = winraw[k + 1];
         }
         #pragma unroll
-        for (int u = 0; u < kUpdUnroll; ++u) {
-            if (t + u < L) {
-                const int i = t + u;
-                if (kCirc) {
-                    *reinterpret_cast<uint4 *>(sp + wr * a.s_ls) = raw[u];
-                    wr = wr + 1 >= S ? 0 : wr + 1;
-                } else if (!in_regs) {
-                    const int r = S - L + i;
-                    if (r >= 0) *reinterpret_cast<uint4 *>(sp + r * a.s_ls) = raw[u];
-                }
-                float cur[C], o[C];
-                unpack<T>(raw[u], cur);
-                #pragma unroll
-                for (int c = 0; c < C; ++c) {
-                    float acc = bv[c];
-                    #pragma unroll
-                    for (int k = 0; k < W - 1; ++k) acc = fmaf(wv[k][c], win[k][c], acc);
-                    acc = fmaf(wv[W - 1][c], cur[c], acc);
-                    o[c] = kSilu ? silu_f(acc) : acc;
-                }
-                st_stream(op + i * a.o_ls, pack<T>(o));
-                #pragma unroll
-                for (int k = 0; k < W - 2; ++k) {
-                    #pragma unroll
-                    for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
-                }
-                #pragma unroll
-                for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
-            }
-        }
+        for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
+        winraw[W - 2] = raw;   // bit-exact copy for the state write-back
+        raw = next;
     }
     if (in_regs) {
         #pragma unroll
-        for (int k = 0; k < W - 1; ++k) *reinterpret_cast<uint4 *>(sp + k * a.s_ls) = pack<T>(win[k]);
+        for (int k = 0; k < W - 1; ++k) *reinterpret_cast<uint4 *>(sp + k * a.s_ls) = winraw[k];
     }
 }
 
@@ -228,12 +205,12 @@ int launch_update(const cc1d_update_params &p, cudaStream_t stream) {
     const bool circ = p.cache_seqlens != nullptr;
     if (vec_ok) {
         a.ncols = (uint32_t)(p.dim / C);
-        a.ncolblk = (a.ncols + 31) / 32;
-        const uint64_t ctas = (uint64_t)a.ncolblk * (uint64_t)((p.batch + kUpdRows - 1) / kUpdRows);
+        a.ncolblk = 0;
+        const uint64_t ctas = ((uint64_t)a.ncols * (uint64_t)p.batch + 127) / 128;
         if (ctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
             CC1D_DISPATCH_BOOL(circ, kCirc, {
-                update_vec_kernel<T, W, kSilu, kCirc><<<(unsigned)ctas, 32 * kUpdRows, 0, stream>>>(a);
+                update_vec_kernel<T, W, kSilu, kCirc><<<(unsigned)ctas, 128, 0, stream>>>(a);
             }););););
     } else {
         a.ncols = 0;

@@ -20,7 +20,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
-OBJ = os.path.join(ROOT, "build", "cc1d")
+OBJ = os.environ.get("CC1D_BUILD_DIR", os.path.join(ROOT, "build", "cc1d"))
 
 LIB_CC1D = os.path.join(PKG, "libcc1d.so")
 LIB_TORCH = os.path.join(PKG, "_cc1d_torch.so")
@@ -36,6 +36,10 @@ NVCC_FLAGS = [
     "--use_fast_math",   # flush-to-zero special-function paths; state copies never go through arithmetic
     "-Xptxas", "-v",
 ]
+
+
+# extra nvcc flags (e.g. -DCC1D_CF_KVECS=8) for tuning experiments
+NVCC_FLAGS += os.environ.get("CC1D_EXTRA_NVCC_FLAGS", "").split()
 
 
 def _nvcc() -> str:

@@ -82,7 +82,7 @@ struct BwdCfArgs {
     int64_t x_bs, x_cs, d_bs, d_cs, o_bs, o_cs, w_cs, w_ws;
     uint32_t dim, seqlen;
     int wtype;
-    uint32_t vpr, upr, n_units;
+    uint32_t vpr, gpr, gpu, upr, n_units;   // see FwdCfArgs
 };
 
 // g = dout * silu'(y) for one element; `y_or_h` is the pre-activation computed with the taps
@@ -93,11 +93,17 @@ __device__ __forceinline__ float grad_through_act(float dout, float y_or_h) {
     return dout * (kTanh ? dsilu_half_arg(y_or_h) : dsilu_f(y_or_h));
 }
 
-// kFull: seqlen is a multiple of the vector width and every unit has all 32 * kVecs vectors.
+// A warp unit is `gpu` consecutive groups of 32 * kVecs vectors of one row, walked BACK to
+// front: dx of a group needs g of the first width-1 elements of the group after it, which
+// the previous iteration left in lane 0's registers; only the unit's last group has to
+// recompute them from one extra x/dout vector.  dweight/dbias accumulate over the whole
+// unit: one partial row per unit.
+// kFull: seqlen is a multiple of the vector width and every group has all 32 * kVecs vectors.
 template <typename T, int W, bool kSilu, bool kFull, int kVecs>
 __global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
     constexpr int V = Elem<T>::kVec;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    constexpr uint32_t kGroupElems = 32 * kVecs * V;
     const int lane = threadIdx.x & 31;
     const uint32_t warps_per_cta = blockDim.x >> 5;
     const uint32_t nwarps = gridDim.x * warps_per_cta;
@@ -111,23 +117,8 @@ __global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
         const T *__restrict__ xr = reinterpret_cast<const T *>(a.x) + b * a.x_bs + c * a.x_cs;
         const T *__restrict__ dr = reinterpret_cast<const T *>(a.dout) + b * a.d_bs + c * a.d_cs;
         T *__restrict__ dxr = reinterpret_cast<T *>(a.dx) + b * a.o_bs + c * a.o_cs;
-        const uint32_t e0 = (seg * (32 * kVecs) + lane) * V;
-
-        uint4 xraw[kVecs], draw[kVecs];
-        #pragma unroll
-        for (int j = 0; j < kVecs; ++j) {
-            xraw[j] = load_row_vec<T, kFull>(xr, e0 + j * 32 * V, L);
-            draw[j] = load_row_vec<T, kFull>(dr, e0 + j * 32 * V, L);
-        }
-        // left halo of the unit (x only) and the first vector of the next unit (x and dout),
-        // needed by lane 0 and lane 31 respectively
-        uint4 halo0 = make_uint4(0, 0, 0, 0), xedge = make_uint4(0, 0, 0, 0), dedge = make_uint4(0, 0, 0, 0);
-        if (lane == 0 && seg > 0) halo0 = ld_cached(xr + e0 - V);
-        if (lane == 31 && seg + 1 < a.upr) {
-            const uint32_t en = e0 + kVecs * 32 * V - 31 * V;   // first element of the next unit
-            if (kSilu) xedge = load_row_vec<T, false>(xr, en, L);
-            dedge = load_row_vec<T, false>(dr, en, L);
-        }
+        const uint32_t g0 = seg * a.gpu;
+        const uint32_t g1 = g0 + a.gpu < a.gpr ? g0 + a.gpu : a.gpr;
 
         float wv[W], wy[W];   // taps, and taps scaled for the pre-activation recompute
         const float pre = kTanh ? 0.5f : 1.f;
@@ -138,83 +129,106 @@ __global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
         }
         const float by = a.bias != nullptr ? pre * load_w(a.bias, c, a.wtype) : 0.f;
 
-        float g[kVecs][V];
         float dw[W], db = 0.f;
         #pragma unroll
         for (int k = 0; k < W; ++k) dw[k] = 0.f;
-
-        // pass 1: g, dweight, dbias (elements past the row end have dout == 0, so g == 0)
+        float ge[W - 1];   // g of the first width-1 elements after the current group
         #pragma unroll
-        for (int j = 0; j < kVecs; ++j) {
-            uint4 prev = prev_vector_tail<V, W>(xraw[j], xraw[j > 0 ? j - 1 : 0], lane);
-            if (j == 0 && lane == 0) prev = halo0;
-            float xx[W - 1 + V];
-            {
-                float pf[V];
-                unpack<T>(prev, pf);
-                #pragma unroll
-                for (int k = 0; k < W - 1; ++k) xx[k] = pf[V - (W - 1) + k];
-            }
-            unpack<T>(xraw[j], xx + (W - 1));
-            unpack<T>(draw[j], g[j]);
+        for (int k = 0; k < W - 1; ++k) ge[k] = 0.f;
+
+        for (uint32_t g = g1; g-- > g0;) {
+            const uint32_t e0 = (g * (32 * kVecs) + lane) * V;
+            uint4 xraw[kVecs], draw[kVecs];
             #pragma unroll
-            for (int i = 0; i < V; ++i) {
-                if (kSilu) {
+            for (int j = 0; j < kVecs; ++j) {
+                xraw[j] = load_row_vec<T, kFull>(xr, e0 + j * 32 * V, L);
+                draw[j] = load_row_vec<T, kFull>(dr, e0 + j * 32 * V, L);
+            }
+            // x vector before lane 0's first one (held by lane 31 for the shuffle), and for the
+            // unit's last group the first vector after it (x and dout) to seed `ge`
+            uint4 carry = make_uint4(0, 0, 0, 0), xedge = make_uint4(0, 0, 0, 0), dedge = make_uint4(0, 0, 0, 0);
+            if (lane == 31 && g > 0) carry = ld_cached(xr + (e0 - 32 * V));
+            const bool seed = g == g1 - 1 && g1 < a.gpr;
+            if (seed) {
+                const uint32_t en = g1 * kGroupElems;   // first element after the unit
+                if (kSilu) xedge = load_row_vec<T, false>(xr, en, L);
+                dedge = load_row_vec<T, false>(dr, en, L);
+            }
+
+            // pass 1: g, dweight, dbias (elements past the row end have dout == 0, so g == 0)
+            float gg[kVecs][V];
+            #pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                const uint4 prev = prev_vector_tail<V, W>(xraw[j], j > 0 ? xraw[j - 1] : carry, lane);
+                float xx[W - 1 + V];
+                {
+                    float pf[V];
+                    unpack<T>(prev, pf);
+                    #pragma unroll
+                    for (int k = 0; k < W - 1; ++k) xx[k] = pf[V - (W - 1) + k];
+                }
+                unpack<T>(xraw[j], xx + (W - 1));
+                unpack<T>(draw[j], gg[j]);
+                #pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    if (kSilu) {
+                        float y = by;
+                        #pragma unroll
+                        for (int k = 0; k < W; ++k) y = fmaf(wy[k], xx[i + k], y);
+                        gg[j][i] = grad_through_act<kSilu, kTanh>(gg[j][i], y);
+                    }
+                    db += gg[j][i];
+                    #pragma unroll
+                    for (int k = 0; k < W; ++k) dw[k] = fmaf(xx[i + k], gg[j][i], dw[k]);
+                }
+            }
+            if (seed) {   // warp-uniform
+                float xt[V], xn[V], dn[V];
+                unpack<T>(xraw[kVecs - 1], xt);   // lane 31: the unit's last vector
+                unpack<T>(xedge, xn);
+                unpack<T>(dedge, dn);
+                float xx[2 * (W - 1)];
+                #pragma unroll
+                for (int k = 0; k < W - 1; ++k) { xx[k] = xt[V - (W - 1) + k]; xx[W - 1 + k] = xn[k]; }
+                #pragma unroll
+                for (int i = 0; i < W - 1; ++i) {
                     float y = by;
                     #pragma unroll
                     for (int k = 0; k < W; ++k) y = fmaf(wy[k], xx[i + k], y);
-                    g[j][i] = grad_through_act<kSilu, kTanh>(g[j][i], y);
+                    ge[i] = grad_through_act<kSilu, kTanh>(dn[i], y);   // valid in lane 31, the only reader
                 }
-                db += g[j][i];
-                #pragma unroll
-                for (int k = 0; k < W; ++k) dw[k] = fmaf(xx[i + k], g[j][i], dw[k]);
             }
-        }
-        // g of the first width-1 elements of the next unit (only lane 31's copy is used)
-        float ge[W - 1];
-        {
-            float xt[V], xn[V], dn[V];
-            unpack<T>(xraw[kVecs - 1], xt);
-            unpack<T>(xedge, xn);
-            unpack<T>(dedge, dn);
-            float xx[2 * (W - 1)];
-            #pragma unroll
-            for (int k = 0; k < W - 1; ++k) { xx[k] = xt[V - (W - 1) + k]; xx[W - 1 + k] = xn[k]; }
-            #pragma unroll
-            for (int i = 0; i < W - 1; ++i) {
-                float y = by;
-                #pragma unroll
-                for (int k = 0; k < W; ++k) y = fmaf(wy[k], xx[i + k], y);
-                ge[i] = grad_through_act<kSilu, kTanh>(dn[i], y);
-            }
-        }
 
-        // pass 2: dx[t] = sum_k w[k] * g[t + (W-1-k)]
-        const int dst_lane = (lane + 1) & 31;
-        #pragma unroll
-        for (int j = 0; j < kVecs; ++j) {
-            float gg[V + W - 1];
+            // pass 2: dx[t] = sum_k w[k] * g[t + (W-1-k)]
+            const int dst_lane = (lane + 1) & 31;
             #pragma unroll
-            for (int i = 0; i < V; ++i) gg[i] = g[j][i];
-            #pragma unroll
-            for (int k = 0; k < W - 1; ++k) {
-                // lane l takes lane l+1's g[j][k]; lane 31 takes lane 0's g[j+1][k]
-                const float send = (lane == 0 && j + 1 < kVecs) ? g[j + 1 < kVecs ? j + 1 : j][k] : g[j][k];
-                float r = __shfl_sync(kFullMask, send, dst_lane);
-                if (j == kVecs - 1 && lane == 31) r = ge[k];
-                gg[V + k] = r;
-            }
-            const uint32_t e = e0 + j * 32 * V;
-            if (!kFull && e >= L) continue;
-            float o[V];
-            #pragma unroll
-            for (int i = 0; i < V; ++i) {
-                float acc = 0.f;
+            for (int j = 0; j < kVecs; ++j) {
+                float gx[V + W - 1];
                 #pragma unroll
-                for (int k = 0; k < W; ++k) acc = fmaf(wv[k], gg[i + (W - 1 - k)], acc);
-                o[i] = acc;
+                for (int i = 0; i < V; ++i) gx[i] = gg[j][i];
+                #pragma unroll
+                for (int k = 0; k < W - 1; ++k) {
+                    // lane l takes lane l+1's g[j][k]; lane 31 takes lane 0's g[j+1][k]
+                    const float send = (lane == 0 && j + 1 < kVecs) ? gg[j + 1 < kVecs ? j + 1 : j][k] : gg[j][k];
+                    float r = __shfl_sync(kFullMask, send, dst_lane);
+                    if (j == kVecs - 1 && lane == 31) r = ge[k];
+                    gx[V + k] = r;
+                }
+                const uint32_t e = e0 + j * 32 * V;
+                if (!kFull && e >= L) continue;
+                float o[V];
+                #pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    float acc = 0.f;
+                    #pragma unroll
+                    for (int k = 0; k < W; ++k) acc = fmaf(wv[k], gx[i + (W - 1 - k)], acc);
+                    o[i] = acc;
+                }
+                store_row_vec<T, kFull>(dxr, e, L, o);
             }
-            store_row_vec<T, kFull>(dxr, e, L, o);
+            // the next (lower) group's right halo is this group's first elements, in lane 0
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) ge[k] = __shfl_sync(kFullMask, gg[0][k], 0);
         }
 
         // warp tree (fixed order), one partial row per unit
@@ -308,11 +322,11 @@ __global__ void __launch_bounds__(256) bwd_cf_scalar_kernel(const BwdCfArgs a) {
 
 struct CfPlan {
     bool vec;
-    uint64_t vpr, upr, n_units;
+    uint64_t vpr, gpr, gpu, upr, n_units;
 };
 
 static CfPlan plan_channel_first(const cc1d_bwd_params &p) {
-    constexpr int kVecs = 4;
+    constexpr int kVecs = kCfVecs;
     const int V = vec_elems(p.itype);
     const int64_t x_bs = p.batch > 1 ? p.x_batch_stride : 0, x_cs = p.dim > 1 ? p.x_c_stride : 0;
     const int64_t d_bs = p.batch > 1 ? p.dout_batch_stride : 0, d_cs = p.dim > 1 ? p.dout_c_stride : 0;
@@ -323,9 +337,12 @@ static CfPlan plan_channel_first(const cc1d_bwd_params &p) {
     const uint64_t rows = (uint64_t)p.batch * (uint64_t)p.dim;
     if (pl.vec) {
         pl.vpr = ((uint64_t)p.seqlen + V - 1) / V;
-        pl.upr = (pl.vpr + 32 * kVecs - 1) / (32 * kVecs);
+        pl.gpr = (pl.vpr + 32 * kVecs - 1) / (32 * kVecs);
+        pl.gpu = groups_per_unit(rows, pl.gpr);
+        pl.upr = (pl.gpr + pl.gpu - 1) / pl.gpu;
     } else {
         pl.vpr = ((uint64_t)p.seqlen + 255) / 256;
+        pl.gpr = pl.gpu = 0;
         pl.upr = pl.vpr;
     }
     pl.n_units = rows * pl.upr;
@@ -338,7 +355,9 @@ size_t bwd_workspace_bytes_channel_first(const cc1d_bwd_params &p) {
     const int V = vec_elems(p.itype);
     const uint64_t rows = (uint64_t)p.batch * (uint64_t)p.dim;
     const uint64_t vpr = ((uint64_t)p.seqlen + V - 1) / V;
-    const uint64_t upr_vec = (vpr + 127) / 128;
+    const uint64_t gpr = (vpr + kCfGroupVecs - 1) / kCfGroupVecs;
+    const uint64_t gpu = groups_per_unit(rows, gpr);
+    const uint64_t upr_vec = gpu ? (gpr + gpu - 1) / gpu : 0;
     const uint64_t upr_sc = ((uint64_t)p.seqlen + 255) / 256;
     const uint64_t upr = upr_vec > upr_sc ? upr_vec : upr_sc;
     return (size_t)(rows * upr * (uint64_t)(p.width + 1) * sizeof(float));
@@ -359,15 +378,17 @@ int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream) {
     a.o_bs = p.batch > 1 ? p.dx_batch_stride : 0; a.o_cs = p.dim > 1 ? p.dx_c_stride : 0;
     a.w_cs = p.weight_c_stride; a.w_ws = p.weight_width_stride;
     a.dim = (uint32_t)p.dim; a.seqlen = (uint32_t)p.seqlen; a.wtype = p.wtype;
-    a.vpr = (uint32_t)pl.vpr; a.upr = (uint32_t)pl.upr; a.n_units = (uint32_t)pl.n_units;
+    a.vpr = (uint32_t)pl.vpr; a.gpr = (uint32_t)pl.gpr; a.gpu = (uint32_t)pl.gpu; a.upr = (uint32_t)pl.upr;
+    a.n_units = (uint32_t)pl.n_units;
     if (rows > 0 && p.seqlen > 0) {
         if (pl.vec) {
             const uint64_t ctas = (pl.n_units + 7) / 8;
-            const bool full = p.seqlen % vec_elems(p.itype) == 0 && pl.vpr % 128 == 0;
+            const bool full = p.seqlen % vec_elems(p.itype) == 0 && pl.vpr % kCfGroupVecs == 0;
             CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
                 CC1D_DISPATCH_BOOL(full, kFull, {
-                    auto kernel = bwd_cf_vec_kernel<T, W, kSilu, kFull, 4>;
-                    kernel<<<persistent_grid(kernel, 256, ctas), 256, 0, stream>>>(a);
+                    auto kernel = bwd_cf_vec_kernel<T, W, kSilu, kFull, kCfVecs>;
+                    const bool persistent = CC1D_CF_BWD_PERSISTENT == 1 || (CC1D_CF_BWD_PERSISTENT == 2 && p.itype != CC1D_F32);
+                    kernel<<<persistent_grid(kernel, 256, ctas, persistent), 256, 0, stream>>>(a);
                 }););););
         } else {
             CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {

@@ -33,10 +33,18 @@ template <> struct Elem<__nv_bfloat16> {
 
 // ---- 16-byte global access ------------------------------------------------------------
 // Read-once input streams: non-coherent path, do not keep the line in L1.
+#ifndef CC1D_STREAM_HINTS
+#define CC1D_STREAM_HINTS 1
+#endif
 __device__ __forceinline__ uint4 ld_stream(const void *p) {
+#if !CC1D_STREAM_HINTS
+    return *reinterpret_cast<const uint4 *>(p);
+#endif
+    // volatile: a plain asm is assumed free of side effects and may be hoisted above the
+    // bounds check that guards it; a load can fault, so it must stay where it is written
     uint4 v;
-    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 // Data that another thread of the same launch may also read (halos): plain cached load.
@@ -45,6 +53,10 @@ __device__ __forceinline__ uint4 ld_cached(const void *p) {
 }
 // Write-once output streams: evict-first.
 __device__ __forceinline__ void st_stream(void *p, const uint4 &v) {
+#if !CC1D_STREAM_HINTS
+    *reinterpret_cast<uint4 *>(p) = v;
+    return;
+#endif
     asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};"
                  :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }

@@ -30,16 +30,23 @@ struct FwdCfArgs {
     uint32_t dim, seqlen;
     int wtype;
     uint32_t vpr;      // 16-byte vectors per row, the last one may be partial
+    uint32_t gpr;      // groups (32 * kVecs vectors) per row
+    uint32_t gpu;      // groups per warp unit
     uint32_t upr;      // warp units per row
     uint32_t n_units;  // rows * upr
 };
 
-// kFull: seqlen is a multiple of the vector width and every unit has all 32 * kVecs vectors,
+// A warp unit is `gpu` consecutive groups of 32 * kVecs vectors of one row, walked front to
+// back: row decode and taps are paid once per unit, the halo of every group after the first
+// is the previous group's last vector (still in lane 31's registers), and the next group's
+// loads are issued before the current group is computed.
+// kFull: seqlen is a multiple of the vector width and every group has all 32 * kVecs vectors,
 // so no bounds check survives in the loop.
 template <typename T, int W, bool kSilu, bool kFull, int kVecs>
 __global__ void __launch_bounds__(256) fwd_cf_vec_kernel(const FwdCfArgs a) {
     constexpr int V = Elem<T>::kVec;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    constexpr uint32_t kGroupElems = 32 * kVecs * V;
     const int lane = threadIdx.x & 31;
     const uint32_t warps_per_cta = blockDim.x >> 5;
     const uint32_t nwarps = gridDim.x * warps_per_cta;
@@ -52,14 +59,15 @@ __global__ void __launch_bounds__(256) fwd_cf_vec_kernel(const FwdCfArgs a) {
         const uint32_t c = row - b * a.dim;
         const T *__restrict__ xr = reinterpret_cast<const T *>(a.x) + b * a.x_bs + c * a.x_cs;
         T *__restrict__ outr = reinterpret_cast<T *>(a.out) + b * a.o_bs + c * a.o_cs;
-        const uint32_t e0 = (seg * (32 * kVecs) + lane) * V;   // this lane's first element
+        const uint32_t g0 = seg * a.gpu;                                  // first group of the unit
+        const uint32_t g1 = g0 + a.gpu < a.gpr ? g0 + a.gpu : a.gpr;      // one past the last
+        uint32_t e0 = (g0 * (32 * kVecs) + lane) * V;                     // this lane's first element
 
-        // issue every load of the unit before any use
-        uint4 raw[kVecs];
+        uint4 nxt[kVecs];
         #pragma unroll
-        for (int j = 0; j < kVecs; ++j) raw[j] = load_row_vec<T, kFull>(xr, e0 + j * 32 * V, L);
-        uint4 halo0 = make_uint4(0, 0, 0, 0);
-        if (lane == 0 && seg > 0) halo0 = ld_cached(xr + e0 - V);
+        for (int j = 0; j < kVecs; ++j) nxt[j] = load_row_vec<T, kFull>(xr, e0 + j * 32 * V, L);
+        uint4 carry = make_uint4(0, 0, 0, 0);   // vector that precedes this lane's first one
+        if (lane == 31 && g0 > 0) carry = ld_cached(xr + (e0 - 32 * V));  // = vector before lane 0's
 
         // tanh form of SiLU works on y/2: fold the 1/2 into the taps
         const float pre = kTanh ? 0.5f : 1.f;
@@ -68,29 +76,38 @@ __global__ void __launch_bounds__(256) fwd_cf_vec_kernel(const FwdCfArgs a) {
         for (int k = 0; k < W; ++k) wv[k] = pre * load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype);
         const float bv = a.bias != nullptr ? pre * load_w(a.bias, c, a.wtype) : 0.f;
 
-        #pragma unroll
-        for (int j = 0; j < kVecs; ++j) {
-            uint4 prev = prev_vector_tail<V, W>(raw[j], raw[j > 0 ? j - 1 : 0], lane);
-            if (j == 0 && lane == 0) prev = halo0;
-            const uint32_t e = e0 + j * 32 * V;
-            if (!kFull && e >= L) continue;
-            float xx[W - 1 + V];
-            {
-                float pf[V];
-                unpack<T>(prev, pf);
-                #pragma unroll
-                for (int k = 0; k < W - 1; ++k) xx[k] = pf[V - (W - 1) + k];
-            }
-            unpack<T>(raw[j], xx + (W - 1));
-            float o[V];
+        for (uint32_t g = g0; g < g1; ++g, e0 += kGroupElems) {
+            uint4 raw[kVecs];
             #pragma unroll
-            for (int i = 0; i < V; ++i) {
-                float acc = bv;
+            for (int j = 0; j < kVecs; ++j) raw[j] = nxt[j];
+            if (g + 1 < g1) {
                 #pragma unroll
-                for (int k = 0; k < W; ++k) acc = fmaf(wv[k], xx[i + k], acc);
-                o[i] = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
+                for (int j = 0; j < kVecs; ++j) nxt[j] = load_row_vec<T, kFull>(xr, e0 + kGroupElems + j * 32 * V, L);
             }
-            store_row_vec<T, kFull>(outr, e, L, o);
+            #pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                const uint4 prev = prev_vector_tail<V, W>(raw[j], j > 0 ? raw[j - 1] : carry, lane);
+                const uint32_t e = e0 + j * 32 * V;
+                if (!kFull && e >= L) continue;
+                float xx[W - 1 + V];
+                {
+                    float pf[V];
+                    unpack<T>(prev, pf);
+                    #pragma unroll
+                    for (int k = 0; k < W - 1; ++k) xx[k] = pf[V - (W - 1) + k];
+                }
+                unpack<T>(raw[j], xx + (W - 1));
+                float o[V];
+                #pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    float acc = bv;
+                    #pragma unroll
+                    for (int k = 0; k < W; ++k) acc = fmaf(wv[k], xx[i + k], acc);
+                    o[i] = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
+                }
+                store_row_vec<T, kFull>(outr, e, L, o);
+            }
+            carry = raw[kVecs - 1];
         }
     }
 }
@@ -117,6 +134,15 @@ __global__ void __launch_bounds__(256) fwd_cf_scalar_kernel(const FwdCfArgs a) {
     }
 }
 
+// Groups of one row handled by one warp: as many as possible (per-unit costs amortise, fewer
+// partial rows in the backward) while leaving enough units to balance ~148 SMs x 48 warps.
+uint64_t groups_per_unit(uint64_t rows, uint64_t groups_per_row) {
+    const uint64_t units_wanted = 148ull * 48 * 4;
+    uint64_t gpu = groups_per_row;
+    while (gpu > 1 && rows * ((groups_per_row + gpu - 1) / gpu) < units_wanted) gpu = (gpu + 1) / 2;
+    return gpu > 0 ? gpu : 1;
+}
+
 int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
     const int V = vec_elems(p.itype);
     const uint64_t rows = (uint64_t)p.batch * (uint64_t)p.dim;
@@ -133,24 +159,28 @@ int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
     const bool vec_ok = is_aligned16(p.x) && is_aligned16(p.out) && a.x_bs % V == 0 && a.x_cs % V == 0 &&
                         a.o_bs % V == 0 && a.o_cs % V == 0;
     if (vec_ok) {
-        constexpr int kVecs = 4;
+        constexpr int kVecs = kCfVecs;
         const uint64_t vpr = ((uint64_t)p.seqlen + V - 1) / V;
-        const uint64_t upr = (vpr + 32 * kVecs - 1) / (32 * kVecs);
+        const uint64_t gpr = (vpr + 32 * kVecs - 1) / (32 * kVecs);
+        const uint64_t gpu = groups_per_unit(rows, gpr);
+        const uint64_t upr = (gpr + gpu - 1) / gpu;
         const uint64_t n_units = rows * upr;
         if (n_units >= (1ull << 32)) return CC1D_ERR_TOO_LARGE;
-        a.vpr = (uint32_t)vpr; a.upr = (uint32_t)upr; a.n_units = (uint32_t)n_units;
+        a.vpr = (uint32_t)vpr; a.gpr = (uint32_t)gpr; a.gpu = (uint32_t)gpu; a.upr = (uint32_t)upr;
+        a.n_units = (uint32_t)n_units;
         const uint64_t ctas = (n_units + 7) / 8;
         const bool full = p.seqlen % V == 0 && vpr % (32 * kVecs) == 0;
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
             CC1D_DISPATCH_BOOL(full, kFull, {
                 auto kernel = fwd_cf_vec_kernel<T, W, kSilu, kFull, kVecs>;
-                kernel<<<persistent_grid(kernel, 256, ctas), 256, 0, stream>>>(a);
+                // memory-bound: fresh CTAs keep more loads in flight than a grid-stride loop does
+                kernel<<<persistent_grid(kernel, 256, ctas, CC1D_CF_FWD_PERSISTENT != 0), 256, 0, stream>>>(a);
             }););););
     } else {
         const uint64_t tpr = ((uint64_t)p.seqlen + 255) / 256;
         const uint64_t n_tiles = rows * tpr;
         if (n_tiles >= (1ull << 32)) return CC1D_ERR_TOO_LARGE;
-        a.vpr = (uint32_t)tpr; a.upr = 0; a.n_units = (uint32_t)n_tiles;
+        a.vpr = (uint32_t)tpr; a.gpr = a.gpu = a.upr = 0; a.n_units = (uint32_t)n_tiles;
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
             auto kernel = fwd_cf_scalar_kernel<T, W, kSilu>;
             kernel<<<persistent_grid(kernel, 256, n_tiles), 256, 0, stream>>>(a);

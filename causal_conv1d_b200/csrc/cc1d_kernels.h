@@ -6,7 +6,21 @@
 
 #include "cc1d.h"
 
+// Compile-time tunables (overridable with -D for experiments).
+#ifndef CC1D_CF_KVECS
+#define CC1D_CF_KVECS 4          // 16-byte vectors per lane per group, channel-first kernels
+#endif
+#ifndef CC1D_CF_FWD_PERSISTENT
+#define CC1D_CF_FWD_PERSISTENT 0   // 1: grid = resident CTAs with a grid-stride loop; 0: one warp unit per warp
+#endif
+#ifndef CC1D_CF_BWD_PERSISTENT
+#define CC1D_CF_BWD_PERSISTENT 2   // 2: persistent only for 16-bit I/O (issue-bound), one unit per warp for fp32
+#endif
+
 namespace cc1d {
+
+constexpr int kCfVecs = CC1D_CF_KVECS;
+constexpr int kCfGroupVecs = 32 * kCfVecs;
 
 // Number of SMs of the current device (cached per device; 148 on B200).
 int num_sms();
@@ -15,6 +29,7 @@ inline bool is_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p)
 inline int elem_size(int dtype) { return dtype == CC1D_F32 ? 4 : 2; }
 inline int vec_elems(int dtype) { return 16 / elem_size(dtype); }
 
+uint64_t groups_per_unit(uint64_t rows, uint64_t groups_per_row);
 int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream);
 int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream);
 
@@ -32,7 +47,8 @@ int launch_varlen_states(const cc1d_varlen_states_params &p, cudaStream_t stream
 int resident_ctas_per_sm(const void *kernel, int threads, size_t dyn_smem);
 
 template <typename K>
-inline unsigned persistent_grid(K kernel, int threads, uint64_t ctas_wanted) {
+inline unsigned persistent_grid(K kernel, int threads, uint64_t ctas_wanted, bool persistent = true) {
+    if (!persistent) return (unsigned)ctas_wanted;
     const uint64_t cap = (uint64_t)num_sms() * (uint64_t)resident_ctas_per_sm(reinterpret_cast<const void *>(kernel), threads, 0);
     return (unsigned)(ctas_wanted < cap ? ctas_wanted : cap);
 }

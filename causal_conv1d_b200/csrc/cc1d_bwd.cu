@@ -432,14 +432,84 @@ struct BwdClArgs {
     uint32_t ncols, ncolblk, ngroups;
 };
 
-constexpr int kBwdClRows = 8;
-constexpr int kBwdClUnroll = 4;
+constexpr int kBwdClRows = 8;     // token chunks per CTA
+constexpr int kBwdClUnroll = 4;   // positions per block (x and dout loads of the next block in flight)
+constexpr int kBwdClC = 4;        // channels per thread: 8-byte vectors for 16-bit I/O, 16-byte for fp32
+
+// One position `pos` of the backward sliding window (channel-last):
+//   g[pos]   = dout[pos] * act'(y[pos])            (y recomputed from the x window)
+//   dweight += x window * g[pos], dbias += g[pos]   (only while pos is inside the thread's chunk)
+//   dx[q]    = sum_m w[W-1-m] * g[q+m],  q = pos-(W-1)   (stored when q is inside the chunk;
+//              for q < 0 the same sum is dinitial_states[q+W-1])
+template <typename T, int W, int C, bool kSilu, bool kSeqIdx, bool kTanh>
+__device__ __forceinline__ void bwd_cl_position(
+    const Raw<T, C> &xraw, const Raw<T, C> &draw, int sid, bool accumulate, bool store_dx, bool store_dinit,
+    float (&xwin)[W - 1][C], float (&gwin)[W - 1][C], int (&swin)[W - 1], const float (&wv)[W][C],
+    const float (&bv)[C], float (&dw)[C][W + 1], const T *dfin_ptr, int64_t df_cs, char *dx_ptr, T *dinit_ptr) {
+    float xc[C], gc[C];
+    unpack_raw<T>(xraw, xc);
+    unpack_raw<T>(draw, gc);   // dout, turned into g below
+    #pragma unroll
+    for (int c = 0; c < C; ++c) {
+        if (kSilu) {
+            float y = bv[c];
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) {
+                if (!kSeqIdx || swin[k] == sid) y = fmaf(wv[k][c], xwin[k][c], y);
+            }
+            y = fmaf(wv[W - 1][c], xc[c], y);
+            gc[c] *= kTanh ? dsilu_half_arg(0.5f * y) : dsilu_f(y);
+        }
+        if (kSeqIdx && sid < 0) gc[c] = 0.f;   // padded token: out == 0 identically
+    }
+    if (accumulate) {
+        #pragma unroll
+        for (int c = 0; c < C; ++c) {
+            dw[c][W] += gc[c];
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) {
+                if (!kSeqIdx || swin[k] == sid) dw[c][k] = fmaf(xwin[k][c], gc[c], dw[c][k]);
+            }
+            dw[c][W - 1] = fmaf(xc[c], gc[c], dw[c][W - 1]);
+        }
+    }
+    if (store_dx || store_dinit) {
+        float o[C];
+        #pragma unroll
+        for (int c = 0; c < C; ++c) {
+            float acc = 0.f;
+            #pragma unroll
+            for (int m = 0; m < W - 1; ++m) {
+                if (!kSeqIdx || swin[m] == swin[0]) acc = fmaf(wv[W - 1 - m][c], gwin[m][c], acc);
+            }
+            if (!kSeqIdx || sid == swin[0]) acc = fmaf(wv[0][c], gc[c], acc);
+            o[c] = acc;
+        }
+        if (dfin_ptr != nullptr) {
+            #pragma unroll
+            for (int c = 0; c < C; ++c) o[c] += Elem<T>::to_f(dfin_ptr[c * df_cs]);
+        }
+        if (store_dx) st_stream_raw(dx_ptr, PackRaw<T, C>::run(o));
+        else st_plain_raw(dinit_ptr, PackRaw<T, C>::run(o));
+    }
+    #pragma unroll
+    for (int k = 0; k < W - 2; ++k) {
+        #pragma unroll
+        for (int c = 0; c < C; ++c) { xwin[k][c] = xwin[k + 1][c]; gwin[k][c] = gwin[k + 1][c]; }
+        swin[k] = swin[k + 1];
+    }
+    #pragma unroll
+    for (int c = 0; c < C; ++c) { xwin[W - 2][c] = xc[c]; gwin[W - 2][c] = gc[c]; }
+    swin[W - 2] = sid;
+}
 
 template <typename T, int W, bool kSilu, bool kSeqIdx>
-__global__ void __launch_bounds__(32 * kBwdClRows) bwd_cl_kernel(const BwdClArgs a) {
-    constexpr int C = Elem<T>::kVec;
+__global__ void __launch_bounds__(32 * kBwdClRows, 2) bwd_cl_kernel(const BwdClArgs a) {
+    constexpr int C = kBwdClC;
+    constexpr int U = kBwdClUnroll;
     constexpr int kAcc = (W + 1) * C;                    // fp32 partial sums per thread
-    __shared__ __align__(16) float s_w[(W + 1) * 32 * C];
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    using R = Raw<T, C>;
     __shared__ __align__(16) float s_red[(kBwdClRows - 1) * 32 * kAcc];
 
     const uint32_t cb = blockIdx.x % a.ncolblk;
@@ -447,14 +517,9 @@ __global__ void __launch_bounds__(32 * kBwdClRows) bwd_cl_kernel(const BwdClArgs
     const uint32_t grp = rest % a.ngroups;
     const uint32_t b = rest / a.ngroups;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-
-    stage_weights<W>(s_w, 32 * C, (int64_t)cb * 32 * C, a.dim, a.weight, a.w_cs, a.w_ws, a.bias,
-                     a.wtype, threadIdx.x, 32 * kBwdClRows);
-    __syncthreads();
-
     const uint32_t col = cb * 32 + tx;
-    const int64_t L = a.seqlen;
-    const int64_t t0 = ((int64_t)grp * kBwdClRows + ty) * a.tpt;
+    const int L = (int)a.seqlen;
+    const int t0 = (int)((grp * kBwdClRows + ty) * (uint32_t)a.tpt);
     const bool active = col < a.ncols && t0 < L;
 
     float dw[C][W + 1];   // [.][W] is dbias
@@ -465,127 +530,87 @@ __global__ void __launch_bounds__(32 * kBwdClRows) bwd_cl_kernel(const BwdClArgs
     }
 
     if (active) {
-        const int64_t t1 = t0 + a.tpt < L ? t0 + a.tpt : L;
-        const int64_t s_end = t1 + (W - 1);
-        float wv[W][C], bv[C];
+        const int t1 = t0 + a.tpt < L ? t0 + a.tpt : L;
+        const int n_ext = t1 - t0 + (W - 1);                                   // positions to process
+        const int n_ld = (t1 + (W - 1) < L ? t1 + (W - 1) : L) - t0;            // positions that exist
+        const int n_x = kSilu ? n_ld : t1 - t0;                                 // x past the chunk only feeds y
+        const int64_t xs = a.x_ls * (int64_t)sizeof(T), ds = a.d_ls * (int64_t)sizeof(T), os = a.o_ls * (int64_t)sizeof(T);
+        const int64_t cofs = (int64_t)col * C * (int64_t)sizeof(T);
+        const char *xptr = reinterpret_cast<const char *>(a.x) + b * a.x_bs * (int64_t)sizeof(T) + cofs + t0 * xs;
+        const char *dptr = reinterpret_cast<const char *>(a.dout) + b * a.d_bs * (int64_t)sizeof(T) + cofs + t0 * ds;
+        char *optr = reinterpret_cast<char *>(a.dx) + b * a.o_bs * (int64_t)sizeof(T) + cofs + (t0 - (W - 1)) * os;
+        const int32_t *__restrict__ sp = kSeqIdx ? a.seq_idx + (int64_t)b * L + t0 : nullptr;
+
+        R xr[U], dr[U];
+        int sid[U];
         #pragma unroll
-        for (int k = 0; k < W; ++k) {
-            #pragma unroll
-            for (int c = 0; c < C; ++c) wv[k][c] = s_w[k * 32 * C + tx * C + c];
+        for (int u = 0; u < U; ++u) {
+            zero_raw(xr[u]); zero_raw(dr[u]);
+            sid[u] = -2;   // beyond the sequence: matches nothing
+            if (u < n_x) ld_stream_raw(xr[u], xptr + u * xs);
+            if (u < n_ld) {
+                ld_stream_raw(dr[u], dptr + u * ds);
+                if (kSeqIdx) sid[u] = sp[u];
+            }
         }
-        #pragma unroll
-        for (int c = 0; c < C; ++c) bv[c] = s_w[W * 32 * C + tx * C + c];
-
-        const T *__restrict__ xp = reinterpret_cast<const T *>(a.x) + b * a.x_bs + (int64_t)col * C;
-        const T *__restrict__ dp = reinterpret_cast<const T *>(a.dout) + b * a.d_bs + (int64_t)col * C;
-        T *__restrict__ op = reinterpret_cast<T *>(a.dx) + b * a.o_bs + (int64_t)col * C;
-        const int32_t *__restrict__ sp = kSeqIdx ? a.seq_idx + (int64_t)b * L : nullptr;
-
-        // x and g at the width-1 positions before the current one; g before t0 is never used
+        // x at the width-1 positions before t0 (x, initial_states or zero); g before t0 is never used
         float xwin[W - 1][C], gwin[W - 1][C];
         int swin[W - 1];
         #pragma unroll
         for (int k = 0; k < W - 1; ++k) {
-            const int64_t p = t0 - (W - 1) + k;
-            uint4 r = make_uint4(0, 0, 0, 0);
+            const int p = t0 - (W - 1) + k;
+            R r;
+            zero_raw(r);
             swin[k] = -1;
             if (p >= 0) {
-                r = ld_cached(xp + p * a.x_ls);
-                if (kSeqIdx) swin[k] = sp[p];
+                ld_cached_raw(r, xptr - (W - 1 - k) * xs);
+                if (kSeqIdx) swin[k] = sp[k - (W - 1)];
             } else if (a.init != nullptr) {
-                r = ld_cached(reinterpret_cast<const T *>(a.init) + b * a.i_bs + (p + (W - 1)) * a.i_ls + (int64_t)col * C);
+                ld_cached_raw(r, reinterpret_cast<const T *>(a.init) + b * a.i_bs + (p + (W - 1)) * a.i_ls + (int64_t)col * C);
             }
-            unpack<T>(r, xwin[k]);
+            unpack_raw<T>(r, xwin[k]);
             #pragma unroll
             for (int c = 0; c < C; ++c) gwin[k][c] = 0.f;
         }
+        float wv[W][C], bv[C];
+        load_taps<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, 1.f);
 
-        for (int64_t s = t0; s < s_end; s += kBwdClUnroll) {
-            uint4 xr[kBwdClUnroll], dr[kBwdClUnroll];
-            int sid[kBwdClUnroll];
+        const bool want_dinit = a.dinit != nullptr && t0 == 0;
+        const T *dfin_base = a.dfin != nullptr ? reinterpret_cast<const T *>(a.dfin) + b * a.df_bs + (int64_t)col * C * a.df_cs : nullptr;
+        T *dinit_base = want_dinit ? reinterpret_cast<T *>(a.dinit) + b * a.di_bs + (int64_t)col * C : nullptr;
+
+        for (int base = 0; base < n_ext; base += U) {
+            R xn[U], dn[U];
+            int nsid[U];
             #pragma unroll
-            for (int u = 0; u < kBwdClUnroll; ++u) {
-                const int64_t pos = s + u;
-                xr[u] = make_uint4(0, 0, 0, 0);
-                dr[u] = make_uint4(0, 0, 0, 0);
-                sid[u] = -2;   // beyond the sequence: matches nothing
-                if (pos < s_end && pos < L) {
-                    if (kSilu || pos < t1) xr[u] = ld_stream(xp + pos * a.x_ls);
-                    dr[u] = ld_stream(dp + pos * a.d_ls);
-                    if (kSeqIdx) sid[u] = sp[pos];
+            for (int u = 0; u < U; ++u) {
+                zero_raw(xn[u]); zero_raw(dn[u]);
+                nsid[u] = -2;
+                const int i = base + U + u;
+                if (i < n_x) ld_stream_raw(xn[u], xptr + (U + u) * xs);
+                if (i < n_ld) {
+                    ld_stream_raw(dn[u], dptr + (U + u) * ds);
+                    if (kSeqIdx) nsid[u] = sp[U + u];
                 }
             }
             #pragma unroll
-            for (int u = 0; u < kBwdClUnroll; ++u) {
-                const int64_t pos = s + u;
-                if (pos < s_end) {
-                    float xc[C], gc[C];
-                    unpack<T>(xr[u], xc);
-                    unpack<T>(dr[u], gc);   // dout, turned into g below
-                    #pragma unroll
-                    for (int c = 0; c < C; ++c) {
-                        if (kSilu) {
-                            float y = bv[c];
-                            #pragma unroll
-                            for (int k = 0; k < W - 1; ++k) {
-                                if (!kSeqIdx || swin[k] == sid[u]) y = fmaf(wv[k][c], xwin[k][c], y);
-                            }
-                            y = fmaf(wv[W - 1][c], xc[c], y);
-                            gc[c] *= dsilu_f(y);
-                        }
-                        if (kSeqIdx && sid[u] < 0) gc[c] = 0.f;   // padded token: out == 0 identically
-                    }
-                    if (pos < t1) {
-                        #pragma unroll
-                        for (int c = 0; c < C; ++c) {
-                            dw[c][W] += gc[c];
-                            #pragma unroll
-                            for (int k = 0; k < W - 1; ++k) {
-                                if (!kSeqIdx || swin[k] == sid[u]) dw[c][k] = fmaf(xwin[k][c], gc[c], dw[c][k]);
-                            }
-                            dw[c][W - 1] = fmaf(xc[c], gc[c], dw[c][W - 1]);
-                        }
-                    }
-                    // gradient w.r.t. the input at q = pos-(W-1): taps g[q .. q+W-1]
-                    const int64_t q = pos - (W - 1);
-                    const bool to_dx = q >= t0;                                   // q < t1 holds
-                    const bool to_dinit = q < 0 && a.dinit != nullptr;           // only when t0 == 0
-                    if (to_dx || to_dinit) {
-                        float o[C];
-                        #pragma unroll
-                        for (int c = 0; c < C; ++c) {
-                            float acc = 0.f;
-                            #pragma unroll
-                            for (int m = 0; m < W - 1; ++m) {
-                                if (!kSeqIdx || swin[m] == swin[0]) acc = fmaf(wv[W - 1 - m][c], gwin[m][c], acc);
-                            }
-                            if (!kSeqIdx || sid[u] == swin[0]) acc = fmaf(wv[0][c], gc[c], acc);
-                            o[c] = acc;
-                        }
-                        if (a.dfin != nullptr && q >= L - (W - 1)) {
-                            const T *df = reinterpret_cast<const T *>(a.dfin) + b * a.df_bs +
-                                          (q - (L - (W - 1))) * a.df_ls + (int64_t)col * C * a.df_cs;
-                            #pragma unroll
-                            for (int c = 0; c < C; ++c) o[c] += Elem<T>::to_f(df[c * a.df_cs]);
-                        }
-                        if (to_dx) {
-                            st_stream(op + q * a.o_ls, pack<T>(o));
-                        } else {
-                            T *di = reinterpret_cast<T *>(a.dinit) + b * a.di_bs + (q + (W - 1)) * a.di_ls + (int64_t)col * C;
-                            *reinterpret_cast<uint4 *>(di) = pack<T>(o);
-                        }
-                    }
-                    #pragma unroll
-                    for (int k = 0; k < W - 2; ++k) {
-                        #pragma unroll
-                        for (int c = 0; c < C; ++c) { xwin[k][c] = xwin[k + 1][c]; gwin[k][c] = gwin[k + 1][c]; }
-                        swin[k] = swin[k + 1];
-                    }
-                    #pragma unroll
-                    for (int c = 0; c < C; ++c) { xwin[W - 2][c] = xc[c]; gwin[W - 2][c] = gc[c]; }
-                    swin[W - 2] = sid[u];
+            for (int u = 0; u < U; ++u) {
+                const int i = base + u;          // position t0 + i
+                if (i < n_ext) {
+                    const int q = t0 + i - (W - 1);   // dx position produced now
+                    const bool st_dx = i >= W - 1;     // q >= t0 (q < t1 always holds)
+                    const bool st_di = q < 0 && want_dinit;
+                    const T *df = (dfin_base != nullptr && q >= L - (W - 1)) ? dfin_base + (q - (L - (W - 1))) * a.df_ls : nullptr;
+                    T *di = st_di ? dinit_base + (q + (W - 1)) * a.di_ls : nullptr;
+                    bwd_cl_position<T, W, C, kSilu, kSeqIdx, kTanh>(
+                        xr[u], dr[u], sid[u], t0 + i < t1, st_dx, st_di, xwin, gwin, swin, wv, bv, dw, df, a.df_cs,
+                        optr + u * os, di);
                 }
             }
+            xptr += U * xs; dptr += U * ds; optr += U * os;
+            if (kSeqIdx) sp += U;
+            #pragma unroll
+            for (int u = 0; u < U; ++u) { xr[u] = xn[u]; dr[u] = dn[u]; sid[u] = nsid[u]; }
         }
     }
 
@@ -627,7 +652,7 @@ struct ClPlan {
 };
 
 static ClPlan plan_channel_last(const cc1d_bwd_params &p) {
-    const int C = vec_elems(p.itype);
+    const int C = kBwdClC;
     ClPlan pl;
     const int64_t ncols = p.dim / C;
     pl.tpt = pick_tokens_per_thread(p.batch, ncols, p.seqlen, kTilingSMs / 2, 128);
@@ -644,7 +669,7 @@ size_t bwd_workspace_bytes_channel_last(const cc1d_bwd_params &p) {
 }
 
 int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
-    const int C = vec_elems(p.itype);
+    const int C = kBwdClC;
     if (!is_aligned16(p.x) || !is_aligned16(p.dout) || !is_aligned16(p.dx)) return CC1D_ERR_ALIGN;
     if (p.initial_states && (!is_aligned16(p.initial_states) || p.initial_states_batch_stride % C ||
                              p.initial_states_l_stride % C)) return CC1D_ERR_ALIGN;

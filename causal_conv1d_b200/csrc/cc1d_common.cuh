@@ -108,6 +108,55 @@ template <> __device__ __forceinline__ uint4 pack<__half>(const float *f) {
     return make_uint4(r[0], r[1], r[2], r[3]);
 }
 
+// ---- 8- or 16-byte per-lane vectors of C elements (channel-last kernels) -------------------
+template <int BYTES> struct RawBytes;
+template <> struct RawBytes<16> { using type = uint4; };
+template <> struct RawBytes<8> { using type = uint2; };
+template <typename T, int C> using Raw = typename RawBytes<sizeof(T) * C>::type;
+
+__device__ __forceinline__ void zero_raw(uint4 &v) { v = make_uint4(0, 0, 0, 0); }
+__device__ __forceinline__ void zero_raw(uint2 &v) { v = make_uint2(0, 0); }
+
+__device__ __forceinline__ void ld_stream_raw(uint4 &v, const void *p) { v = ld_stream(p); }
+__device__ __forceinline__ void ld_stream_raw(uint2 &v, const void *p) {
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+}
+__device__ __forceinline__ void ld_cached_raw(uint4 &v, const void *p) { v = *reinterpret_cast<const uint4 *>(p); }
+__device__ __forceinline__ void ld_cached_raw(uint2 &v, const void *p) { v = *reinterpret_cast<const uint2 *>(p); }
+__device__ __forceinline__ void st_stream_raw(void *p, const uint4 &v) { st_stream(p, v); }
+__device__ __forceinline__ void st_stream_raw(void *p, const uint2 &v) {
+    asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" :: "l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ void st_plain_raw(void *p, const uint4 &v) { *reinterpret_cast<uint4 *>(p) = v; }
+__device__ __forceinline__ void st_plain_raw(void *p, const uint2 &v) { *reinterpret_cast<uint2 *>(p) = v; }
+
+template <typename T> __device__ __forceinline__ void unpack_raw(const uint4 &v, float *f) { unpack<T>(v, f); }
+template <typename T> __device__ __forceinline__ void unpack_raw(const uint2 &v, float *f);   // 4 x 16-bit
+template <> __device__ __forceinline__ void unpack_raw<__nv_bfloat16>(const uint2 &v, float *f) {
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void unpack_raw<__half>(const uint2 &v, float *f) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&v.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+template <typename T, int C> struct PackRaw;
+template <typename T> struct PackRaw<T, 8> { static __device__ __forceinline__ uint4 run(const float *f) { return pack<T>(f); } };
+template <> struct PackRaw<float, 4> { static __device__ __forceinline__ uint4 run(const float *f) { return pack<float>(f); } };
+template <> struct PackRaw<__nv_bfloat16, 4> {
+    static __device__ __forceinline__ uint2 run(const float *f) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+        return make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
+    }
+};
+template <> struct PackRaw<__half, 4> {
+    static __device__ __forceinline__ uint2 run(const float *f) {
+        const __half2 a = __floats2half2_rn(f[0], f[1]), b = __floats2half2_rn(f[2], f[3]);
+        return make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
+    }
+};
+
 // ---- activation ---------------------------------------------------------------------------
 // Two evaluations of SiLU.  "exact": sigmoid through ex2 + rcp (2 special-function ops per
 // element).  "tanh": sigmoid(y) = 0.5 * tanh(y/2) + 0.5 with the hardware tanh.approx (1

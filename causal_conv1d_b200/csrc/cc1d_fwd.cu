@@ -210,106 +210,127 @@ struct FwdClArgs {
 };
 
 constexpr int kClRows = 8;    // token chunks per CTA (threadIdx.y)
-constexpr int kClUnroll = 4;  // independent 16-byte loads in flight per thread
+constexpr int kClUnroll = 4;  // tokens per block: loads of one block are in flight while the previous computes
+
+// One token of the sliding window: out = act(bias + sum_k w[k] * window[k]), then shift.
+template <typename T, int W, int C, bool kSilu, bool kSeqIdx, bool kTanh>
+__device__ __forceinline__ void fwd_cl_token(const Raw<T, C> &raw, int sid, float (&win)[W - 1][C], int (&sw)[W - 1],
+                                             const float (&wv)[W][C], const float (&bv)[C], char *optr) {
+    float cur[C], o[C];
+    unpack_raw<T>(raw, cur);
+    #pragma unroll
+    for (int c = 0; c < C; ++c) {
+        float acc = bv[c];
+        #pragma unroll
+        for (int k = 0; k < W - 1; ++k) {
+            if (!kSeqIdx || sw[k] == sid) acc = fmaf(wv[k][c], win[k][c], acc);
+        }
+        acc = fmaf(wv[W - 1][c], cur[c], acc);
+        if (kSilu) acc = kTanh ? silu_half_arg(acc) : silu_f(acc);
+        // a padded token (seq_idx < 0) outputs exactly zero: no bias, no activation
+        o[c] = (kSeqIdx && sid < 0) ? 0.f : acc;
+    }
+    st_stream_raw(optr, PackRaw<T, C>::run(o));
+    #pragma unroll
+    for (int k = 0; k < W - 2; ++k) {
+        #pragma unroll
+        for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
+        sw[k] = sw[k + 1];
+    }
+    #pragma unroll
+    for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
+    sw[W - 2] = sid;
+}
 
 template <typename T, int W, bool kSilu, bool kSeqIdx>
-__global__ void __launch_bounds__(32 * kClRows) fwd_cl_kernel(const FwdClArgs a) {
-    constexpr int C = Elem<T>::kVec;  // channels per thread
-    __shared__ __align__(16) float s_w[(W + 1) * 32 * C];
+__global__ void __launch_bounds__(32 * kClRows, 2) fwd_cl_kernel(const FwdClArgs a) {
+    constexpr int C = Elem<T>::kVec;  // channels per thread (one 16-byte vector)
+    constexpr int U = kClUnroll;
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    using R = Raw<T, C>;
 
     const uint32_t cb = blockIdx.x % a.ncolblk;
     const uint32_t rest = blockIdx.x / a.ncolblk;
     const uint32_t grp = rest % a.ngroups;
     const uint32_t b = rest / a.ngroups;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-
-    stage_weights<W>(s_w, 32 * C, (int64_t)cb * 32 * C, a.dim, a.weight, a.w_cs, a.w_ws, a.bias,
-                     a.wtype, threadIdx.x, 32 * kClRows);
-    __syncthreads();
-
     const uint32_t col = cb * 32 + tx;
-    const int64_t t0 = ((int64_t)grp * kClRows + ty) * a.tpt;
-    if (col >= a.ncols || t0 >= a.seqlen) return;
-    const int64_t t1 = t0 + a.tpt < a.seqlen ? t0 + a.tpt : a.seqlen;
+    const int L = (int)a.seqlen;
+    const int t0 = (int)((grp * kClRows + ty) * (uint32_t)a.tpt);
+    if (col >= a.ncols || t0 >= L) return;
+    const int t1 = t0 + a.tpt < L ? t0 + a.tpt : L;
 
-    float wv[W][C], bv[C];
+    const int64_t xs = a.x_ls * (int64_t)sizeof(T), os = a.o_ls * (int64_t)sizeof(T);   // token strides in bytes
+    const char *xptr = reinterpret_cast<const char *>(a.x) + (b * a.x_bs + (int64_t)col * C) * (int64_t)sizeof(T) + t0 * xs;
+    char *optr = reinterpret_cast<char *>(a.out) + (b * a.o_bs + (int64_t)col * C) * (int64_t)sizeof(T) + t0 * os;
+    const int32_t *__restrict__ sp = kSeqIdx ? a.seq_idx + (int64_t)b * L + t0 : nullptr;
+
+    // first block of tokens and the window in front of it: all requested before the taps
+    const int n = t1 - t0, nfull = n / U;
+    R raw[U];
+    int sid[U];
     #pragma unroll
-    for (int k = 0; k < W; ++k) {
-        #pragma unroll
-        for (int c = 0; c < C; ++c) wv[k][c] = s_w[k * 32 * C + tx * C + c];
+    for (int u = 0; u < U; ++u) {
+        zero_raw(raw[u]);
+        sid[u] = 0;
+        if (u < n) {
+            ld_stream_raw(raw[u], xptr + u * xs);
+            if (kSeqIdx) sid[u] = sp[u];
+        }
     }
-    #pragma unroll
-    for (int c = 0; c < C; ++c) bv[c] = s_w[W * 32 * C + tx * C + c];
-
-    const T *__restrict__ xp = reinterpret_cast<const T *>(a.x) + b * a.x_bs + (int64_t)col * C;
-    T *__restrict__ op = reinterpret_cast<T *>(a.out) + b * a.o_bs + (int64_t)col * C;
-    const int32_t *__restrict__ sp = kSeqIdx ? a.seq_idx + (int64_t)b * a.seqlen : nullptr;
-
     // window = the width-1 tokens before t0 (x, or initial_states, or zero)
     float win[W - 1][C];
     int sw[W - 1];
     #pragma unroll
     for (int k = 0; k < W - 1; ++k) {
-        const int64_t p = t0 - (W - 1) + k;
-        uint4 r = make_uint4(0, 0, 0, 0);
+        const int p = t0 - (W - 1) + k;
+        R r;
+        zero_raw(r);
         sw[k] = -1;
         if (p >= 0) {
-            r = ld_cached(xp + p * a.x_ls);
-            if (kSeqIdx) sw[k] = sp[p];
+            ld_cached_raw(r, xptr - (W - 1 - k) * xs);
+            if (kSeqIdx) sw[k] = sp[k - (W - 1)];
         } else if (a.init != nullptr) {
-            r = ld_cached(reinterpret_cast<const T *>(a.init) + b * a.i_bs + (p + (W - 1)) * a.i_ls + (int64_t)col * C);
+            ld_cached_raw(r, reinterpret_cast<const T *>(a.init) + b * a.i_bs + (p + (W - 1)) * a.i_ls + (int64_t)col * C);
         }
-        unpack<T>(r, win[k]);
+        unpack_raw<T>(r, win[k]);
     }
+    float wv[W][C], bv[C];
+    load_taps<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, kTanh ? 0.5f : 1.f);
 
-    for (int64_t t = t0; t < t1; t += kClUnroll) {
-        uint4 raw[kClUnroll];
-        int sid[kClUnroll];
+    // full blocks: the next block's loads are issued before the current block is computed
+    for (int blk = 0; blk < nfull; ++blk) {
+        R nxt[U];
+        int nsid[U];
+        const int left = n - (blk + 1) * U;   // tokens after this block
         #pragma unroll
-        for (int u = 0; u < kClUnroll; ++u) {
-            raw[u] = make_uint4(0, 0, 0, 0);
-            sid[u] = 0;
-            if (t + u < t1) {
-                raw[u] = ld_stream(xp + (t + u) * a.x_ls);
-                if (kSeqIdx) sid[u] = sp[t + u];
+        for (int u = 0; u < U; ++u) {
+            zero_raw(nxt[u]);
+            nsid[u] = 0;
+            if (u < left) {
+                ld_stream_raw(nxt[u], xptr + (U + u) * xs);
+                if (kSeqIdx) nsid[u] = sp[U + u];
             }
         }
         #pragma unroll
-        for (int u = 0; u < kClUnroll; ++u) {
-            if (t + u < t1) {
-                float cur[C], o[C];
-                unpack<T>(raw[u], cur);
-                #pragma unroll
-                for (int c = 0; c < C; ++c) {
-                    float acc = bv[c];
-                    #pragma unroll
-                    for (int k = 0; k < W - 1; ++k) {
-                        if (!kSeqIdx || sw[k] == sid[u]) acc = fmaf(wv[k][c], win[k][c], acc);
-                    }
-                    acc = fmaf(wv[W - 1][c], cur[c], acc);
-                    if (kSilu) acc = silu_f(acc);
-                    // a padded token (seq_idx < 0) outputs exactly zero: no bias, no activation
-                    o[c] = (kSeqIdx && sid[u] < 0) ? 0.f : acc;
-                }
-                st_stream(op + (t + u) * a.o_ls, pack<T>(o));
-                #pragma unroll
-                for (int k = 0; k < W - 2; ++k) {
-                    #pragma unroll
-                    for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
-                    sw[k] = sw[k + 1];
-                }
-                #pragma unroll
-                for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
-                sw[W - 2] = sid[u];
-            }
-        }
+        for (int u = 0; u < U; ++u) fwd_cl_token<T, W, C, kSilu, kSeqIdx, kTanh>(raw[u], sid[u], win, sw, wv, bv, optr + u * os);
+        xptr += U * xs;
+        optr += U * os;
+        if (kSeqIdx) sp += U;
+        #pragma unroll
+        for (int u = 0; u < U; ++u) { raw[u] = nxt[u]; sid[u] = nsid[u]; }
+    }
+    // ragged tail (already loaded)
+    #pragma unroll
+    for (int u = 0; u < U; ++u) {
+        if (u < n - nfull * U) fwd_cl_token<T, W, C, kSilu, kSeqIdx, kTanh>(raw[u], sid[u], win, sw, wv, bv, optr + u * os);
     }
 
     // the thread that consumed the last token holds the last width-1 entries of [initial | x]
-    if (a.fin != nullptr && t1 == a.seqlen) {
+    if (a.fin != nullptr && t1 == L) {
         T *fp = reinterpret_cast<T *>(a.fin) + b * a.f_bs + (int64_t)col * C;
         #pragma unroll
-        for (int k = 0; k < W - 1; ++k) *reinterpret_cast<uint4 *>(fp + k * a.f_ls) = pack<T>(win[k]);
+        for (int k = 0; k < W - 1; ++k) st_plain_raw(fp + k * a.f_ls, PackRaw<T, C>::run(win[k]));
     }
 }
 

@@ -432,8 +432,17 @@ struct BwdClArgs {
     uint32_t ncols, ncolblk, ngroups;
 };
 
-constexpr int kBwdClRows = 8;     // token chunks per CTA
-constexpr int kBwdClUnroll = 4;   // positions per block (x and dout loads of the next block in flight)
+#ifndef CC1D_BWD_CL_ROWS
+#define CC1D_BWD_CL_ROWS 4
+#endif
+#ifndef CC1D_BWD_CL_UNROLL
+#define CC1D_BWD_CL_UNROLL 4
+#endif
+#ifndef CC1D_BWD_CL_MINBLK
+#define CC1D_BWD_CL_MINBLK 3
+#endif
+constexpr int kBwdClRows = CC1D_BWD_CL_ROWS;       // token chunks per CTA
+constexpr int kBwdClUnroll = CC1D_BWD_CL_UNROLL;   // positions per block (x and dout loads of the next block in flight)
 constexpr int kBwdClC = 4;        // channels per thread: 8-byte vectors for 16-bit I/O, 16-byte for fp32
 
 // One position `pos` of the backward sliding window (channel-last):
@@ -441,70 +450,98 @@ constexpr int kBwdClC = 4;        // channels per thread: 8-byte vectors for 16-
 //   dweight += x window * g[pos], dbias += g[pos]   (only while pos is inside the thread's chunk)
 //   dx[q]    = sum_m w[W-1-m] * g[q+m],  q = pos-(W-1)   (stored when q is inside the chunk;
 //              for q < 0 the same sum is dinitial_states[q+W-1])
-template <typename T, int W, int C, bool kSilu, bool kSeqIdx, bool kTanh>
-__device__ __forceinline__ void bwd_cl_position(
+// All arithmetic is on fp32 pairs of adjacent channels (FFMA2: two FMAs per issue slot).
+template <typename T, int W, int C, bool kSilu, bool kMask, bool kTanh>
+__device__ __forceinline__ void bwd_cl_position_impl(
     const Raw<T, C> &xraw, const Raw<T, C> &draw, int sid, bool accumulate, bool store_dx, bool store_dinit,
-    float (&xwin)[W - 1][C], float (&gwin)[W - 1][C], int (&swin)[W - 1], const float (&wv)[W][C],
-    const float (&bv)[C], float (&dw)[C][W + 1], const T *dfin_ptr, int64_t df_cs, char *dx_ptr, T *dinit_ptr) {
-    float xc[C], gc[C];
-    unpack_raw<T>(xraw, xc);
-    unpack_raw<T>(draw, gc);   // dout, turned into g below
+    float2 (&xwin)[W - 1][C / 2], float2 (&gwin)[W - 1][C / 2], int (&swin)[W - 1], const float2 (&wv)[W][C / 2],
+    const float2 (&bv)[C / 2], float2 (&dw)[C / 2][W + 1], const T *dfin_ptr, int64_t df_cs, char *dx_ptr, T *dinit_ptr) {
+    constexpr int P = C / 2;
+    float2 xc[P], gc[P];
+    unpack_pairs<T>(xraw, xc);
+    unpack_pairs<T>(draw, gc);   // dout, turned into g below
     #pragma unroll
-    for (int c = 0; c < C; ++c) {
+    for (int c = 0; c < P; ++c) {
         if (kSilu) {
-            float y = bv[c];
+            float2 y = bv[c];
             #pragma unroll
             for (int k = 0; k < W - 1; ++k) {
-                if (!kSeqIdx || swin[k] == sid) y = fmaf(wv[k][c], xwin[k][c], y);
+                if (!kMask || swin[k] == sid) y = fma2(wv[k][c], xwin[k][c], y);
             }
-            y = fmaf(wv[W - 1][c], xc[c], y);
-            gc[c] *= kTanh ? dsilu_half_arg(0.5f * y) : dsilu_f(y);
+            y = fma2(wv[W - 1][c], xc[c], y);
+            if (kTanh) y = mul2(y, splat2(0.5f));
+            gc[c] = mul2(gc[c], dsilu_pair<kTanh>(y));
         }
-        if (kSeqIdx && sid < 0) gc[c] = 0.f;   // padded token: out == 0 identically
+        if (kMask && sid < 0) gc[c] = make_float2(0.f, 0.f);   // padded token: out == 0 identically
     }
     if (accumulate) {
         #pragma unroll
-        for (int c = 0; c < C; ++c) {
-            dw[c][W] += gc[c];
+        for (int c = 0; c < P; ++c) {
+            dw[c][W] = add2(dw[c][W], gc[c]);
             #pragma unroll
             for (int k = 0; k < W - 1; ++k) {
-                if (!kSeqIdx || swin[k] == sid) dw[c][k] = fmaf(xwin[k][c], gc[c], dw[c][k]);
+                if (!kMask || swin[k] == sid) dw[c][k] = fma2(xwin[k][c], gc[c], dw[c][k]);
             }
-            dw[c][W - 1] = fmaf(xc[c], gc[c], dw[c][W - 1]);
+            dw[c][W - 1] = fma2(xc[c], gc[c], dw[c][W - 1]);
         }
     }
     if (store_dx || store_dinit) {
-        float o[C];
+        float2 o[P];
         #pragma unroll
-        for (int c = 0; c < C; ++c) {
-            float acc = 0.f;
+        for (int c = 0; c < P; ++c) {
+            float2 acc = make_float2(0.f, 0.f);
             #pragma unroll
             for (int m = 0; m < W - 1; ++m) {
-                if (!kSeqIdx || swin[m] == swin[0]) acc = fmaf(wv[W - 1 - m][c], gwin[m][c], acc);
+                if (!kMask || swin[m] == swin[0]) acc = fma2(wv[W - 1 - m][c], gwin[m][c], acc);
             }
-            if (!kSeqIdx || sid == swin[0]) acc = fmaf(wv[0][c], gc[c], acc);
+            if (!kMask || sid == swin[0]) acc = fma2(wv[0][c], gc[c], acc);
             o[c] = acc;
         }
         if (dfin_ptr != nullptr) {
             #pragma unroll
-            for (int c = 0; c < C; ++c) o[c] += Elem<T>::to_f(dfin_ptr[c * df_cs]);
+            for (int c = 0; c < P; ++c) {
+                o[c].x += Elem<T>::to_f(dfin_ptr[(2 * c) * df_cs]);
+                o[c].y += Elem<T>::to_f(dfin_ptr[(2 * c + 1) * df_cs]);
+            }
         }
-        if (store_dx) st_stream_raw(dx_ptr, PackRaw<T, C>::run(o));
-        else st_plain_raw(dinit_ptr, PackRaw<T, C>::run(o));
+        if (store_dx) st_stream_raw(dx_ptr, PackPairs<T, C>::run(o));
+        else st_plain_raw(dinit_ptr, PackPairs<T, C>::run(o));
     }
     #pragma unroll
     for (int k = 0; k < W - 2; ++k) {
         #pragma unroll
-        for (int c = 0; c < C; ++c) { xwin[k][c] = xwin[k + 1][c]; gwin[k][c] = gwin[k + 1][c]; }
+        for (int c = 0; c < P; ++c) { xwin[k][c] = xwin[k + 1][c]; gwin[k][c] = gwin[k + 1][c]; }
         swin[k] = swin[k + 1];
     }
     #pragma unroll
-    for (int c = 0; c < C; ++c) { xwin[W - 2][c] = xc[c]; gwin[W - 2][c] = gc[c]; }
+    for (int c = 0; c < P; ++c) { xwin[W - 2][c] = xc[c]; gwin[W - 2][c] = gc[c]; }
     swin[W - 2] = sid;
 }
 
+// seq_idx depends on (batch, token) only, so it is uniform across a warp.  Sequence
+// boundaries are rare: when the window and the current token all carry one non-negative id,
+// no tap is masked and the unmasked code runs (a warp-uniform branch).
+template <typename T, int W, int C, bool kSilu, bool kSeqIdx, bool kTanh>
+__device__ __forceinline__ void bwd_cl_position(
+    const Raw<T, C> &xraw, const Raw<T, C> &draw, int sid, bool accumulate, bool store_dx, bool store_dinit,
+    float2 (&xwin)[W - 1][C / 2], float2 (&gwin)[W - 1][C / 2], int (&swin)[W - 1], const float2 (&wv)[W][C / 2],
+    const float2 (&bv)[C / 2], float2 (&dw)[C / 2][W + 1], const T *dfin_ptr, int64_t df_cs, char *dx_ptr, T *dinit_ptr) {
+    if (kSeqIdx) {
+        bool same = sid >= 0;
+        #pragma unroll
+        for (int k = 0; k < W - 1; ++k) same = same && swin[k] == sid;
+        if (same) {
+            bwd_cl_position_impl<T, W, C, kSilu, false, kTanh>(xraw, draw, sid, accumulate, store_dx, store_dinit, xwin, gwin,
+                                                                 swin, wv, bv, dw, dfin_ptr, df_cs, dx_ptr, dinit_ptr);
+            return;
+        }
+    }
+    bwd_cl_position_impl<T, W, C, kSilu, kSeqIdx, kTanh>(xraw, draw, sid, accumulate, store_dx, store_dinit, xwin, gwin, swin,
+                                                           wv, bv, dw, dfin_ptr, df_cs, dx_ptr, dinit_ptr);
+}
+
 template <typename T, int W, bool kSilu, bool kSeqIdx>
-__global__ void __launch_bounds__(32 * kBwdClRows, 2) bwd_cl_kernel(const BwdClArgs a) {
+__global__ void __launch_bounds__(32 * kBwdClRows, CC1D_BWD_CL_MINBLK) bwd_cl_kernel(const BwdClArgs a) {
     constexpr int C = kBwdClC;
     constexpr int U = kBwdClUnroll;
     constexpr int kAcc = (W + 1) * C;                    // fp32 partial sums per thread
@@ -522,11 +559,11 @@ __global__ void __launch_bounds__(32 * kBwdClRows, 2) bwd_cl_kernel(const BwdClA
     const int t0 = (int)((grp * kBwdClRows + ty) * (uint32_t)a.tpt);
     const bool active = col < a.ncols && t0 < L;
 
-    float dw[C][W + 1];   // [.][W] is dbias
+    float2 dw[C / 2][W + 1];   // pairs of adjacent channels; [.][W] is dbias
     #pragma unroll
-    for (int c = 0; c < C; ++c) {
+    for (int c = 0; c < C / 2; ++c) {
         #pragma unroll
-        for (int k = 0; k <= W; ++k) dw[c][k] = 0.f;
+        for (int k = 0; k <= W; ++k) dw[c][k] = make_float2(0.f, 0.f);
     }
 
     if (active) {
@@ -554,7 +591,7 @@ __global__ void __launch_bounds__(32 * kBwdClRows, 2) bwd_cl_kernel(const BwdClA
             }
         }
         // x at the width-1 positions before t0 (x, initial_states or zero); g before t0 is never used
-        float xwin[W - 1][C], gwin[W - 1][C];
+        float2 xwin[W - 1][C / 2], gwin[W - 1][C / 2];
         int swin[W - 1];
         #pragma unroll
         for (int k = 0; k < W - 1; ++k) {
@@ -568,17 +605,22 @@ __global__ void __launch_bounds__(32 * kBwdClRows, 2) bwd_cl_kernel(const BwdClA
             } else if (a.init != nullptr) {
                 ld_cached_raw(r, reinterpret_cast<const T *>(a.init) + b * a.i_bs + (p + (W - 1)) * a.i_ls + (int64_t)col * C);
             }
-            unpack_raw<T>(r, xwin[k]);
+            unpack_pairs<T>(r, xwin[k]);
             #pragma unroll
-            for (int c = 0; c < C; ++c) gwin[k][c] = 0.f;
+            for (int c = 0; c < C / 2; ++c) gwin[k][c] = make_float2(0.f, 0.f);
         }
-        float wv[W][C], bv[C];
-        load_taps<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, 1.f);
+        float2 wv[W][C / 2], bv[C / 2];
+        load_taps_pairs<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, 1.f);
 
         const bool want_dinit = a.dinit != nullptr && t0 == 0;
         const T *dfin_base = a.dfin != nullptr ? reinterpret_cast<const T *>(a.dfin) + b * a.df_bs + (int64_t)col * C * a.df_cs : nullptr;
         T *dinit_base = want_dinit ? reinterpret_cast<T *>(a.dinit) + b * a.di_bs + (int64_t)col * C : nullptr;
 
+        // Positions are processed in blocks of U with the next block's loads in flight.  Blocks
+        // that lie fully inside [t0 + W-1, t1) take the unconditional path (every position both
+        // accumulates and stores dx), so the window rotation stays in renamed registers; the
+        // first block and the blocks around the chunk end take the flagged path.
+        const int n_in = t1 - t0;
         for (int base = 0; base < n_ext; base += U) {
             R xn[U], dn[U];
             int nsid[U];
@@ -593,18 +635,28 @@ __global__ void __launch_bounds__(32 * kBwdClRows, 2) bwd_cl_kernel(const BwdClA
                     if (kSeqIdx) nsid[u] = sp[U + u];
                 }
             }
-            #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int i = base + u;          // position t0 + i
-                if (i < n_ext) {
-                    const int q = t0 + i - (W - 1);   // dx position produced now
-                    const bool st_dx = i >= W - 1;     // q >= t0 (q < t1 always holds)
-                    const bool st_di = q < 0 && want_dinit;
-                    const T *df = (dfin_base != nullptr && q >= L - (W - 1)) ? dfin_base + (q - (L - (W - 1))) * a.df_ls : nullptr;
-                    T *di = st_di ? dinit_base + (q + (W - 1)) * a.di_ls : nullptr;
+            const bool steady = base >= W - 1 && base + U <= n_in && (a.dfin == nullptr || t0 + base + U <= L - (W - 1));
+            if (steady) {
+                #pragma unroll
+                for (int u = 0; u < U; ++u) {
                     bwd_cl_position<T, W, C, kSilu, kSeqIdx, kTanh>(
-                        xr[u], dr[u], sid[u], t0 + i < t1, st_dx, st_di, xwin, gwin, swin, wv, bv, dw, df, a.df_cs,
-                        optr + u * os, di);
+                        xr[u], dr[u], sid[u], true, true, false, xwin, gwin, swin, wv, bv, dw, nullptr, 0,
+                        optr + u * os, nullptr);
+                }
+            } else {
+                #pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int i = base + u;          // position t0 + i
+                    if (i < n_ext) {
+                        const int q = t0 + i - (W - 1);   // dx position produced now
+                        const bool st_dx = i >= W - 1;     // q >= t0 (q < t1 always holds)
+                        const bool st_di = q < 0 && want_dinit;
+                        const T *df = (dfin_base != nullptr && q >= L - (W - 1)) ? dfin_base + (q - (L - (W - 1))) * a.df_ls : nullptr;
+                        T *di = st_di ? dinit_base + (q + (W - 1)) * a.di_ls : nullptr;
+                        bwd_cl_position<T, W, C, kSilu, kSeqIdx, kTanh>(
+                            xr[u], dr[u], sid[u], i < n_in, st_dx, st_di, xwin, gwin, swin, wv, bv, dw, df, a.df_cs,
+                            optr + u * os, di);
+                    }
                 }
             }
             xptr += U * xs; dptr += U * ds; optr += U * os;
@@ -616,12 +668,14 @@ __global__ void __launch_bounds__(32 * kBwdClRows, 2) bwd_cl_kernel(const BwdClA
 
     // fixed-order sum over the CTA's token chunks: rows 1..7 park their sums, row 0 adds them
     // in ascending row order and writes the CTA's partial row
+    // channel c of the thread lives in pair c/2, component c%2
+    auto dwv = [&](int c, int k) -> float & { return (c & 1) ? dw[c >> 1][k].y : dw[c >> 1][k].x; };
     if (ty > 0) {
         float *r = s_red + ((ty - 1) * 32 + tx) * kAcc;
         #pragma unroll
         for (int c = 0; c < C; ++c) {
             #pragma unroll
-            for (int k = 0; k <= W; ++k) r[c * (W + 1) + k] = dw[c][k];
+            for (int k = 0; k <= W; ++k) r[c * (W + 1) + k] = dwv(c, k);
         }
     }
     __syncthreads();
@@ -632,14 +686,14 @@ __global__ void __launch_bounds__(32 * kBwdClRows, 2) bwd_cl_kernel(const BwdClA
             #pragma unroll
             for (int c = 0; c < C; ++c) {
                 #pragma unroll
-                for (int k = 0; k <= W; ++k) dw[c][k] += r[c * (W + 1) + k];
+                for (int k = 0; k <= W; ++k) dwv(c, k) += r[c * (W + 1) + k];
             }
         }
         float *p = a.ws + (((uint64_t)b * a.ngroups + grp) * (uint64_t)a.dim + (uint64_t)col * C) * (W + 1);
         #pragma unroll
         for (int c = 0; c < C; ++c) {
             #pragma unroll
-            for (int k = 0; k <= W; ++k) p[c * (W + 1) + k] = dw[c][k];
+            for (int k = 0; k <= W; ++k) p[c * (W + 1) + k] = dwv(c, k);
         }
     }
 }

@@ -157,6 +157,54 @@ template <> struct PackRaw<__half, 4> {
     }
 };
 
+// ---- packed fp32 pairs (sm_100 FFMA2 / FMUL2 / FADD2: two fp32 operations per issue slot) --
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 splat2(float v) { return make_float2(v, v); }
+
+// C elements of a raw vector as C/2 fp32 pairs (adjacent elements share a pair)
+template <typename T> __device__ __forceinline__ float2 unpack_pair(uint32_t r);
+template <> __device__ __forceinline__ float2 unpack_pair<__nv_bfloat16>(uint32_t r) {
+    return make_float2(__uint_as_float(r << 16), __uint_as_float(r & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 unpack_pair<__half>(uint32_t r) {
+    return __half22float2(*reinterpret_cast<const __half2 *>(&r));
+}
+template <typename T> __device__ __forceinline__ void unpack_pairs(const uint4 &v, float2 *f) {   // 8 x 16-bit
+    f[0] = unpack_pair<T>(v.x); f[1] = unpack_pair<T>(v.y); f[2] = unpack_pair<T>(v.z); f[3] = unpack_pair<T>(v.w);
+}
+template <> __device__ __forceinline__ void unpack_pairs<float>(const uint4 &v, float2 *f) {       // 4 x fp32
+    f[0] = make_float2(__uint_as_float(v.x), __uint_as_float(v.y));
+    f[1] = make_float2(__uint_as_float(v.z), __uint_as_float(v.w));
+}
+template <typename T> __device__ __forceinline__ void unpack_pairs(const uint2 &v, float2 *f) {   // 4 x 16-bit
+    f[0] = unpack_pair<T>(v.x); f[1] = unpack_pair<T>(v.y);
+}
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float2 v);
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float2 v) {
+    const __nv_bfloat162 t = __floats2bfloat162_rn(v.x, v.y);
+    return *reinterpret_cast<const uint32_t *>(&t);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float2 v) {
+    const __half2 t = __floats2half2_rn(v.x, v.y);
+    return *reinterpret_cast<const uint32_t *>(&t);
+}
+template <typename T, int C> struct PackPairs;   // C/2 pairs -> Raw<T, C>
+template <typename T> struct PackPairs<T, 8> {
+    static __device__ __forceinline__ uint4 run(const float2 *f) {
+        return make_uint4(pack_pair<T>(f[0]), pack_pair<T>(f[1]), pack_pair<T>(f[2]), pack_pair<T>(f[3]));
+    }
+};
+template <typename T> struct PackPairs<T, 4> {
+    static __device__ __forceinline__ uint2 run(const float2 *f) { return make_uint2(pack_pair<T>(f[0]), pack_pair<T>(f[1])); }
+};
+template <> struct PackPairs<float, 4> {
+    static __device__ __forceinline__ uint4 run(const float2 *f) {
+        return make_uint4(__float_as_uint(f[0].x), __float_as_uint(f[0].y), __float_as_uint(f[1].x), __float_as_uint(f[1].y));
+    }
+};
+
 // ---- activation ---------------------------------------------------------------------------
 // Two evaluations of SiLU.  "exact": sigmoid through ex2 + rcp (2 special-function ops per
 // element).  "tanh": sigmoid(y) = 0.5 * tanh(y/2) + 0.5 with the hardware tanh.approx (1
@@ -181,6 +229,19 @@ __device__ __forceinline__ float silu_half_arg(float h) { return fmaf(h, tanh_ap
 __device__ __forceinline__ float dsilu_half_arg(float h) {
     const float t = tanh_approx(h);
     return fmaf(0.5f, fmaf(h, fmaf(-t, t, 1.f), t), 0.5f);
+}
+// pair forms: kTanh takes h = y/2 (see above), otherwise y
+template <bool kTanh> __device__ __forceinline__ float2 silu_pair(float2 v) {
+    if (kTanh) return fma2(v, make_float2(tanh_approx(v.x), tanh_approx(v.y)), v);
+    return make_float2(silu_f(v.x), silu_f(v.y));
+}
+template <bool kTanh> __device__ __forceinline__ float2 dsilu_pair(float2 v) {
+    if (kTanh) {
+        const float2 t = make_float2(tanh_approx(v.x), tanh_approx(v.y));
+        const float2 q = fma2(make_float2(-t.x, -t.y), t, splat2(1.f));
+        return fma2(splat2(0.5f), fma2(v, q, t), splat2(0.5f));
+    }
+    return make_float2(dsilu_f(v.x), dsilu_f(v.y));
 }
 template <typename T> struct UseTanhSilu { static constexpr bool value = false; };
 template <> struct UseTanhSilu<__nv_bfloat16> { static constexpr bool value = true; };
@@ -275,6 +336,22 @@ __device__ __forceinline__ void load_taps(float (&wv)[W][C], float (&bv)[C], con
     }
     #pragma unroll
     for (int c = 0; c < C; ++c) bv[c] = bias != nullptr ? scale * load_w(bias, c0 + c, wtype) : 0.f;
+}
+
+// Same, as fp32 pairs of adjacent channels: wv2[k][c/2] = (w[c][k], w[c+1][k]).
+template <int W, int C>
+__device__ __forceinline__ void load_taps_pairs(float2 (&wv2)[W][C / 2], float2 (&bv2)[C / 2], const void *weight,
+                                                int64_t w_cs, int64_t w_ws, const void *bias, int wtype, int64_t c0,
+                                                float scale) {
+    float wv[W][C], bv[C];
+    load_taps<W, C>(wv, bv, weight, w_cs, w_ws, bias, wtype, c0, scale);
+    #pragma unroll
+    for (int k = 0; k < W; ++k) {
+        #pragma unroll
+        for (int c = 0; c < C / 2; ++c) wv2[k][c] = make_float2(wv[k][2 * c], wv[k][2 * c + 1]);
+    }
+    #pragma unroll
+    for (int c = 0; c < C / 2; ++c) bv2[c] = make_float2(bv[2 * c], bv[2 * c + 1]);
 }
 
 // Stage weight taps and bias of `nch` consecutive channels starting at c0 into shared memory

@@ -88,10 +88,10 @@ def test_bwd_workspace_and_rejects(lib):
     assert lib.cc1d_bwd(ctypes.byref(p), None) == 1
     p.width = 9
     assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(p)) == 0
-    # channel-last problem: partial rows per (batch, 8-chunk group)
+    # channel-last problem: partial rows per (batch, group of 4 chunks of 128 tokens)
     q = cabi.BwdParams(itype=cabi.BF16, wtype=cabi.BF16, width=4, silu=1, batch=1, dim=5376, seqlen=32768,
                        x=FAKE, x_batch_stride=5376 * 32768, x_c_stride=1, x_l_stride=5376)
-    assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(q)) == 32 * 5376 * 5 * 4
+    assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(q)) == 64 * 5376 * 5 * 4
 
 
 def test_varlen_rejects(lib):

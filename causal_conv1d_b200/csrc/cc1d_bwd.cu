@@ -93,6 +93,176 @@ __device__ __forceinline__ float grad_through_act(float dout, float y_or_h) {
     return dout * (kTanh ? dsilu_half_arg(y_or_h) : dsilu_f(y_or_h));
 }
 
+// Shared by both group bodies: g of the first width-1 elements AFTER the unit, recomputed from
+// the unit's last x vector (lane 31's xt) and one extra x/dout vector.  Only lane 31 reads it.
+template <typename T, int W, bool kSilu, bool kTanh>
+__device__ __forceinline__ void seed_right_halo(const uint4 &xlast, const uint4 &xedge, const uint4 &dedge,
+                                                const float (&wy)[W], float by, float (&ge)[W - 1]) {
+    constexpr int V = Elem<T>::kVec;
+    float xt[V], xn[V], dn[V];
+    unpack<T>(xlast, xt);
+    unpack<T>(xedge, xn);
+    unpack<T>(dedge, dn);
+    float xx[2 * (W - 1)];
+    #pragma unroll
+    for (int k = 0; k < W - 1; ++k) { xx[k] = xt[V - (W - 1) + k]; xx[W - 1 + k] = xn[k]; }
+    #pragma unroll
+    for (int i = 0; i < W - 1; ++i) {
+        float y = by;
+        #pragma unroll
+        for (int k = 0; k < W; ++k) y = fmaf(wy[k], xx[i + k], y);
+        ge[i] = grad_through_act<kSilu, kTanh>(dn[i], y);
+    }
+}
+
+// One group (kVecs vectors per lane), scalar fp32 arithmetic.  Used for fp32 I/O, where the
+// kernel is memory-bound and the smaller register footprint matters more than issue slots.
+template <typename T, int W, bool kSilu, bool kFull, int kVecs>
+__device__ __forceinline__ void bwd_cf_group_scalar(
+    const uint4 (&xraw)[kVecs], const uint4 (&draw)[kVecs], const uint4 &carry, bool seed, const uint4 &xedge,
+    const uint4 &dedge, const float (&wv)[W], const float (&wy)[W], float by, float (&ge)[W - 1], float (&dw)[W],
+    float &db, T *__restrict__ dxr, uint32_t e0, uint32_t L, int lane) {
+    constexpr int V = Elem<T>::kVec;
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    // pass 1: g, dweight, dbias (elements past the row end have dout == 0, so g == 0)
+    float gg[kVecs][V];
+    #pragma unroll
+    for (int j = 0; j < kVecs; ++j) {
+        const uint4 prev = prev_vector_tail<V, W>(xraw[j], j > 0 ? xraw[j - 1] : carry, lane);
+        float xx[W - 1 + V];
+        {
+            float pf[V];
+            unpack<T>(prev, pf);
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) xx[k] = pf[V - (W - 1) + k];
+        }
+        unpack<T>(xraw[j], xx + (W - 1));
+        unpack<T>(draw[j], gg[j]);
+        #pragma unroll
+        for (int i = 0; i < V; ++i) {
+            if (kSilu) {
+                float y = by;
+                #pragma unroll
+                for (int k = 0; k < W; ++k) y = fmaf(wy[k], xx[i + k], y);
+                gg[j][i] = grad_through_act<kSilu, kTanh>(gg[j][i], y);
+            }
+            db += gg[j][i];
+            #pragma unroll
+            for (int k = 0; k < W; ++k) dw[k] = fmaf(xx[i + k], gg[j][i], dw[k]);
+        }
+    }
+    if (seed) seed_right_halo<T, W, kSilu, kTanh>(xraw[kVecs - 1], xedge, dedge, wy, by, ge);   // warp-uniform
+
+    // pass 2: dx[t] = sum_k w[k] * g[t + (W-1-k)]
+    const int dst_lane = (lane + 1) & 31;
+    #pragma unroll
+    for (int j = 0; j < kVecs; ++j) {
+        float gx[V + W - 1];
+        #pragma unroll
+        for (int i = 0; i < V; ++i) gx[i] = gg[j][i];
+        #pragma unroll
+        for (int k = 0; k < W - 1; ++k) {
+            // lane l takes lane l+1's g[j][k]; lane 31 takes lane 0's g[j+1][k]
+            const float send = (lane == 0 && j + 1 < kVecs) ? gg[j + 1 < kVecs ? j + 1 : j][k] : gg[j][k];
+            float r = __shfl_sync(kFullMask, send, dst_lane);
+            if (j == kVecs - 1 && lane == 31) r = ge[k];
+            gx[V + k] = r;
+        }
+        const uint32_t e = e0 + j * 32 * V;
+        if (!kFull && e >= L) continue;
+        float o[V];
+        #pragma unroll
+        for (int i = 0; i < V; ++i) {
+            float acc = 0.f;
+            #pragma unroll
+            for (int k = 0; k < W; ++k) acc = fmaf(wv[k], gx[i + (W - 1 - k)], acc);
+            o[i] = acc;
+        }
+        store_row_vec<T, kFull>(dxr, e, L, o);
+    }
+    // the next (lower) group's right halo is this group's first elements, in lane 0
+    #pragma unroll
+    for (int k = 0; k < W - 1; ++k) ge[k] = __shfl_sync(kFullMask, gg[0][k], 0);
+}
+
+// Same group, arithmetic on fp32 pairs (FFMA2): vectors 2*jp and 2*jp+1 of a lane share a
+// pair (.x / .y), so every multiply-add covers two elements per issue slot.  Used for 16-bit
+// I/O, where the kernel is issue-bound.  dw2/db2 hold per-component partial sums.
+template <typename T, int W, bool kSilu, bool kFull, int kVecs>
+__device__ __forceinline__ void bwd_cf_group_pairs(
+    const uint4 (&xraw)[kVecs], const uint4 (&draw)[kVecs], const uint4 &carry, bool seed, const uint4 &xedge,
+    const uint4 &dedge, const float (&wv)[W], const float (&wy)[W], float by, float (&ge)[W - 1], float2 (&dw2)[W],
+    float2 &db2, T *__restrict__ dxr, uint32_t e0, uint32_t L, int lane) {
+    constexpr int V = Elem<T>::kVec;
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    float2 gg[kVecs / 2][V];
+    #pragma unroll
+    for (int jp = 0; jp < kVecs / 2; ++jp) {
+        const int j0 = 2 * jp, j1 = 2 * jp + 1;
+        const uint4 prev0 = prev_vector_tail<V, W>(xraw[j0], j0 > 0 ? xraw[j0 - 1] : carry, lane);
+        const uint4 prev1 = prev_vector_tail<V, W>(xraw[j1], xraw[j0], lane);
+        float2 xx[W - 1 + V];
+        {
+            float p0[V], p1[V], a0[V], a1[V], d0[V], d1[V];
+            unpack<T>(prev0, p0); unpack<T>(prev1, p1);
+            unpack<T>(xraw[j0], a0); unpack<T>(xraw[j1], a1);
+            unpack<T>(draw[j0], d0); unpack<T>(draw[j1], d1);
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) xx[k] = make_float2(p0[V - (W - 1) + k], p1[V - (W - 1) + k]);
+            #pragma unroll
+            for (int i = 0; i < V; ++i) { xx[W - 1 + i] = make_float2(a0[i], a1[i]); gg[jp][i] = make_float2(d0[i], d1[i]); }
+        }
+        #pragma unroll
+        for (int i = 0; i < V; ++i) {
+            if (kSilu) {
+                float2 y = splat2(by);
+                #pragma unroll
+                for (int k = 0; k < W; ++k) y = fma2(splat2(wy[k]), xx[i + k], y);
+                gg[jp][i] = mul2(gg[jp][i], dsilu_pair<kTanh>(y));
+            }
+            db2 = add2(db2, gg[jp][i]);
+            #pragma unroll
+            for (int k = 0; k < W; ++k) dw2[k] = fma2(xx[i + k], gg[jp][i], dw2[k]);
+        }
+    }
+    auto gval = [&](int j, int i) -> float { return (j & 1) ? gg[j >> 1][i].y : gg[j >> 1][i].x; };
+    if (seed) seed_right_halo<T, W, kSilu, kTanh>(xraw[kVecs - 1], xedge, dedge, wy, by, ge);   // warp-uniform
+
+    const int dst_lane = (lane + 1) & 31;
+    #pragma unroll
+    for (int jp = 0; jp < kVecs / 2; ++jp) {
+        float2 gx[V + W - 1];
+        #pragma unroll
+        for (int i = 0; i < V; ++i) gx[i] = gg[jp][i];
+        #pragma unroll
+        for (int k = 0; k < W - 1; ++k) {
+            // lane l takes lane l+1's g[j][k]; lane 31 takes lane 0's g[j+1][k]
+            float r[2];
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int j = 2 * jp + h;
+                const float send = (lane == 0 && j + 1 < kVecs) ? gval(j + 1 < kVecs ? j + 1 : j, k) : gval(j, k);
+                r[h] = __shfl_sync(kFullMask, send, dst_lane);
+                if (j == kVecs - 1 && lane == 31) r[h] = ge[k];
+            }
+            gx[V + k] = make_float2(r[0], r[1]);
+        }
+        float o0[V], o1[V];
+        #pragma unroll
+        for (int i = 0; i < V; ++i) {
+            float2 acc = make_float2(0.f, 0.f);
+            #pragma unroll
+            for (int k = 0; k < W; ++k) acc = fma2(splat2(wv[k]), gx[i + (W - 1 - k)], acc);
+            o0[i] = acc.x; o1[i] = acc.y;
+        }
+        const uint32_t ea = e0 + (2 * jp) * 32 * V, eb = ea + 32 * V;
+        if (kFull || ea < L) store_row_vec<T, kFull>(dxr, ea, L, o0);
+        if (kFull || eb < L) store_row_vec<T, kFull>(dxr, eb, L, o1);
+    }
+    #pragma unroll
+    for (int k = 0; k < W - 1; ++k) ge[k] = __shfl_sync(kFullMask, gg[0][k].x, 0);
+}
+
 // A warp unit is `gpu` consecutive groups of 32 * kVecs vectors of one row, walked BACK to
 // front: dx of a group needs g of the first width-1 elements of the group after it, which
 // the previous iteration left in lane 0's registers; only the unit's last group has to
@@ -103,6 +273,7 @@ template <typename T, int W, bool kSilu, bool kFull, int kVecs>
 __global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
     constexpr int V = Elem<T>::kVec;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    constexpr bool kPairs = sizeof(T) == 2;
     constexpr uint32_t kGroupElems = 32 * kVecs * V;
     const int lane = threadIdx.x & 31;
     const uint32_t warps_per_cta = blockDim.x >> 5;
@@ -130,8 +301,9 @@ __global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
         const float by = a.bias != nullptr ? pre * load_w(a.bias, c, a.wtype) : 0.f;
 
         float dw[W], db = 0.f;
+        float2 dw2[W], db2 = make_float2(0.f, 0.f);
         #pragma unroll
-        for (int k = 0; k < W; ++k) dw[k] = 0.f;
+        for (int k = 0; k < W; ++k) { dw[k] = 0.f; dw2[k] = make_float2(0.f, 0.f); }
         float ge[W - 1];   // g of the first width-1 elements after the current group
         #pragma unroll
         for (int k = 0; k < W - 1; ++k) ge[k] = 0.f;
@@ -154,84 +326,22 @@ __global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
                 if (kSilu) xedge = load_row_vec<T, false>(xr, en, L);
                 dedge = load_row_vec<T, false>(dr, en, L);
             }
-
-            // pass 1: g, dweight, dbias (elements past the row end have dout == 0, so g == 0)
-            float gg[kVecs][V];
-            #pragma unroll
-            for (int j = 0; j < kVecs; ++j) {
-                const uint4 prev = prev_vector_tail<V, W>(xraw[j], j > 0 ? xraw[j - 1] : carry, lane);
-                float xx[W - 1 + V];
-                {
-                    float pf[V];
-                    unpack<T>(prev, pf);
-                    #pragma unroll
-                    for (int k = 0; k < W - 1; ++k) xx[k] = pf[V - (W - 1) + k];
-                }
-                unpack<T>(xraw[j], xx + (W - 1));
-                unpack<T>(draw[j], gg[j]);
-                #pragma unroll
-                for (int i = 0; i < V; ++i) {
-                    if (kSilu) {
-                        float y = by;
-                        #pragma unroll
-                        for (int k = 0; k < W; ++k) y = fmaf(wy[k], xx[i + k], y);
-                        gg[j][i] = grad_through_act<kSilu, kTanh>(gg[j][i], y);
-                    }
-                    db += gg[j][i];
-                    #pragma unroll
-                    for (int k = 0; k < W; ++k) dw[k] = fmaf(xx[i + k], gg[j][i], dw[k]);
-                }
+            if constexpr (kPairs) {
+                bwd_cf_group_pairs<T, W, kSilu, kFull, kVecs>(xraw, draw, carry, seed, xedge, dedge, wv, wy, by, ge, dw2, db2,
+                                                              dxr, e0, L, lane);
+            } else {
+                bwd_cf_group_scalar<T, W, kSilu, kFull, kVecs>(xraw, draw, carry, seed, xedge, dedge, wv, wy, by, ge, dw, db,
+                                                               dxr, e0, L, lane);
             }
-            if (seed) {   // warp-uniform
-                float xt[V], xn[V], dn[V];
-                unpack<T>(xraw[kVecs - 1], xt);   // lane 31: the unit's last vector
-                unpack<T>(xedge, xn);
-                unpack<T>(dedge, dn);
-                float xx[2 * (W - 1)];
-                #pragma unroll
-                for (int k = 0; k < W - 1; ++k) { xx[k] = xt[V - (W - 1) + k]; xx[W - 1 + k] = xn[k]; }
-                #pragma unroll
-                for (int i = 0; i < W - 1; ++i) {
-                    float y = by;
-                    #pragma unroll
-                    for (int k = 0; k < W; ++k) y = fmaf(wy[k], xx[i + k], y);
-                    ge[i] = grad_through_act<kSilu, kTanh>(dn[i], y);   // valid in lane 31, the only reader
-                }
-            }
-
-            // pass 2: dx[t] = sum_k w[k] * g[t + (W-1-k)]
-            const int dst_lane = (lane + 1) & 31;
-            #pragma unroll
-            for (int j = 0; j < kVecs; ++j) {
-                float gx[V + W - 1];
-                #pragma unroll
-                for (int i = 0; i < V; ++i) gx[i] = gg[j][i];
-                #pragma unroll
-                for (int k = 0; k < W - 1; ++k) {
-                    // lane l takes lane l+1's g[j][k]; lane 31 takes lane 0's g[j+1][k]
-                    const float send = (lane == 0 && j + 1 < kVecs) ? gg[j + 1 < kVecs ? j + 1 : j][k] : gg[j][k];
-                    float r = __shfl_sync(kFullMask, send, dst_lane);
-                    if (j == kVecs - 1 && lane == 31) r = ge[k];
-                    gx[V + k] = r;
-                }
-                const uint32_t e = e0 + j * 32 * V;
-                if (!kFull && e >= L) continue;
-                float o[V];
-                #pragma unroll
-                for (int i = 0; i < V; ++i) {
-                    float acc = 0.f;
-                    #pragma unroll
-                    for (int k = 0; k < W; ++k) acc = fmaf(wv[k], gx[i + (W - 1 - k)], acc);
-                    o[i] = acc;
-                }
-                store_row_vec<T, kFull>(dxr, e, L, o);
-            }
-            // the next (lower) group's right halo is this group's first elements, in lane 0
-            #pragma unroll
-            for (int k = 0; k < W - 1; ++k) ge[k] = __shfl_sync(kFullMask, gg[0][k], 0);
         }
 
-        // warp tree (fixed order), one partial row per unit
+        // fold the pair components (16-bit path), then the warp tree (fixed order): one partial
+        // row per unit
+        if constexpr (kPairs) {
+            db = db2.x + db2.y;
+            #pragma unroll
+            for (int k = 0; k < W; ++k) dw[k] = dw2[k].x + dw2[k].y;
+        }
         #pragma unroll
         for (int off = 16; off > 0; off >>= 1) {
             #pragma unroll

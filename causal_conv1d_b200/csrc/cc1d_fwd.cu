@@ -213,35 +213,32 @@ constexpr int kClRows = 8;    // token chunks per CTA (threadIdx.y)
 constexpr int kClUnroll = 4;  // tokens per block: loads of one block are in flight while the previous computes
 
 // One token of the sliding window: out = act(bias + sum_k w[k] * window[k]), then shift.
-// All arithmetic is on fp32 pairs of adjacent channels (FFMA2: two FMAs per issue slot).
-template <typename T, int W, int C, bool kSilu, bool kMask, bool kTanh>
-__device__ __forceinline__ void fwd_cl_token_impl(const Raw<T, C> &raw, int sid, float2 (&win)[W - 1][C / 2],
-                                                  int (&sw)[W - 1], const float2 (&wv)[W][C / 2],
-                                                  const float2 (&bv)[C / 2], char *optr) {
-    constexpr int P = C / 2;
-    float2 cur[P], o[P];
-    unpack_pairs<T>(raw, cur);
+template <typename T, int W, int C, bool kSilu, bool kSeqIdx, bool kTanh>
+__device__ __forceinline__ void fwd_cl_token_impl(const Raw<T, C> &raw, int sid, float (&win)[W - 1][C], int (&sw)[W - 1],
+                                                  const float (&wv)[W][C], const float (&bv)[C], char *optr) {
+    float cur[C], o[C];
+    unpack_raw<T>(raw, cur);
     #pragma unroll
-    for (int c = 0; c < P; ++c) {
-        float2 acc = bv[c];
+    for (int c = 0; c < C; ++c) {
+        float acc = bv[c];
         #pragma unroll
         for (int k = 0; k < W - 1; ++k) {
-            if (!kMask || sw[k] == sid) acc = fma2(wv[k][c], win[k][c], acc);
+            if (!kSeqIdx || sw[k] == sid) acc = fmaf(wv[k][c], win[k][c], acc);
         }
-        acc = fma2(wv[W - 1][c], cur[c], acc);
-        if (kSilu) acc = silu_pair<kTanh>(acc);
+        acc = fmaf(wv[W - 1][c], cur[c], acc);
+        if (kSilu) acc = kTanh ? silu_half_arg(acc) : silu_f(acc);
         // a padded token (seq_idx < 0) outputs exactly zero: no bias, no activation
-        o[c] = (kMask && sid < 0) ? make_float2(0.f, 0.f) : acc;
+        o[c] = (kSeqIdx && sid < 0) ? 0.f : acc;
     }
-    st_stream_raw(optr, PackPairs<T, C>::run(o));
+    st_stream_raw(optr, PackRaw<T, C>::run(o));
     #pragma unroll
     for (int k = 0; k < W - 2; ++k) {
         #pragma unroll
-        for (int c = 0; c < P; ++c) win[k][c] = win[k + 1][c];
+        for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
         sw[k] = sw[k + 1];
     }
     #pragma unroll
-    for (int c = 0; c < P; ++c) win[W - 2][c] = cur[c];
+    for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
     sw[W - 2] = sid;
 }
 
@@ -249,8 +246,8 @@ __device__ __forceinline__ void fwd_cl_token_impl(const Raw<T, C> &raw, int sid,
 // boundaries are rare: when the window and the current token all carry one non-negative id,
 // no tap is masked and the unmasked code runs (a warp-uniform branch).
 template <typename T, int W, int C, bool kSilu, bool kSeqIdx, bool kTanh>
-__device__ __forceinline__ void fwd_cl_token(const Raw<T, C> &raw, int sid, float2 (&win)[W - 1][C / 2], int (&sw)[W - 1],
-                                             const float2 (&wv)[W][C / 2], const float2 (&bv)[C / 2], char *optr) {
+__device__ __forceinline__ void fwd_cl_token(const Raw<T, C> &raw, int sid, float (&win)[W - 1][C], int (&sw)[W - 1],
+                                             const float (&wv)[W][C], const float (&bv)[C], char *optr) {
     if (kSeqIdx) {
         bool same = sid >= 0;
         #pragma unroll
@@ -266,7 +263,6 @@ __device__ __forceinline__ void fwd_cl_token(const Raw<T, C> &raw, int sid, floa
 template <typename T, int W, bool kSilu, bool kSeqIdx>
 __global__ void __launch_bounds__(32 * kClRows, 2) fwd_cl_kernel(const FwdClArgs a) {
     constexpr int C = Elem<T>::kVec;  // channels per thread (one 16-byte vector)
-    constexpr int P = C / 2;
     constexpr int U = kClUnroll;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
     using R = Raw<T, C>;
@@ -301,7 +297,7 @@ __global__ void __launch_bounds__(32 * kClRows, 2) fwd_cl_kernel(const FwdClArgs
         }
     }
     // window = the width-1 tokens before t0 (x, or initial_states, or zero)
-    float2 win[W - 1][P];
+    float win[W - 1][C];
     int sw[W - 1];
     #pragma unroll
     for (int k = 0; k < W - 1; ++k) {
@@ -315,10 +311,10 @@ __global__ void __launch_bounds__(32 * kClRows, 2) fwd_cl_kernel(const FwdClArgs
         } else if (a.init != nullptr) {
             ld_cached_raw(r, reinterpret_cast<const T *>(a.init) + b * a.i_bs + (p + (W - 1)) * a.i_ls + (int64_t)col * C);
         }
-        unpack_pairs<T>(r, win[k]);
+        unpack_raw<T>(r, win[k]);
     }
-    float2 wv[W][P], bv[P];
-    load_taps_pairs<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, kTanh ? 0.5f : 1.f);
+    float wv[W][C], bv[C];
+    load_taps<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, kTanh ? 0.5f : 1.f);
 
     // full blocks: the next block's loads are issued before the current block is computed
     for (int blk = 0; blk < nfull; ++blk) {
@@ -352,7 +348,7 @@ __global__ void __launch_bounds__(32 * kClRows, 2) fwd_cl_kernel(const FwdClArgs
     if (a.fin != nullptr && t1 == L) {
         T *fp = reinterpret_cast<T *>(a.fin) + b * a.f_bs + (int64_t)col * C;
         #pragma unroll
-        for (int k = 0; k < W - 1; ++k) st_plain_raw(fp + k * a.f_ls, PackPairs<T, C>::run(win[k]));
+        for (int k = 0; k < W - 1; ++k) st_plain_raw(fp + k * a.f_ls, PackRaw<T, C>::run(win[k]));
     }
 }
 

@@ -125,6 +125,80 @@ __global__ void __launch_bounds__(128, 4) update_vec_kernel(const UpdArgs a) {
     }
 }
 
+// ---- channel-first state, single-token decode ------------------------------------------
+// conv_state contiguous as (entries, dim, S): the S state elements of a channel are adjacent,
+// so the C channels of a thread own C*S contiguous elements = S 16-byte vectors.  They are
+// shifted as raw bits in registers (bit-exact by construction) and written back whole.
+// Element (c, s) of the thread's block sits at flat index c*S + s.
+template <typename T> struct Bits;   // raw element <-> fp32, element extraction from 32-bit registers
+template <> struct Bits<float> {
+    static __device__ __forceinline__ uint32_t get(const uint32_t *r, int i) { return r[i]; }
+    static __device__ __forceinline__ void put(uint32_t *r, int i, uint32_t v) { r[i] = v; }
+    static __device__ __forceinline__ float to_f(uint32_t v) { return __uint_as_float(v); }
+};
+template <> struct Bits<__nv_bfloat16> {
+    static __device__ __forceinline__ uint32_t get(const uint32_t *r, int i) { return (i & 1) ? r[i >> 1] >> 16 : r[i >> 1] & 0xffffu; }
+    static __device__ __forceinline__ void put(uint32_t *r, int i, uint32_t v) { r[i >> 1] |= (i & 1) ? v << 16 : v; }
+    static __device__ __forceinline__ float to_f(uint32_t v) { return __uint_as_float(v << 16); }
+};
+template <> struct Bits<__half> {
+    static __device__ __forceinline__ uint32_t get(const uint32_t *r, int i) { return (i & 1) ? r[i >> 1] >> 16 : r[i >> 1] & 0xffffu; }
+    static __device__ __forceinline__ void put(uint32_t *r, int i, uint32_t v) { r[i >> 1] |= (i & 1) ? v << 16 : v; }
+    static __device__ __forceinline__ float to_f(uint32_t v) {
+        const unsigned short h = (unsigned short)v;
+        return __half2float(*reinterpret_cast<const __half *>(&h));
+    }
+};
+
+template <typename T, int W, bool kSilu, int S>
+__global__ void __launch_bounds__(128, 4) update_cfstate_kernel(const UpdArgs a) {
+    constexpr int C = Elem<T>::kVec;
+    constexpr int kRegs = S * 4;   // C * S elements in 32-bit registers
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    const uint64_t gid = (uint64_t)blockIdx.x * 128 + threadIdx.x;
+    const int32_t b = (int32_t)(gid / a.ncols);
+    const uint32_t col = (uint32_t)(gid - (uint64_t)b * a.ncols);
+    if (b >= a.batch) return;
+
+    const int32_t coord = a.indices != nullptr ? __ldg(a.indices + b) : b;
+    const T *__restrict__ xp = reinterpret_cast<const T *>(a.x) + (int64_t)b * a.x_bs + (int64_t)col * C;
+    T *__restrict__ op = reinterpret_cast<T *>(a.out) + (int64_t)b * a.o_bs + (int64_t)col * C;
+    const uint4 xraw = ld_stream(xp);
+    if (coord < 0) {   // padded entry: zero output, state untouched
+        st_stream(op, make_uint4(0, 0, 0, 0));
+        return;
+    }
+    uint4 *sp = reinterpret_cast<uint4 *>(reinterpret_cast<T *>(a.state) + coord * a.s_bs + (int64_t)col * C * S);
+    uint4 sv[S];
+    #pragma unroll
+    for (int i = 0; i < S; ++i) sv[i] = ld_cached(sp + i);
+    float wv[W][C], bv[C];
+    load_taps<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, kTanh ? 0.5f : 1.f);
+
+    uint32_t old[kRegs], nw[kRegs], xr[4] = {xraw.x, xraw.y, xraw.z, xraw.w};
+    #pragma unroll
+    for (int i = 0; i < S; ++i) { old[4 * i] = sv[i].x; old[4 * i + 1] = sv[i].y; old[4 * i + 2] = sv[i].z; old[4 * i + 3] = sv[i].w; }
+    #pragma unroll
+    for (int i = 0; i < kRegs; ++i) nw[i] = 0;
+    float o[C];
+    #pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const uint32_t xb = Bits<T>::get(xr, c);
+        float acc = bv[c];
+        #pragma unroll
+        for (int k = 0; k < W - 1; ++k) acc = fmaf(wv[k][c], Bits<T>::to_f(Bits<T>::get(old, c * S + S - (W - 1) + k)), acc);
+        acc = fmaf(wv[W - 1][c], Bits<T>::to_f(xb), acc);
+        o[c] = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
+        // new state of the channel: the old one shifted by one token, x appended
+        #pragma unroll
+        for (int t = 0; t < S - 1; ++t) Bits<T>::put(nw, c * S + t, Bits<T>::get(old, c * S + t + 1));
+        Bits<T>::put(nw, c * S + S - 1, xb);
+    }
+    st_stream(op, pack<T>(o));
+    #pragma unroll
+    for (int i = 0; i < S; ++i) sp[i] = make_uint4(nw[4 * i], nw[4 * i + 1], nw[4 * i + 2], nw[4 * i + 3]);
+}
+
 template <typename T, int W, bool kSilu, bool kCirc>
 __global__ void __launch_bounds__(128) update_generic_kernel(const UpdArgs a) {
     const int64_t c = (int64_t)(blockIdx.x % a.ncolblk) * 128 + threadIdx.x;
@@ -203,6 +277,26 @@ int launch_update(const cc1d_update_params &p, cudaStream_t stream) {
                         x_ls % C == 0 && o_ls % C == 0 && x_bs % C == 0 && o_bs % C == 0 && s_ls % C == 0 &&
                         p.conv_state_batch_stride % C == 0;
     const bool circ = p.cache_seqlens != nullptr;
+    // contiguous (entries, dim, S) state, one token, S == width-1 or width: whole-block register shift
+    const int64_t S = p.conv_state_len;
+    const bool cf_state_ok = !circ && p.seqlen == 1 && p.dim % C == 0 && (p.dim == 1 || (p.x_c_stride == 1 && p.out_c_stride == 1)) &&
+                             p.conv_state_l_stride == 1 && p.conv_state_c_stride == S && (S == p.width - 1 || S == p.width) &&
+                             S >= 2 && is_aligned16(p.x) && is_aligned16(p.out) && is_aligned16(p.conv_state) &&
+                             x_bs % C == 0 && o_bs % C == 0 && (p.conv_state_batch_stride * elem_size(p.itype)) % 16 == 0;
+    if (cf_state_ok) {
+        a.ncols = (uint32_t)(p.dim / C);
+        a.ncolblk = 0;
+        const uint64_t ctas = ((uint64_t)a.ncols * (uint64_t)p.batch + 127) / 128;
+        if (ctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
+        const bool s_is_w = S == p.width;
+        CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
+            CC1D_DISPATCH_BOOL(s_is_w, kSW, {
+                if constexpr (W - 1 + (kSW ? 1 : 0) >= 2) {
+                    update_cfstate_kernel<T, W, kSilu, W - 1 + (kSW ? 1 : 0)><<<(unsigned)ctas, 128, 0, stream>>>(a);
+                }
+            }););););
+        return check_launch();
+    }
     if (vec_ok) {
         a.ncols = (uint32_t)(p.dim / C);
         a.ncolblk = 0;

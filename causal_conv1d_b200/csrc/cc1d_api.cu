@@ -102,6 +102,7 @@ const char *cc1d_status_str(int status) {
         case CC1D_ERR_ALIGN: return "pointer or stride not aligned for the required access width";
         case CC1D_ERR_TOO_LARGE: return "problem size exceeds an internal index range";
         case CC1D_ERR_LAUNCH: return "CUDA kernel launch failed";
+        case CC1D_ERR_SCRATCH_LIMIT: return "problem needs more scratch than cc1d_bwd_noalloc has built in (CC1D_NOALLOC_SCRATCH_BYTES); use cc1d_bwd with a caller workspace";
         default: return "unknown cc1d status";
     }
 }
@@ -167,6 +168,50 @@ int cc1d_bwd(const cc1d_bwd_params *p, cc1d_stream_t stream) {
     }
     if (q.width == 2) q.initial_states_l_stride = q.dfinal_states_l_stride = q.dinitial_states_l_stride = 0;
     return cl ? launch_bwd_channel_last(q, s) : launch_bwd_channel_first(q, s);
+}
+
+}  // extern "C"
+
+// Scratch of cc1d_bwd_noalloc: part of the library image, so no allocation is ever needed.
+// In host code the name below is only a host-side stand-in for the symbol, not a device
+// address; the address a kernel can use comes from cudaGetSymbolAddress, looked up once per
+// device (with that device current) and cached.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[CC1D_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_scratch_mu;
+void *g_scratch_ptr[64] = {nullptr};
+
+// Device address of g_noalloc_scratch on the current device, or nullptr on failure.
+void *noalloc_scratch_address() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    if (g_scratch_ptr[dev] == nullptr) {
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        g_scratch_ptr[dev] = ptr;
+    }
+    return g_scratch_ptr[dev];
+}
+}  // namespace
+
+extern "C" {
+
+int cc1d_bwd_noalloc(const cc1d_bwd_params *p, cc1d_stream_t stream) {
+    bool cl = false;
+    const int rc = check_bwd(p, &cl);
+    if (rc != CC1D_OK) return rc;
+    if (cc1d_bwd_workspace_bytes(p) > (size_t)CC1D_NOALLOC_SCRATCH_BYTES) return CC1D_ERR_SCRATCH_LIMIT;
+    void *scratch = noalloc_scratch_address();   // first call per device: one symbol lookup
+    if (scratch == nullptr) return CC1D_ERR_LAUNCH;
+    cc1d_bwd_params q = *p;
+    q.workspace = scratch;
+    q.workspace_bytes = CC1D_NOALLOC_SCRATCH_BYTES;
+    return cc1d_bwd(&q, stream);
 }
 
 int cc1d_update(const cc1d_update_params *p, cc1d_stream_t stream) {

@@ -43,7 +43,8 @@ typedef enum cc1d_status {
     CC1D_ERR_WORKSPACE = 11,    /* workspace missing or too small                    */
     CC1D_ERR_ALIGN = 12,        /* pointer not aligned for its element type          */
     CC1D_ERR_TOO_LARGE = 13,    /* problem exceeds an internal index range           */
-    CC1D_ERR_LAUNCH = 14        /* the CUDA launch itself failed (see cudaGetLastError) */
+    CC1D_ERR_LAUNCH = 14,       /* the CUDA launch itself failed (see cudaGetLastError) */
+    CC1D_ERR_SCRATCH_LIMIT = 15 /* problem needs more than the built-in scratch of cc1d_bwd_noalloc */
 } cc1d_status;
 
 /* ---------------------------------------------------------------------------
@@ -131,6 +132,35 @@ typedef struct cc1d_bwd_params {
  * Returns 0 on invalid parameters. */
 size_t cc1d_bwd_workspace_bytes(const cc1d_bwd_params *p);
 int cc1d_bwd(const cc1d_bwd_params *p, cc1d_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * Backward for callers that cannot allocate.  No counterpart in the reference
+ * (its host code always allocates through PyTorch).
+ *
+ * Some hosts of this library have no way to hand cc1d_bwd a workspace: code that
+ * runs where device allocation is forbidden or would stall (inside a region that
+ * must not touch the allocator, a plugin whose host owns all device memory, a
+ * latency-critical loop that may not call cudaMalloc).  For them this entry point
+ * does the same work as cc1d_bwd with the partial-sum scratch taken from a fixed
+ * buffer of CC1D_NOALLOC_SCRATCH_BYTES that lives inside the library image: every
+ * GPU that loads libcc1d.so holds that much device memory until the process
+ * exits.  p->workspace and p->workspace_bytes are ignored; x, dout, dx, dweight,
+ * dbias and the state tensors are still the caller's.
+ *
+ *  - A problem whose cc1d_bwd_workspace_bytes() exceeds the buffer is rejected
+ *    with CC1D_ERR_SCRATCH_LIMIT and nothing is launched.
+ *  - It calls no cudaMalloc / cudaFree / allocating library routine.  The first
+ *    call on each device looks up the buffer's device address (one
+ *    cudaGetSymbolAddress, with that device current); make that first call
+ *    outside any stream capture.
+ *  - All calls share the one buffer and it keeps the previous call's contents.
+ *    Nothing in it has to start at zero (every slot that is read was written
+ *    earlier in the same call), but two calls that overlap on the GPU (different
+ *    streams, or different host threads without ordering) race on it: keep calls
+ *    on one device ordered.
+ * ------------------------------------------------------------------------- */
+#define CC1D_NOALLOC_SCRATCH_BYTES (8u * 1024u * 1024u)
+int cc1d_bwd_noalloc(const cc1d_bwd_params *p, cc1d_stream_t stream);
 
 /* ---------------------------------------------------------------------------
  * Decode-step state update.  Replaces causal_conv1d_update()

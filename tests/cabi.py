@@ -61,7 +61,8 @@ def load():
     lib.cc1d_status_str.argtypes = [ctypes.c_int]
     lib.cc1d_bwd_workspace_bytes.restype = sz
     lib.cc1d_bwd_workspace_bytes.argtypes = [ctypes.POINTER(BwdParams)]
-    for name, st in (("cc1d_fwd", FwdParams), ("cc1d_bwd", BwdParams), ("cc1d_update", UpdateParams),
+    for name, st in (("cc1d_fwd", FwdParams), ("cc1d_bwd", BwdParams), ("cc1d_bwd_noalloc", BwdParams),
+                     ("cc1d_update", UpdateParams),
                      ("cc1d_varlen_states", VarlenParams)):
         getattr(lib, name).argtypes = [ctypes.POINTER(st), vp]
         getattr(lib, name).restype = ctypes.c_int

@@ -1,0 +1,98 @@
+"""cc1d_bwd_noalloc: the backward for hosts that cannot allocate device memory.
+
+Some callers of libcc1d.so own no allocator they may call at launch time (a plugin whose
+host manages all device memory, a latency-critical loop that must never reach cudaMalloc).
+cc1d_bwd needs a caller-provided workspace; cc1d_bwd_noalloc does the same work with the
+scratch taken from a fixed buffer inside the library (CC1D_NOALLOC_SCRATCH_BYTES = 8 MiB),
+so the caller passes inputs and outputs only.
+
+This test drives both entry points through the C ABI on the same inputs, twice in a row
+(the shared buffer keeps the first call's contents; the second call must not be disturbed
+by them), and checks that the results agree.  It lives in a file that sorts last so that a
+run stopping at the first failure has already executed every other test.
+"""
+import ctypes
+
+import pytest
+import torch
+
+import cabi
+from conftest import TOL, assert_close, assert_close_sum
+
+pytestmark = pytest.mark.gpu
+
+SCRATCH_BYTES = 8 * 1024 * 1024
+CODE = {torch.float32: cabi.F32, torch.bfloat16: cabi.BF16}
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _params(x, w, b, dout, dx, dw, db, channel_last):
+    B, D, L = x.shape
+    W = w.shape[1]
+    s = lambda t: dict(zip(("batch", "c", "l"), t.stride()))
+    p = cabi.BwdParams(itype=CODE[x.dtype], wtype=cabi.F32, width=W, silu=1, batch=B, dim=D, seqlen=L,
+                       x=x.data_ptr(), weight=w.data_ptr(), weight_c_stride=W, weight_width_stride=1,
+                       bias=b.data_ptr(), dout=dout.data_ptr(), dx=dx.data_ptr(),
+                       dweight=dw.data_ptr(), dweight_c_stride=W, dweight_width_stride=1, dbias=db.data_ptr(),
+                       accumulate=0)
+    for name, t in (("x", x), ("dout", dout), ("dx", dx)):
+        for k, v in s(t).items():
+            setattr(p, f"{name}_{k}_stride", v)
+    return p
+
+
+def _inputs(seed, itype, channel_last, B=3, D=72, L=333, W=4):
+    torch.manual_seed(seed)
+    mk = (lambda: torch.randn(B, L, D, device="cuda", dtype=itype).transpose(1, 2)) if channel_last else \
+         (lambda: torch.randn(B, D, L, device="cuda", dtype=itype))
+    x, dout = mk(), mk()
+    w = torch.randn(D, W, device="cuda")
+    b = torch.randn(D, device="cuda")
+    return x, w, b, dout
+
+
+@pytest.mark.parametrize("channel_last", [False, True])
+@pytest.mark.parametrize("itype", [torch.float32, torch.bfloat16])
+def test_noalloc_matches_workspace_entry_point(itype, channel_last):
+    lib = cabi.load()
+    for call, seed in enumerate((11, 12)):          # two calls in a row on the shared scratch
+        x, w, b, dout = _inputs(seed, itype, channel_last)
+        ref = [torch.empty_like(x), torch.empty(w.shape, device="cuda"), torch.empty(b.shape, device="cuda")]
+        got = [torch.empty_like(x), torch.empty(w.shape, device="cuda"), torch.empty(b.shape, device="cuda")]
+        # existing entry point: caller workspace
+        p = _params(x, w, b, dout, *ref, channel_last)
+        n = lib.cc1d_bwd_workspace_bytes(ctypes.byref(p))
+        assert 0 < n <= SCRATCH_BYTES
+        ws = torch.empty(n, dtype=torch.uint8, device="cuda")
+        p.workspace, p.workspace_bytes = ws.data_ptr(), n
+        assert lib.cc1d_bwd(ctypes.byref(p), _stream()) == 0
+        # new entry point: no workspace handed over at all
+        q = _params(x, w, b, dout, *got, channel_last)
+        q.workspace, q.workspace_bytes = None, 0
+        assert lib.cc1d_bwd_noalloc(ctypes.byref(q), _stream()) == 0, f"call {call}"
+        torch.cuda.synchronize()
+        assert_close(got[0], ref[0], TOL[itype], f"dx (call {call})")
+        assert_close_sum(got[1], ref[1], 2e-5, f"dweight (call {call})")
+        assert_close_sum(got[2], ref[2], 2e-5, f"dbias (call {call})")
+        # same kernels, same fixed summation order: the bits agree as well
+        assert all(torch.equal(a, c) for a, c in zip(got, ref))
+
+
+def test_noalloc_rejects_problems_beyond_its_scratch():
+    lib = cabi.load()
+    # (32, 8192, 8192) bf16 channel-first needs 42 MB of partial rows: more than the built-in 8 MiB.
+    # Validation happens before anything is launched, so the pointers are never dereferenced.
+    fake = 0x1000
+    p = cabi.BwdParams(itype=cabi.BF16, wtype=cabi.F32, width=4, silu=1, batch=32, dim=8192, seqlen=8192,
+                       x=fake, x_batch_stride=8192 * 8192, x_c_stride=8192, x_l_stride=1,
+                       weight=fake, weight_c_stride=4, weight_width_stride=1,
+                       dout=fake, dout_batch_stride=8192 * 8192, dout_c_stride=8192, dout_l_stride=1,
+                       dx=fake, dx_batch_stride=8192 * 8192, dx_c_stride=8192, dx_l_stride=1,
+                       dweight=fake, dweight_c_stride=4, dweight_width_stride=1)
+    assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(p)) > SCRATCH_BYTES
+    rc = lib.cc1d_bwd_noalloc(ctypes.byref(p), None)
+    assert rc == 15
+    assert b"cc1d_bwd_noalloc" in lib.cc1d_status_str(rc)

@@ -269,8 +269,11 @@ __device__ __forceinline__ void bwd_cf_group_pairs(
 // recompute them from one extra x/dout vector.  dweight/dbias accumulate over the whole
 // unit: one partial row per unit.
 // kFull: seqlen is a multiple of the vector width and every group has all 32 * kVecs vectors.
+#ifndef CC1D_BWD_CF_MINBLK
+#define CC1D_BWD_CF_MINBLK 1
+#endif
 template <typename T, int W, bool kSilu, bool kFull, int kVecs>
-__global__ void __launch_bounds__(256) bwd_cf_vec_kernel(const BwdCfArgs a) {
+__global__ void __launch_bounds__(256, CC1D_BWD_CF_MINBLK) bwd_cf_vec_kernel(const BwdCfArgs a) {
     constexpr int V = Elem<T>::kVec;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
     constexpr bool kPairs = sizeof(T) == 2;

@@ -8,6 +8,7 @@
 
 #include "cc1d.h"
 #include "cc1d_kernels.h"
+#include "cc1d_tma.cuh"
 
 namespace cc1d {
 
@@ -37,6 +38,46 @@ int resident_ctas_per_sm(const void *kernel, int threads, size_t dyn_smem) {
     }
     cache[key] = n;
     return n;
+}
+
+bool make_channel_last_tensor_map(CUtensorMap *map, int dtype, const void *base, int64_t dim, int64_t seqlen,
+                                  int64_t batch, int64_t l_stride, int64_t batch_stride, int row_bytes) {
+    using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    static bool looked_up = false;
+    {
+        static std::mutex mu;
+        std::lock_guard<std::mutex> lock(mu);
+        if (!looked_up) {
+            looked_up = true;
+            void *fn = nullptr;
+            cudaDriverEntryPointQueryResult qres;
+            if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+                qres == cudaDriverEntryPointSuccess) {
+                encode = reinterpret_cast<EncodeFn>(fn);
+            } else {
+                (void)cudaGetLastError();
+            }
+        }
+    }
+    if (encode == nullptr) return false;
+    const int es = elem_size(dtype);
+    const CUtensorMapDataType dt = dtype == CC1D_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : dtype == CC1D_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    if (batch < 1) batch = 1;
+    if (batch == 1 || batch_stride <= 0) batch_stride = l_stride * seqlen;   // unused extent: any legal stride
+    const cuuint64_t dims[3] = {(cuuint64_t)dim, (cuuint64_t)seqlen, (cuuint64_t)batch};
+    const cuuint64_t strides[2] = {(cuuint64_t)l_stride * es, (cuuint64_t)batch_stride * es};   // bytes, dims 1..2
+    const cuuint32_t box[3] = {(cuuint32_t)(row_bytes / es), (cuuint32_t)kTmaRows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    if (strides[0] % 16 || strides[1] % 16 || strides[0] >= (1ull << 40) || strides[1] >= (1ull << 40)) return false;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
+    const CUresult rc = encode(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
 }
 
 namespace {

@@ -11,6 +11,7 @@
 // the deterministic-mode workspaces + ATen sums of csrc/causal_conv1d.cpp:388-462.
 #include "cc1d_common.cuh"
 #include "cc1d_kernels.h"
+#include "cc1d_tma.cuh"
 
 namespace cc1d {
 
@@ -270,7 +271,7 @@ __device__ __forceinline__ void bwd_cf_group_pairs(
 // unit: one partial row per unit.
 // kFull: seqlen is a multiple of the vector width and every group has all 32 * kVecs vectors.
 #ifndef CC1D_BWD_CF_MINBLK
-#define CC1D_BWD_CF_MINBLK 1
+#define CC1D_BWD_CF_MINBLK 3
 #endif
 template <typename T, int W, bool kSilu, bool kFull, int kVecs>
 __global__ void __launch_bounds__(256, CC1D_BWD_CF_MINBLK) bwd_cf_vec_kernel(const BwdCfArgs a) {
@@ -811,6 +812,233 @@ __global__ void __launch_bounds__(32 * kBwdClRows, CC1D_BWD_CL_MINBLK) bwd_cl_ke
     }
 }
 
+// ---- TMA variant ----------------------------------------------------------------------------
+// Same arithmetic and the same partial-row layout as bwd_cl_kernel, but x and dout reach the
+// warp through the TMA unit: each warp is an independent pipeline over its own ring of
+// kBwdTmaStages stages, a stage = one x box + one dout box of [kTmaRows positions x 32 lanes x
+// C channels], one mbarrier per stage.  Rows past seqlen arrive as zeros, which is exactly what
+// the right halo needs (x = 0, dout = 0 beyond the sequence).
+#ifndef CC1D_BWD_CL_TMA
+#define CC1D_BWD_CL_TMA 1
+#endif
+#ifndef CC1D_BWD_TMA_STAGES
+#define CC1D_BWD_TMA_STAGES 3
+#endif
+constexpr int kBwdTmaStages = CC1D_BWD_TMA_STAGES;
+
+template <typename T> struct BwdTma {
+    static constexpr int kRowBytes = 32 * kBwdClC * (int)sizeof(T);      // one token of a warp's strip
+    static constexpr int kBoxBytes = kTmaRows * kRowBytes;
+    static constexpr int kStageBytes = 2 * kBoxBytes;                     // x box, then dout box
+    static constexpr size_t kSmem = (size_t)kBwdClRows * kBwdTmaStages * kStageBytes + (size_t)kBwdClRows * kBwdTmaStages * 8;
+};
+
+template <typename R> __device__ __forceinline__ R lds_raw(uint32_t addr);
+template <> __device__ __forceinline__ uint4 lds_raw<uint4>(uint32_t addr) { return lds128(addr); }
+template <> __device__ __forceinline__ uint2 lds_raw<uint2>(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+template <typename T, int W, bool kSilu, bool kSeqIdx>
+__global__ void __launch_bounds__(32 * kBwdClRows, CC1D_BWD_CL_MINBLK)
+bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap dmap) {
+    constexpr int C = kBwdClC;
+    constexpr int kAcc = (W + 1) * C;
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    constexpr int kRowBytes = BwdTma<T>::kRowBytes, kBoxBytes = BwdTma<T>::kBoxBytes, kStageBytes = BwdTma<T>::kStageBytes;
+    using R = Raw<T, C>;
+    __shared__ __align__(16) float s_red[(kBwdClRows - 1) * 32 * kAcc];
+    extern __shared__ __align__(1024) unsigned char smem[];
+
+    const uint32_t cb = blockIdx.x % a.ncolblk;
+    const uint32_t rest = blockIdx.x / a.ncolblk;
+    const uint32_t grp = rest % a.ngroups;
+    const uint32_t b = rest / a.ngroups;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const uint32_t col = cb * 32 + tx;
+    const bool lane_ok = col < a.ncols;
+    const int L = (int)a.seqlen;
+    const int t0 = (int)((grp * kBwdClRows + ty) * (uint32_t)a.tpt);
+    const bool active = t0 < L;                      // warp-uniform
+
+    float2 dw[C / 2][W + 1];   // pairs of adjacent channels; [.][W] is dbias
+    #pragma unroll
+    for (int c = 0; c < C / 2; ++c) {
+        #pragma unroll
+        for (int k = 0; k <= W; ++k) dw[c][k] = make_float2(0.f, 0.f);
+    }
+
+    if (active) {
+        const int t1 = t0 + a.tpt < L ? t0 + a.tpt : L;
+        const int n_in = t1 - t0;
+        const int n_ext = n_in + (W - 1);                 // positions to process
+        const int nst = (n_ext + kTmaRows - 1) / kTmaRows;
+        const uint32_t ring = smem_u32(smem) + ty * (kBwdTmaStages * kStageBytes);
+        const uint32_t bars = smem_u32(smem) + kBwdClRows * kBwdTmaStages * kStageBytes + ty * (kBwdTmaStages * 8);
+        const int c0 = (int)(cb * 32 * C);
+        if (tx == 0) {
+            tma_prefetch_desc(&xmap);
+            tma_prefetch_desc(&dmap);
+            #pragma unroll
+            for (int s = 0; s < kBwdTmaStages; ++s) mbar_init(bars + 8 * s, 1);
+            fence_mbar_init();
+            #pragma unroll
+            for (int s = 0; s < kBwdTmaStages; ++s) {
+                if (s < nst) {
+                    mbar_expect_tx(bars + 8 * s, kStageBytes);
+                    tma_load_3d(ring + s * kStageBytes, &xmap, c0, t0 + s * kTmaRows, (int)b, bars + 8 * s);
+                    tma_load_3d(ring + s * kStageBytes + kBoxBytes, &dmap, c0, t0 + s * kTmaRows, (int)b, bars + 8 * s);
+                }
+            }
+        }
+        __syncwarp();
+
+        const int64_t xs = a.x_ls * (int64_t)sizeof(T), os = a.o_ls * (int64_t)sizeof(T);
+        const int64_t cofs = (int64_t)col * C * (int64_t)sizeof(T);
+        const char *xptr = reinterpret_cast<const char *>(a.x) + b * a.x_bs * (int64_t)sizeof(T) + cofs + t0 * xs;
+        char *optr = reinterpret_cast<char *>(a.dx) + b * a.o_bs * (int64_t)sizeof(T) + cofs + (t0 - (W - 1)) * os;
+        const int32_t *__restrict__ sp = kSeqIdx ? a.seq_idx + (int64_t)b * L + t0 : nullptr;
+        const int n_ld = (t1 + (W - 1) < L ? t1 + (W - 1) : L) - t0;   // positions that exist
+
+        // x at the width-1 positions before t0 (x, initial_states or zero); g before t0 is never used
+        float2 xwin[W - 1][C / 2], gwin[W - 1][C / 2];
+        int swin[W - 1];
+        #pragma unroll
+        for (int k = 0; k < W - 1; ++k) {
+            const int p = t0 - (W - 1) + k;
+            R r;
+            zero_raw(r);
+            swin[k] = -1;
+            if (p >= 0) {
+                if (lane_ok) ld_cached_raw(r, xptr - (W - 1 - k) * xs);
+                if (kSeqIdx) swin[k] = sp[k - (W - 1)];
+            } else if (a.init != nullptr && lane_ok) {
+                ld_cached_raw(r, reinterpret_cast<const T *>(a.init) + b * a.i_bs + (p + (W - 1)) * a.i_ls + (int64_t)col * C);
+            }
+            unpack_pairs<T>(r, xwin[k]);
+            #pragma unroll
+            for (int c = 0; c < C / 2; ++c) gwin[k][c] = make_float2(0.f, 0.f);
+        }
+        float2 wv[W][C / 2], bv[C / 2];
+        if (lane_ok) {
+            load_taps_pairs<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, 1.f);
+        } else {
+            #pragma unroll
+            for (int c = 0; c < C / 2; ++c) {
+                bv[c] = make_float2(0.f, 0.f);
+                #pragma unroll
+                for (int k = 0; k < W; ++k) wv[k][c] = make_float2(0.f, 0.f);
+            }
+        }
+        const bool want_dinit = a.dinit != nullptr && t0 == 0 && lane_ok;
+        const T *dfin_base = (a.dfin != nullptr && lane_ok) ? reinterpret_cast<const T *>(a.dfin) + b * a.df_bs + (int64_t)col * C * a.df_cs : nullptr;
+        T *dinit_base = want_dinit ? reinterpret_cast<T *>(a.dinit) + b * a.di_bs + (int64_t)col * C : nullptr;
+
+        int nsid[kTmaRows];   // sequence ids one stage ahead; -2 beyond the sequence (matches nothing)
+        #pragma unroll
+        for (int r = 0; r < kTmaRows; ++r) nsid[r] = (kSeqIdx && r < n_ld) ? sp[r] : -2;
+
+        for (int st = 0; st < nst; ++st) {
+            const int s = st % kBwdTmaStages;
+            const int base = st * kTmaRows;
+            int sid[kTmaRows];
+            #pragma unroll
+            for (int r = 0; r < kTmaRows; ++r) {
+                sid[r] = nsid[r];
+                nsid[r] = (kSeqIdx && base + kTmaRows + r < n_ld) ? sp[kTmaRows + r] : -2;
+            }
+            if (!mbar_wait(bars + 8 * s, (uint32_t)(st / kBwdTmaStages) & 1u)) {
+                g_tma_wait_expired = 1;     // never expected; stop consuming, still join the block reduction
+                break;
+            }
+            const uint32_t xsrc = ring + s * kStageBytes + tx * (C * (int)sizeof(T));
+            const uint32_t dsrc = xsrc + kBoxBytes;
+            const bool steady = base >= W - 1 && base + kTmaRows <= n_in &&
+                                (a.dfin == nullptr || t0 + base + kTmaRows <= L - (W - 1));
+            // one test per stage instead of one per position: when the window and all positions of
+            // the stage carry the same non-negative sequence id, nothing is masked (warp-uniform)
+            bool plain = steady;
+            if (kSeqIdx) {
+                plain = plain && sid[0] >= 0;
+                #pragma unroll
+                for (int k = 0; k < W - 1; ++k) plain = plain && swin[k] == sid[0];
+                #pragma unroll
+                for (int r = 1; r < kTmaRows; ++r) plain = plain && sid[r] == sid[0];
+            }
+            if (plain) {
+                #pragma unroll
+                for (int r = 0; r < kTmaRows; ++r) {
+                    const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = lds_raw<R>(dsrc + r * kRowBytes);
+                    bwd_cl_position_impl<T, W, C, kSilu, false, kTanh>(
+                        xr, dr, sid[r], true, lane_ok, false, xwin, gwin, swin, wv, bv, dw, nullptr, 0, optr + r * os, nullptr);
+                }
+            } else if (steady) {
+                #pragma unroll
+                for (int r = 0; r < kTmaRows; ++r) {
+                    const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = lds_raw<R>(dsrc + r * kRowBytes);
+                    bwd_cl_position_impl<T, W, C, kSilu, kSeqIdx, kTanh>(
+                        xr, dr, sid[r], true, lane_ok, false, xwin, gwin, swin, wv, bv, dw, nullptr, 0, optr + r * os, nullptr);
+                }
+            } else {
+                #pragma unroll
+                for (int r = 0; r < kTmaRows; ++r) {
+                    const int i = base + r;               // position t0 + i
+                    if (i < n_ext) {
+                        const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = lds_raw<R>(dsrc + r * kRowBytes);
+                        const int q = t0 + i - (W - 1);   // dx position produced now
+                        const bool st_dx = i >= W - 1 && lane_ok;
+                        const bool st_di = q < 0 && want_dinit;
+                        const T *df = (dfin_base != nullptr && q >= L - (W - 1)) ? dfin_base + (q - (L - (W - 1))) * a.df_ls : nullptr;
+                        T *di = st_di ? dinit_base + (q + (W - 1)) * a.di_ls : nullptr;
+                        bwd_cl_position<T, W, C, kSilu, kSeqIdx, kTanh>(
+                            xr, dr, sid[r], i < n_in, st_dx, st_di, xwin, gwin, swin, wv, bv, dw, df, a.df_cs, optr + r * os, di);
+                    }
+                }
+            }
+            optr += kTmaRows * os;
+            if (kSeqIdx) sp += kTmaRows;
+            __syncwarp();                                   // every lane has consumed the stage
+            if (tx == 0 && st + kBwdTmaStages < nst) {      // refill it
+                fence_proxy_async_smem();
+                mbar_expect_tx(bars + 8 * s, kStageBytes);
+                tma_load_3d(ring + s * kStageBytes, &xmap, c0, t0 + (st + kBwdTmaStages) * kTmaRows, (int)b, bars + 8 * s);
+                tma_load_3d(ring + s * kStageBytes + kBoxBytes, &dmap, c0, t0 + (st + kBwdTmaStages) * kTmaRows, (int)b, bars + 8 * s);
+            }
+        }
+    }
+
+    // fixed-order sum over the CTA's token chunks (see bwd_cl_kernel)
+    auto dwv = [&](int c, int k) -> float & { return (c & 1) ? dw[c >> 1][k].y : dw[c >> 1][k].x; };
+    if (ty > 0) {
+        float *r = s_red + ((ty - 1) * 32 + tx) * kAcc;
+        #pragma unroll
+        for (int c = 0; c < C; ++c) {
+            #pragma unroll
+            for (int k = 0; k <= W; ++k) r[c * (W + 1) + k] = dwv(c, k);
+        }
+    }
+    __syncthreads();
+    if (ty == 0 && lane_ok) {
+        #pragma unroll 1
+        for (int y = 1; y < kBwdClRows; ++y) {
+            const float *r = s_red + ((y - 1) * 32 + tx) * kAcc;
+            #pragma unroll
+            for (int c = 0; c < C; ++c) {
+                #pragma unroll
+                for (int k = 0; k <= W; ++k) dwv(c, k) += r[c * (W + 1) + k];
+            }
+        }
+        float *p = a.ws + (((uint64_t)b * a.ngroups + grp) * (uint64_t)a.dim + (uint64_t)col * C) * (W + 1);
+        #pragma unroll
+        for (int c = 0; c < C; ++c) {
+            #pragma unroll
+            for (int k = 0; k <= W; ++k) p[c * (W + 1) + k] = dwv(c, k);
+        }
+    }
+}
+
 int pick_tokens_per_thread(int64_t batch, int64_t ncols, int64_t seqlen, int sms, int max_tpt);
 
 struct ClPlan {
@@ -860,10 +1088,33 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
     a.dim = p.dim; a.seqlen = p.seqlen; a.wtype = p.wtype; a.tpt = pl.tpt;
     a.ncols = pl.ncols; a.ncolblk = pl.ncolblk; a.ngroups = pl.ngroups;
     if (ctas > 0) {
-        CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
-            CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
-                bwd_cl_kernel<T, W, kSilu, kSeqIdx><<<(unsigned)ctas, 32 * kBwdClRows, 0, stream>>>(a);
-            }););););
+        bool launched = false;
+#if CC1D_BWD_CL_TMA
+        CUtensorMap xmap, dmap;
+        const int row_bytes = 32 * kBwdClC * elem_size(p.itype);
+        // 16-bit I/O only: fp32 stages would leave room for a single CTA per SM
+        if (p.itype != CC1D_F32 && p.seqlen < (1ll << 31) - 16 && p.batch < (1ll << 31) &&
+            make_channel_last_tensor_map(&xmap, p.itype, p.x, p.dim, p.seqlen, p.batch, p.x_l_stride, p.x_batch_stride, row_bytes) &&
+            make_channel_last_tensor_map(&dmap, p.itype, p.dout, p.dim, p.seqlen, p.batch, p.dout_l_stride, p.dout_batch_stride, row_bytes)) {
+            CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
+                CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
+                    auto kernel = bwd_cl_tma_kernel<T, W, kSilu, kSeqIdx>;
+                    static bool attr_set = false;   // per instantiation
+                    if (!attr_set) {
+                        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BwdTma<T>::kSmem);
+                        attr_set = true;
+                    }
+                    kernel<<<(unsigned)ctas, 32 * kBwdClRows, BwdTma<T>::kSmem, stream>>>(a, xmap, dmap);
+                }););););
+            launched = true;
+        }
+#endif
+        if (!launched) {
+            CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
+                CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
+                    bwd_cl_kernel<T, W, kSilu, kSeqIdx><<<(unsigned)ctas, 32 * kBwdClRows, 0, stream>>>(a);
+                }););););
+        }
         if (check_launch() != CC1D_OK) return CC1D_ERR_LAUNCH;
     }
     ReduceArgs r;

@@ -15,6 +15,7 @@
 // of the reference.
 #include "cc1d_common.cuh"
 #include "cc1d_kernels.h"
+#include "cc1d_tma.cuh"
 
 namespace cc1d {
 
@@ -209,13 +210,16 @@ struct FwdClArgs {
     uint32_t ngroups;   // CTAs along seqlen per batch entry (kRows chunks each)
 };
 
+#ifndef CC1D_FWD_CL_TMA
+#define CC1D_FWD_CL_TMA 1
+#endif
 constexpr int kClRows = 8;    // token chunks per CTA (threadIdx.y)
 constexpr int kClUnroll = 4;  // tokens per block: loads of one block are in flight while the previous computes
 
 // One token of the sliding window: out = act(bias + sum_k w[k] * window[k]), then shift.
 template <typename T, int W, int C, bool kSilu, bool kSeqIdx, bool kTanh>
 __device__ __forceinline__ void fwd_cl_token_impl(const Raw<T, C> &raw, int sid, float (&win)[W - 1][C], int (&sw)[W - 1],
-                                                  const float (&wv)[W][C], const float (&bv)[C], char *optr) {
+                                                  const float (&wv)[W][C], const float (&bv)[C], char *optr, bool store) {
     float cur[C], o[C];
     unpack_raw<T>(raw, cur);
     #pragma unroll
@@ -230,7 +234,7 @@ __device__ __forceinline__ void fwd_cl_token_impl(const Raw<T, C> &raw, int sid,
         // a padded token (seq_idx < 0) outputs exactly zero: no bias, no activation
         o[c] = (kSeqIdx && sid < 0) ? 0.f : acc;
     }
-    st_stream_raw(optr, PackRaw<T, C>::run(o));
+    if (store) st_stream_raw(optr, PackRaw<T, C>::run(o));
     #pragma unroll
     for (int k = 0; k < W - 2; ++k) {
         #pragma unroll
@@ -247,17 +251,17 @@ __device__ __forceinline__ void fwd_cl_token_impl(const Raw<T, C> &raw, int sid,
 // no tap is masked and the unmasked code runs (a warp-uniform branch).
 template <typename T, int W, int C, bool kSilu, bool kSeqIdx, bool kTanh>
 __device__ __forceinline__ void fwd_cl_token(const Raw<T, C> &raw, int sid, float (&win)[W - 1][C], int (&sw)[W - 1],
-                                             const float (&wv)[W][C], const float (&bv)[C], char *optr) {
+                                             const float (&wv)[W][C], const float (&bv)[C], char *optr, bool store = true) {
     if (kSeqIdx) {
         bool same = sid >= 0;
         #pragma unroll
         for (int k = 0; k < W - 1; ++k) same = same && sw[k] == sid;
         if (same) {
-            fwd_cl_token_impl<T, W, C, kSilu, false, kTanh>(raw, sid, win, sw, wv, bv, optr);
+            fwd_cl_token_impl<T, W, C, kSilu, false, kTanh>(raw, sid, win, sw, wv, bv, optr, store);
             return;
         }
     }
-    fwd_cl_token_impl<T, W, C, kSilu, kSeqIdx, kTanh>(raw, sid, win, sw, wv, bv, optr);
+    fwd_cl_token_impl<T, W, C, kSilu, kSeqIdx, kTanh>(raw, sid, win, sw, wv, bv, optr, store);
 }
 
 template <typename T, int W, bool kSilu, bool kSeqIdx>
@@ -352,6 +356,162 @@ __global__ void __launch_bounds__(32 * kClRows, 2) fwd_cl_kernel(const FwdClArgs
     }
 }
 
+// ---- TMA variant ----------------------------------------------------------------------------
+// Same sliding-window arithmetic, but x reaches the warp through the TMA unit: each warp is an
+// independent pipeline over its own ring of kTmaStages boxes ([kTmaRows tokens x 512 bytes]) in
+// shared memory, one mbarrier per box.  Lane 0 requests boxes kTmaStages ahead; all lanes wait
+// on the box's barrier, read their 16 bytes per token with ld.shared and store results
+// straight to global memory.  Rows past seqlen and channels past dim are zero-filled by the
+// TMA unit, so the loop has no load predicates.  Warps never synchronise with each other.
+#ifndef CC1D_TMA_WARPS
+#define CC1D_TMA_WARPS 4
+#endif
+#ifndef CC1D_TMA_STAGES
+#define CC1D_TMA_STAGES 3
+#endif
+constexpr int kTmaWarps = CC1D_TMA_WARPS;
+constexpr int kTmaStages = CC1D_TMA_STAGES;
+constexpr size_t kFwdTmaSmem = (size_t)kTmaWarps * kTmaStages * kTmaStageBytes + (size_t)kTmaWarps * kTmaStages * 8;
+
+template <typename T, int W, bool kSilu, bool kSeqIdx>
+__global__ void __launch_bounds__(32 * kTmaWarps) fwd_cl_tma_kernel(const FwdClArgs a, const __grid_constant__ CUtensorMap xmap) {
+    constexpr int C = Elem<T>::kVec;
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    using R = Raw<T, C>;
+    extern __shared__ __align__(1024) unsigned char smem[];
+
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const uint32_t cb = blockIdx.x % a.ncolblk;
+    const uint32_t rest = blockIdx.x / a.ncolblk;
+    const uint32_t grp = rest % a.ngroups;
+    const uint32_t b = rest / a.ngroups;
+    const uint32_t col = cb * 32 + lane;
+    const bool lane_ok = col < a.ncols;            // lanes past dim compute on zeros and never store
+    const int L = (int)a.seqlen;
+    const int t0 = (int)((grp * kTmaWarps + wid) * (uint32_t)a.tpt);
+    if (t0 >= L) return;                           // whole warp
+    const int t1 = t0 + a.tpt < L ? t0 + a.tpt : L;
+    const int n = t1 - t0, nst = (n + kTmaRows - 1) / kTmaRows;
+
+    const uint32_t ring = smem_u32(smem) + wid * (kTmaStages * kTmaStageBytes);
+    const uint32_t bars = smem_u32(smem) + kTmaWarps * kTmaStages * kTmaStageBytes + wid * (kTmaStages * 8);
+    if (lane == 0) {
+        tma_prefetch_desc(&xmap);
+        #pragma unroll
+        for (int s = 0; s < kTmaStages; ++s) mbar_init(bars + 8 * s, 1);
+        fence_mbar_init();
+        #pragma unroll
+        for (int s = 0; s < kTmaStages; ++s) {
+            if (s < nst) {
+                mbar_expect_tx(bars + 8 * s, kTmaStageBytes);
+                tma_load_3d(ring + s * kTmaStageBytes, &xmap, (int)(cb * 32 * C), t0 + s * kTmaRows, (int)b, bars + 8 * s);
+            }
+        }
+    }
+    __syncwarp();
+
+    const int64_t xs = a.x_ls * (int64_t)sizeof(T), os = a.o_ls * (int64_t)sizeof(T);
+    const char *xptr = reinterpret_cast<const char *>(a.x) + (b * a.x_bs + (int64_t)col * C) * (int64_t)sizeof(T) + t0 * xs;
+    char *optr = reinterpret_cast<char *>(a.out) + (b * a.o_bs + (int64_t)col * C) * (int64_t)sizeof(T) + t0 * os;
+    const int32_t *__restrict__ sp = kSeqIdx ? a.seq_idx + (int64_t)b * L + t0 : nullptr;
+
+    // window = the width-1 tokens before t0 (x, or initial_states, or zero)
+    float win[W - 1][C];
+    int sw[W - 1];
+    #pragma unroll
+    for (int k = 0; k < W - 1; ++k) {
+        const int p = t0 - (W - 1) + k;
+        R r;
+        zero_raw(r);
+        sw[k] = -1;
+        if (p >= 0) {
+            if (lane_ok) ld_cached_raw(r, xptr - (W - 1 - k) * xs);
+            if (kSeqIdx) sw[k] = sp[k - (W - 1)];
+        } else if (a.init != nullptr && lane_ok) {
+            ld_cached_raw(r, reinterpret_cast<const T *>(a.init) + b * a.i_bs + (p + (W - 1)) * a.i_ls + (int64_t)col * C);
+        }
+        unpack_raw<T>(r, win[k]);
+    }
+    float wv[W][C], bv[C];
+    if (lane_ok) {
+        load_taps<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, kTanh ? 0.5f : 1.f);
+    } else {
+        #pragma unroll
+        for (int c = 0; c < C; ++c) {
+            bv[c] = 0.f;
+            #pragma unroll
+            for (int k = 0; k < W; ++k) wv[k][c] = 0.f;
+        }
+    }
+
+    // sequence ids of a box are fetched one box ahead, so that their latency hides behind a box
+    int nsid[kTmaRows];
+    #pragma unroll
+    for (int r = 0; r < kTmaRows; ++r) nsid[r] = (kSeqIdx && r < n) ? sp[r] : 0;
+    for (int st = 0; st < nst; ++st) {
+        const int s = st % kTmaStages;
+        const int rows = n - st * kTmaRows;            // >= kTmaRows except in the last box
+        int sid[kTmaRows];
+        #pragma unroll
+        for (int r = 0; r < kTmaRows; ++r) {
+            sid[r] = nsid[r];
+            nsid[r] = (kSeqIdx && kTmaRows + r < rows) ? sp[kTmaRows + r] : 0;
+        }
+        if (!mbar_wait(bars + 8 * s, (uint32_t)(st / kTmaStages) & 1u)) {
+            g_tma_wait_expired = 1;                    // never expected; leave without touching more memory
+            return;
+        }
+        const uint32_t src = ring + s * kTmaStageBytes + lane * 16;
+        // one test per box instead of one per token: a box whose tokens and window all carry the
+        // same non-negative sequence id needs no masking at all (warp-uniform branch)
+        bool plain = rows >= kTmaRows;
+        if (kSeqIdx) {
+            plain = plain && sid[0] >= 0;
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) plain = plain && sw[k] == sid[0];
+            #pragma unroll
+            for (int r = 1; r < kTmaRows; ++r) plain = plain && sid[r] == sid[0];
+        }
+        if (plain) {
+            #pragma unroll
+            for (int r = 0; r < kTmaRows; ++r) {
+                const R raw = lds128(src + r * kTmaRowBytes);
+                fwd_cl_token_impl<T, W, C, kSilu, false, kTanh>(raw, sid[r], win, sw, wv, bv, optr + r * os, lane_ok);
+            }
+        } else if (rows >= kTmaRows) {
+            #pragma unroll
+            for (int r = 0; r < kTmaRows; ++r) {
+                const R raw = lds128(src + r * kTmaRowBytes);
+                fwd_cl_token_impl<T, W, C, kSilu, kSeqIdx, kTanh>(raw, sid[r], win, sw, wv, bv, optr + r * os, lane_ok);
+            }
+        } else {
+            #pragma unroll
+            for (int r = 0; r < kTmaRows; ++r) {
+                if (r < rows) {
+                    const R raw = lds128(src + r * kTmaRowBytes);
+                    fwd_cl_token<T, W, C, kSilu, kSeqIdx, kTanh>(raw, sid[r], win, sw, wv, bv, optr + r * os, lane_ok);
+                }
+            }
+        }
+        optr += kTmaRows * os;
+        if (kSeqIdx) sp += kTmaRows;
+        __syncwarp();                                   // every lane has consumed the box
+        if (lane == 0 && st + kTmaStages < nst) {       // refill it
+            fence_proxy_async_smem();
+            mbar_expect_tx(bars + 8 * s, kTmaStageBytes);
+            tma_load_3d(ring + s * kTmaStageBytes, &xmap, (int)(cb * 32 * C), t0 + (st + kTmaStages) * kTmaRows, (int)b,
+                        bars + 8 * s);
+        }
+    }
+
+    // the thread that consumed the last token holds the last width-1 entries of [initial | x]
+    if (a.fin != nullptr && t1 == L && lane_ok) {
+        T *fp = reinterpret_cast<T *>(a.fin) + b * a.f_bs + (int64_t)col * C;
+        #pragma unroll
+        for (int k = 0; k < W - 1; ++k) st_plain_raw(fp + k * a.f_ls, PackRaw<T, C>::run(win[k]));
+    }
+}
+
 // Tokens per thread: long enough to amortise the (width-1)-token halo re-read, short enough
 // to fill the machine (~2 CTAs of 256 threads per SM and more).
 int pick_tokens_per_thread(int64_t batch, int64_t ncols, int64_t seqlen, int sms, int max_tpt) {
@@ -381,10 +541,37 @@ int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream) {
     a.dim = p.dim; a.seqlen = p.seqlen; a.wtype = p.wtype;
     const int64_t ncols = p.dim / C;
     a.tpt = pick_tokens_per_thread(p.batch, ncols, p.seqlen, sms, 64);
+#ifndef CC1D_TMA_TPT
+#define CC1D_TMA_TPT 64
+#endif
     a.ncols = (uint32_t)ncols;
     a.ncolblk = (uint32_t)((ncols + 31) / 32);
     const int64_t chunks = (p.seqlen + a.tpt - 1) / a.tpt;
     a.ngroups = (uint32_t)((chunks + kClRows - 1) / kClRows);
+#if CC1D_FWD_CL_TMA
+    // TMA path: 16-bit I/O only (the fp32 kernel is already at the memory roof without it)
+    CUtensorMap xmap;
+    if (p.itype != CC1D_F32 && p.seqlen < (1ll << 31) && p.batch < (1ll << 31) &&
+        make_channel_last_tensor_map(&xmap, p.itype, p.x, p.dim, p.seqlen, p.batch, p.x_l_stride, p.x_batch_stride)) {
+        // each warp keeps kTmaStages boxes in flight, so fewer and longer chunks fill the machine
+        a.tpt = pick_tokens_per_thread(p.batch, ncols, p.seqlen, sms / 2, CC1D_TMA_TPT);
+        const int64_t tchunks = (p.seqlen + a.tpt - 1) / a.tpt;
+        a.ngroups = (uint32_t)((tchunks + kTmaWarps - 1) / kTmaWarps);
+        const uint64_t tctas = (uint64_t)a.ncolblk * a.ngroups * (uint64_t)p.batch;
+        if (tctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
+        CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
+            CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
+                auto kernel = fwd_cl_tma_kernel<T, W, kSilu, kSeqIdx>;
+                static bool attr_set = false;   // per instantiation
+                if (!attr_set) {
+                    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwdTmaSmem);
+                    attr_set = true;
+                }
+                kernel<<<(unsigned)tctas, 32 * kTmaWarps, kFwdTmaSmem, stream>>>(a, xmap);
+            }););););
+        return check_launch();
+    }
+#endif
     const uint64_t ctas = (uint64_t)a.ncolblk * a.ngroups * (uint64_t)p.batch;
     if (ctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
     CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,

@@ -369,6 +369,107 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+# ---- secondary workloads (same JSON shape; the default stays the C2 line above) ---------------------
+def _time_steps(torch, fn, nsets, steps, warmup):
+    for i in range(max(warmup, 3)):
+        fn(i % nsets)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for i in range(steps):
+        fn(i % nsets)
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / steps   # ms
+
+
+def run_secondary(args):
+    """--workload c3: BASELINE config 3a (packed varlen prefill, channel-last, seq_idx), fwd+bwd.
+    --workload c4: BASELINE config 4 (decode update, batch 256, pool of 512 states), us per step."""
+    import torch
+
+    from causal_conv1d_b200._ext import ext
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peak, peak_src = measured_peak()
+    bf = torch.bfloat16
+    nsets = max(1, args.buffer_sets)
+    if args.workload == "c3":
+        D, L, W = 5376, 32768, 4
+        torch.manual_seed(2)
+        lens = torch.randint(256, 3841, (16,)).double()
+        lens = (lens / lens.sum() * L).long()
+        lens[-1] = L - lens[:-1].sum()
+        sidx = torch.repeat_interleave(torch.arange(16), lens).int().view(1, L).to(dev)
+        w = (torch.rand(D, W) - 0.5).to(dev, bf)
+        b = (torch.rand(D) - 0.5).to(dev, bf)
+        sets = []
+        for _ in range(nsets):
+            x = torch.randn(1, L, D, device=dev, dtype=bf).transpose(1, 2)
+            dout = torch.randn(1, L, D, device=dev, dtype=bf).transpose(1, 2)
+            sets.append((x, dout, torch.empty_like(x), torch.empty_like(x)))
+        dw, db = torch.empty(D, W, device=dev), torch.empty(D, device=dev)
+        fwd = lambda i: ext.causal_conv1d_fwd(sets[i][0], w, b, sidx, None, sets[i][2], None, True)
+        bwd = lambda i: ext.causal_conv1d_bwd(sets[i][0], w, b, sets[i][1], sidx, None, None, sets[i][3], dw, db, None, True, False)
+        t_f = _time_steps(torch, fwd, nsets, args.steps, args.warmup)
+        t_b = _time_steps(torch, bwd, nsets, args.steps, args.warmup)
+        n = D * L
+        fb, bb = 2 * n * ELEM + 4 * L, 3 * n * ELEM + 4 * L
+        line = {"metric": "fwd+bwd algorithmic HBM GB/s, Mamba-2 2.7B packed varlen prefill (1,5376,32768) bf16 channel-last, seq_idx",
+                "value": round((fb + bb) / ((t_f + t_b) * 1e-3) / 1e9, 1), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": round(t_f + t_b, 5), "higher_is_better": True, "dtype": "bf16",
+                "data": "synthetic", "config": {"workload": "C3a packed varlen prefill: 16 sequences, 32768 tokens, dim 5376, width 4, SiLU, seed 2",
+                                                "l2": f"{nsets} rotating buffer sets of 1.4 GB"},
+                "kernels": {"fwd_cl (TMA)": {"ms": round(t_f, 5), "gbs": round(fb / t_f / 1e6, 1), "frac": round(fb / t_f / 1e6 / peak, 4)},
+                            "bwd_cl (TMA) + reduce": {"ms": round(t_b, 5), "gbs": round(bb / t_b / 1e6, 1), "frac": round(bb / t_b / 1e6 / peak, 4)}},
+                "roofline": {"bound": "hbm", "kernel": "bwd_cl_tma_kernel (+ reduce_partials_kernel)", "achieved": round(bb / t_b / 1e6, 1),
+                             "peak": peak, "unit": UNIT, "frac": round(bb / t_b / 1e6 / peak, 4), "traffic": None, "peak_source": peak_src},
+                "gpu_launches": 3 * args.steps, "tokens_per_s": round(L / ((t_f + t_b) * 1e-3), 1)}
+    else:
+        B, D, S, W, POOL = 256, 5376, 3, 4, 512
+        torch.manual_seed(3)
+        nsets = max(nsets, 8)   # 8 x 22 MB > L2
+        w = (torch.rand(D, W) - 0.5).to(dev, bf)
+        b = (torch.rand(D) - 0.5).to(dev, bf)
+        idx = torch.randperm(POOL)[:B].int().to(dev)
+        res = {}
+        for name, cl in (("channel_last_state", True), ("contiguous_state", False)):
+            sets = []
+            for _ in range(nsets):
+                x = torch.randn(B, D, 1, device=dev, dtype=bf)
+                st = torch.randn(POOL, S, D, device=dev, dtype=bf).transpose(1, 2) if cl else torch.randn(POOL, D, S, device=dev, dtype=bf)
+                sets.append((x, st, torch.empty_like(x)))
+            run = lambda i: ext.causal_conv1d_update(sets[i][0], sets[i][1], w, b, sets[i][2], True, None, idx)
+            t_stream = _time_steps(torch, run, nsets, args.steps, args.warmup)
+            g, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for i in range(nsets):
+                    run(i)
+                torch.cuda.synchronize()
+                with torch.cuda.graph(g, stream=side):
+                    for i in range(nsets):
+                        run(i)
+            t_graph = _time_steps(torch, lambda i: g.replay(), 1, max(3, args.steps // nsets), 3) / nsets
+            res[name] = {"us_stream": round(t_stream * 1e3, 3), "us_graph": round(t_graph * 1e3, 3)}
+        byts = B * D * ELEM * (2 + (W - 1) + S) + 4 * B
+        best = min(r["us_graph"] for r in res.values())
+        line = {"metric": "decode update us per step, batch 256, dim 5376, bf16, pool of 512 states (state_len 3), gathered by conv_state_indices",
+                "value": best, "unit": "us", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": round(best * 1e-3, 6), "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": "C4 decode update, seqlen 1, SiLU, seed 3", "l2": f"{nsets} rotating x/state/out sets (> 2x L2)",
+                           "timing": "us_stream: back-to-back launches; us_graph: CUDA-graph replay of the same launches"},
+                "layouts": res,
+                "roofline": {"bound": "hbm", "kernel": "update_vec_kernel / update_cfstate_kernel", "achieved": round(byts / best / 1e3, 1),
+                             "peak": peak, "unit": UNIT, "frac": round(byts / best / 1e3 / peak, 4), "traffic": None,
+                             "peak_source": peak_src, "algorithmic_bytes_per_launch": byts,
+                             "lower_bound_us": round(byts / peak / 1e3, 3)},
+                "gpu_launches": args.steps}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -378,9 +479,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the ~12 s CPU-port timing")
     ap.add_argument("--buffer-sets", type=int, default=3, help="rotating input/output sets (profiling: 1)")
     ap.add_argument("--skip-e2e", action="store_true", help="kernel loop only (for ncu captures)")
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4"],
+                    help="c2 (default, the headline line); c3: packed varlen channel-last prefill; c4: decode update")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "c2":
+        run_secondary(args)
     else:
         run_b200(args)
 

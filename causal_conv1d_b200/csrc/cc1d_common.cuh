@@ -243,8 +243,14 @@ template <bool kTanh> __device__ __forceinline__ float2 dsilu_pair(float2 v) {
     }
     return make_float2(dsilu_f(v.x), dsilu_f(v.y));
 }
+#ifndef CC1D_TANH_SILU_FP16
+#define CC1D_TANH_SILU_FP16 1
+#endif
 template <typename T> struct UseTanhSilu { static constexpr bool value = false; };
 template <> struct UseTanhSilu<__nv_bfloat16> { static constexpr bool value = true; };
+#if CC1D_TANH_SILU_FP16
+template <> struct UseTanhSilu<__half> { static constexpr bool value = true; };
+#endif
 
 // ---- channel-first row access: 16-byte vectors of one (batch, channel) row -----------------
 // Vector at element offset e of a row of L elements: one 16-byte load when it lies fully

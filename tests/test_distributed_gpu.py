@@ -1,0 +1,59 @@
+"""Batch-sharded backward and channel-sharded decode on 2 real GPUs (NCCL).  Skipped when
+fewer than 2 devices are visible."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from causal_conv1d_b200 import causal_conv1d_update
+        from causal_conv1d_b200.distributed import batch_shard, batch_sharded_backward, channel_shard
+        torch.manual_seed(0)   # the same full problem on every rank
+        B, D, L, W = 6, 256, 1000, 4
+        x = torch.randn(B, D, L, dtype=torch.bfloat16).to(dev)
+        dout = torch.randn(B, D, L, dtype=torch.bfloat16).to(dev)
+        w, b = torch.randn(D, W).to(dev), torch.randn(D).to(dev)
+        # unsharded result on this GPU
+        full = batch_sharded_backward(x, w, b, dout, activation="silu", group=dist.new_group([rank]))
+        dx, dw, db, _, packed = batch_sharded_backward(batch_shard(x, rank, world), w, b, batch_shard(dout, rank, world),
+                                                       activation="silu")
+        ok = torch.equal(dx, batch_shard(full[0], rank, world))                 # dx needs no communication
+        ok &= torch.allclose(dw, full[1], rtol=1e-5, atol=1e-4) and torch.allclose(db, full[2], rtol=1e-5, atol=1e-4)
+        gathered = [torch.empty_like(packed) for _ in range(world)]
+        dist.all_gather(gathered, packed)
+        ok &= all(torch.equal(gathered[0], g) for g in gathered)                # every rank holds the same bits
+        # channel-sharded decode: shards of x / state / weight, no collective
+        xs = torch.randn(8, D, dtype=torch.bfloat16).to(dev)
+        st = torch.randn(8, 3, D, dtype=torch.bfloat16).to(dev).transpose(1, 2)
+        st_full = st.clone()
+        out_full = causal_conv1d_update(xs, st_full, w, b, activation="silu")
+        st_sh = channel_shard(st, rank, world).contiguous().transpose(1, 2).contiguous().transpose(1, 2)
+        out_sh = causal_conv1d_update(channel_shard(xs, rank, world).contiguous(), st_sh, channel_shard(w, rank, world, dim=0),
+                                      channel_shard(b, rank, world, dim=0), activation="silu")
+        ok &= torch.equal(out_sh, channel_shard(out_full, rank, world)) and torch.equal(st_sh, channel_shard(st_full, rank, world))
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_sharding():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
+    assert ret.get(0) is True and ret.get(1) is True

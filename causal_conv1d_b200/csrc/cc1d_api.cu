@@ -95,7 +95,8 @@ int check_conv_common(int itype, int wtype, int width, int64_t batch, int64_t di
     if (bad_dtype(itype) || bad_dtype(wtype)) return CC1D_ERR_DTYPE;
     if (width < 2 || width > 4) return CC1D_ERR_WIDTH;
     if (batch < 0 || dim < 0 || seqlen < 0) return CC1D_ERR_SHAPE;
-    if (x == nullptr || weight == nullptr) return CC1D_ERR_NULL;
+    const bool empty = batch == 0 || dim == 0 || seqlen == 0;   // nothing to read: pointers may be NULL
+    if ((!empty && x == nullptr) || (dim > 0 && weight == nullptr)) return CC1D_ERR_NULL;
     if (x_ls != 1 && x_cs != 1) return CC1D_ERR_STRIDE;
     if (!elem_aligned(x, itype) || !elem_aligned(weight, wtype)) return CC1D_ERR_ALIGN;
     *channel_last = x_cs == 1 && x_ls > 1;
@@ -154,6 +155,7 @@ int cc1d_fwd(const cc1d_fwd_params *p, cc1d_stream_t stream) {
     int rc = check_conv_common(p->itype, p->wtype, p->width, p->batch, p->dim, p->seqlen, p->x,
                                p->x_batch_stride, p->x_c_stride, p->x_l_stride, p->weight, &cl);
     if (rc != CC1D_OK) return rc;
+    if (p->batch == 0 || p->dim == 0 || p->seqlen == 0) return CC1D_OK;   // empty problem: nothing to write
     if (p->out == nullptr) return CC1D_ERR_NULL;
     if (!elem_aligned(p->out, p->itype)) return CC1D_ERR_ALIGN;
     rc = check_same_layout(cl, p->out_batch_stride, p->out_c_stride, p->out_l_stride, p->seqlen, p->dim, p->batch);
@@ -174,7 +176,8 @@ static int check_bwd(const cc1d_bwd_params *p, bool *cl) {
     int rc = check_conv_common(p->itype, p->wtype, p->width, p->batch, p->dim, p->seqlen, p->x,
                                p->x_batch_stride, p->x_c_stride, p->x_l_stride, p->weight, cl);
     if (rc != CC1D_OK) return rc;
-    if (p->dout == nullptr || p->dx == nullptr || p->dweight == nullptr) return CC1D_ERR_NULL;
+    const bool empty = p->batch == 0 || p->dim == 0 || p->seqlen == 0;   // only dweight/dbias get written (zeros)
+    if ((!empty && (p->dout == nullptr || p->dx == nullptr)) || (p->dim > 0 && p->dweight == nullptr)) return CC1D_ERR_NULL;
     if ((p->bias == nullptr) != (p->dbias == nullptr)) return CC1D_ERR_NULL;
     if (!elem_aligned(p->dout, p->itype) || !elem_aligned(p->dx, p->itype) ||
         !elem_aligned(p->dweight, CC1D_F32) || !elem_aligned(p->dbias, CC1D_F32)) return CC1D_ERR_ALIGN;
@@ -260,8 +263,9 @@ int cc1d_update(const cc1d_update_params *p, cc1d_stream_t stream) {
     if (bad_dtype(p->itype) || bad_dtype(p->wtype)) return CC1D_ERR_DTYPE;
     if (p->width < 2 || p->width > 4) return CC1D_ERR_WIDTH;
     if (p->batch < 0 || p->dim < 0 || p->seqlen < 0 || p->conv_state_len < 0) return CC1D_ERR_SHAPE;
-    if (p->x == nullptr || p->weight == nullptr || p->out == nullptr || p->conv_state == nullptr) return CC1D_ERR_NULL;
     if (p->conv_state_len < p->width - 1) return CC1D_ERR_STATE_LEN;
+    if (p->batch == 0 || p->dim == 0 || p->seqlen == 0) return CC1D_OK;   // empty problem
+    if (p->x == nullptr || p->weight == nullptr || p->out == nullptr || p->conv_state == nullptr) return CC1D_ERR_NULL;
     if (!elem_aligned(p->x, p->itype) || !elem_aligned(p->out, p->itype) || !elem_aligned(p->conv_state, p->itype) ||
         !elem_aligned(p->weight, p->wtype)) return CC1D_ERR_ALIGN;
     return launch_update(*p, reinterpret_cast<cudaStream_t>(stream));

@@ -401,3 +401,45 @@ def test_errors():
         api.causal_conv1d_fn(x.cpu(), torch.randn(16, 4))
     with pytest.raises(RuntimeError, match="width - 1"):
         api.causal_conv1d_update(torch.randn(2, 16, device=DEV), torch.randn(2, 16, 2, device=DEV), torch.randn(16, 4, device=DEV))
+
+
+def test_empty_inputs():
+    """Zero-sized batch / seqlen: empty outputs, zero weight gradients, no error."""
+    api = _api()
+    w = torch.randn(16, 4, device=DEV, requires_grad=True)
+    b = torch.randn(16, device=DEV, requires_grad=True)
+    for shape in ((0, 16, 32), (2, 16, 0)):
+        x = torch.randn(*shape, device=DEV, requires_grad=True)
+        out = api.causal_conv1d_fn(x, w, b, activation="silu")
+        assert out.shape == x.shape
+        w.grad = b.grad = None
+        out.backward(torch.empty_like(out))
+        assert x.grad.shape == x.shape
+        assert (w.grad == 0).all() and (b.grad == 0).all()
+    out = api.causal_conv1d_update(torch.randn(0, 16, device=DEV), torch.randn(0, 16, 3, device=DEV), w.detach(), b.detach())
+    assert out.shape == (0, 16)
+
+
+def test_registered_custom_ops():
+    """The torch.library ops (the path torch.compile traces) give the same bits as the direct calls."""
+    import causal_conv1d_b200.cpp_functions  # noqa: F401  (registers the ops)
+    torch.manual_seed(9)
+    x = torch.randn(2, 24, 100, device=DEV, dtype=torch.bfloat16)
+    w, b = torch.randn(24, 4, device=DEV), torch.randn(24, device=DEV)
+    ref = _api().causal_conv1d_fn(x, w, b, activation="silu")
+    out = torch.empty_like(x)
+    torch.ops.cc1d_b200._causal_conv1d_fwd_cpp(x, w, b, None, None, out, None, True)
+    assert torch.equal(out, ref)
+    dout = torch.randn_like(x)
+    dx, dw, db = torch.empty_like(x), torch.empty(24, 4, device=DEV), torch.empty(24, device=DEV)
+    torch.ops.cc1d_b200._causal_conv1d_bwd_cpp(x, w, b, dout, None, None, None, dx, dw, db, None, True)
+    xr = x.clone().requires_grad_()
+    wr = w.clone().requires_grad_()
+    _api().causal_conv1d_fn(xr, wr, b, activation="silu").backward(dout)
+    assert torch.equal(dx, xr.grad) and torch.equal(dw, wr.grad)
+    st = torch.randn(2, 3, 24, device=DEV, dtype=torch.bfloat16).transpose(1, 2)
+    st2 = st.clone()
+    o1 = torch.empty(2, 24, 1, device=DEV, dtype=torch.bfloat16)
+    torch.ops.cc1d_b200._causal_conv1d_update_cpp(x[:, :, :1].contiguous(), st, w, b, o1, True, None, None)
+    o2 = _api().causal_conv1d_update(x[:, :, 0].contiguous(), st2, w, b, activation="silu")
+    assert torch.equal(o1.squeeze(-1), o2) and torch.equal(st, st2)

@@ -420,6 +420,7 @@ def _time_steps(torch, fn, nsets, steps, warmup):
 
 def run_secondary(args):
     """--workload c3: BASELINE config 3a (packed varlen prefill, channel-last, seq_idx), fwd+bwd.
+    --workload c3p: the C3 pack through cc1d_prefill_varlen (forward with per-sequence conv states).
     --workload c4: BASELINE config 4 (decode update, batch 256, pool of 512 states), us per step."""
     import torch
 
@@ -463,6 +464,48 @@ def run_secondary(args):
                 "roofline": {"bound": "hbm", "kernel": "bwd_cl_tma_kernel (+ reduce_partials_kernel)", "achieved": round(bb / t_b / 1e6, 1),
                              "peak": peak, "unit": UNIT, "frac": round(bb / t_b / 1e6 / peak, 4), "traffic": None, "peak_source": peak_src},
                 "gpu_launches": 3 * args.steps, "tokens_per_s": round(L / ((t_f + t_b) * 1e-3), 1)}
+    elif args.workload == "c3p":
+        # The C3 pack as a serving prefill: every sequence continues from, and leaves behind, a row of a
+        # conv-state pool (one cc1d_prefill_varlen call = masked forward + boundary kernel).
+        D, L, W, S, NSEQ, POOL = 5376, 32768, 4, 3, 16, 64
+        torch.manual_seed(2)
+        lens = torch.randint(256, 3841, (NSEQ,)).double()
+        lens = (lens / lens.sum() * L).long()
+        lens[-1] = L - lens[:-1].sum()
+        cu = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)]).int().to(dev)
+        sidx = torch.empty(L, dtype=torch.int32, device=dev)
+        ext.seq_idx_from_cu_seqlens(cu, sidx)
+        w = (torch.rand(D, W) - 0.5).to(dev, bf)
+        b = (torch.rand(D) - 0.5).to(dev, bf)
+        rows = torch.randperm(POOL)[:NSEQ].int().to(dev)
+        pool = torch.randn(POOL, S, D, device=dev, dtype=bf).transpose(1, 2)
+        sets = []
+        for _ in range(nsets):
+            x = torch.randn(L, D, device=dev, dtype=bf)
+            sets.append((x, torch.empty_like(x)))
+        states_out = torch.empty(NSEQ, S, D, device=dev, dtype=bf).transpose(1, 2)
+        fused = lambda i: ext.causal_conv1d_prefill_varlen(sets[i][0], w, b, sidx, cu, pool, pool, rows, None, sets[i][1], True)
+        plain = lambda i: ext.causal_conv1d_fwd(sets[i][0].T.unsqueeze(0), w, b, sidx.view(1, L), None,
+                                                sets[i][1].T.unsqueeze(0), None, True)
+        two_pass = lambda i: (plain(i), ext.causal_conv1d_varlen_states(sets[i][0], cu, states_out))
+        t_fused = _time_steps(torch, fused, nsets, args.steps, args.warmup)
+        t_plain = _time_steps(torch, plain, nsets, args.steps, args.warmup)
+        t_two = _time_steps(torch, two_pass, nsets, args.steps, args.warmup)
+        byts = 2 * D * L * ELEM + 4 * L + 2 * NSEQ * D * S * ELEM
+        line = {"metric": "packed varlen prefill with per-sequence conv states, algorithmic HBM GB/s, (32768 tokens, dim 5376) bf16",
+                "value": round(byts / t_fused / 1e6, 1), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": round(t_fused, 5), "higher_is_better": True, "dtype": "bf16",
+                "data": "synthetic",
+                "config": {"workload": "C3 pack (16 sequences, 32768 tokens, dim 5376, width 4, SiLU, seed 2), each sequence prefixed by "
+                                       "and written back to its row of a (64, 5376, 3) state pool",
+                           "l2": f"{nsets} rotating x/out sets of 705 MB"},
+                "calls": {"cc1d_prefill_varlen (masked forward + boundary kernel)": {"ms": round(t_fused, 5)},
+                          "masked forward alone (no states)": {"ms": round(t_plain, 5)},
+                          "masked forward + cc1d_varlen_states (two calls, no prefix possible)": {"ms": round(t_two, 5)}},
+                "roofline": {"bound": "hbm", "kernel": "fwd_cl_tma_kernel (+ prefill_boundary_kernel)", "achieved": round(byts / t_fused / 1e6, 1),
+                             "peak": peak, "unit": UNIT, "frac": round(byts / t_fused / 1e6 / peak, 4), "traffic": None,
+                             "peak_source": peak_src, "algorithmic_bytes_per_launch": byts},
+                "gpu_launches": 2 * args.steps, "tokens_per_s": round(L / (t_fused * 1e-3), 1)}
     else:
         B, D, S, W, POOL = 256, 5376, 3, 4, 512
         torch.manual_seed(3)
@@ -514,8 +557,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the ~12 s CPU-port timing")
     ap.add_argument("--buffer-sets", type=int, default=3, help="rotating input/output sets (profiling: 1)")
     ap.add_argument("--skip-e2e", action="store_true", help="kernel loop only (for ncu captures)")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4"],
-                    help="c2 (default, the headline line); c3: packed varlen channel-last prefill; c4: decode update")
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c3p", "c4"],
+                    help="c2 (default, the headline line); c3: packed varlen channel-last prefill fwd+bwd; "
+                         "c3p: the same pack as a serving prefill with per-sequence conv states; c4: decode update")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

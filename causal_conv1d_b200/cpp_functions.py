@@ -146,3 +146,39 @@ def causal_conv1d_varlen_states_function(x: torch.Tensor, cu_seqlens: torch.Tens
     fn = _causal_conv1d_varlen_states_cpp if _compiling() else _ext.causal_conv1d_varlen_states
     fn(x, cu_seqlens.contiguous(), states)
     return states
+
+
+def seq_idx_from_cu_seqlens_function(cu_seqlens: torch.Tensor, total_tokens: int) -> torch.Tensor:
+    seq_idx = torch.empty(total_tokens, dtype=torch.int32, device=cu_seqlens.device)
+    _ext.seq_idx_from_cu_seqlens(cu_seqlens.to(torch.int32).contiguous(), seq_idx)
+    return seq_idx
+
+
+def causal_conv1d_prefill_varlen_function(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: torch.Tensor | None,
+    cu_seqlens: torch.Tensor,
+    seq_idx: torch.Tensor | None,
+    conv_states: torch.Tensor | None,
+    state_indices: torch.Tensor | None,
+    has_initial_state: torch.Tensor | None,
+    update_states: bool,
+    silu_activation: bool,
+) -> torch.Tensor:
+    """Packed varlen prefill continuing from / updating per-sequence conv states; eager only
+    (no custom op is registered for it)."""
+    cu = cu_seqlens.to(torch.int32).contiguous()
+    if seq_idx is None:
+        seq_idx = seq_idx_from_cu_seqlens_function(cu, x.shape[0])
+    out = torch.empty_like(x)
+    if has_initial_state is not None:
+        has_initial_state = has_initial_state.to(torch.bool).contiguous()
+    if state_indices is not None:
+        state_indices = state_indices.to(torch.int32).contiguous()
+    _ext.causal_conv1d_prefill_varlen(
+        x, weight, bias, seq_idx.reshape(-1), cu,
+        conv_states,
+        conv_states if (conv_states is not None and update_states) else None,
+        state_indices, has_initial_state, out, silu_activation)
+    return out

@@ -261,6 +261,90 @@ void causal_conv1d_varlen_states(const at::Tensor &x, const at::Tensor &cu_seqle
     raise_on(cc1d_varlen_states(&p, at::cuda::getCurrentCUDAStream().stream()), "causal_conv1d_varlen_states");
 }
 
+// Packed variable-length prefill (cc1d_prefill_varlen): x, out (total_tokens, dim) with
+// stride(1) == 1; seq_idx (total_tokens,) int32; cu_seqlens (nseq + 1,) int32; conv states
+// (rows, dim, state_len) with stride(1) == 1, read as each sequence's left context and/or
+// overwritten with its final state.
+void causal_conv1d_prefill_varlen(const at::Tensor &x, const at::Tensor &weight, const OptTensor &bias_,
+                                  const at::Tensor &seq_idx, const at::Tensor &cu_seqlens,
+                                  const OptTensor &initial_states_, const OptTensor &final_states_,
+                                  const OptTensor &state_indices_, const OptTensor &has_initial_state_,
+                                  at::Tensor &out, bool silu_activation) {
+    need_cuda(x, "x"); need_cuda(weight, "weight"); need_cuda(out, "out"); need_cuda(seq_idx, "seq_idx");
+    need_cuda(cu_seqlens, "cu_seqlens");
+    TORCH_CHECK(x.dim() == 2 && weight.dim() == 2, "expected x (total_tokens, dim) and weight (dim, width)");
+    const int64_t total = x.size(0), dim = x.size(1), width = weight.size(1);
+    need_shape(weight, {dim, width}, "weight");
+    need_shape(out, {total, dim}, "out");
+    TORCH_CHECK(out.scalar_type() == x.scalar_type(), "out must have the dtype of x");
+    TORCH_CHECK((x.stride(1) == 1 && out.stride(1) == 1) || dim <= 1, "x and out must be contiguous along dim");
+    TORCH_CHECK(seq_idx.scalar_type() == at::kInt && seq_idx.is_contiguous() && seq_idx.numel() == total,
+                "seq_idx must be a contiguous int32 tensor of total_tokens entries");
+    TORCH_CHECK(cu_seqlens.scalar_type() == at::kInt && cu_seqlens.dim() == 1 && cu_seqlens.is_contiguous() &&
+                cu_seqlens.size(0) >= 1, "cu_seqlens must be a contiguous int32 tensor (nseq + 1,)");
+    const int64_t nseq = cu_seqlens.size(0) - 1;
+
+    cc1d_prefill_varlen_params p = {};
+    p.itype = dtype_code(x, "x"); p.wtype = dtype_code(weight, "weight");
+    p.width = (int32_t)width; p.silu = silu_activation;
+    p.total_tokens = total; p.dim = dim; p.nseq = nseq;
+    p.x = x.data_ptr(); p.x_l_stride = x.stride(0);
+    p.weight = weight.data_ptr(); p.weight_c_stride = weight.stride(0); p.weight_width_stride = weight.stride(1);
+    p.bias = bias_ptr(bias_, weight, dim);
+    p.out = out.data_ptr(); p.out_l_stride = out.stride(0);
+    p.seq_idx = seq_idx.data_ptr<int32_t>();
+    p.cu_seqlens = cu_seqlens.data_ptr<int32_t>();
+    auto state = [&](const at::Tensor &t, const char *what) {
+        need_cuda(t, what);
+        TORCH_CHECK(t.dim() == 3 && t.size(1) == dim, what, " must be (rows, dim, state_len)");
+        TORCH_CHECK(t.scalar_type() == x.scalar_type(), what, " must have the dtype of x");
+        TORCH_CHECK(t.stride(1) == 1 || dim <= 1, what, " must have stride(1) == 1");
+        TORCH_CHECK(state_indices_.has_value() || t.size(0) >= nseq, what, " has fewer rows than there are sequences");
+    };
+    if (initial_states_.has_value()) {
+        const at::Tensor &t = *initial_states_;
+        state(t, "initial_states");
+        p.state_len = t.size(2);
+        p.initial_states = t.data_ptr();
+        p.initial_states_batch_stride = t.stride(0); p.initial_states_l_stride = t.stride(2);
+    }
+    if (final_states_.has_value()) {
+        const at::Tensor &t = *final_states_;
+        state(t, "final_states");
+        TORCH_CHECK(!initial_states_.has_value() || t.size(2) == p.state_len, "initial_states and final_states differ in state_len");
+        p.state_len = t.size(2);
+        p.final_states = t.data_ptr();
+        p.final_states_batch_stride = t.stride(0); p.final_states_l_stride = t.stride(2);
+    }
+    if (state_indices_.has_value()) {
+        const at::Tensor &t = *state_indices_;
+        need_cuda(t, "state_indices");
+        TORCH_CHECK(t.scalar_type() == at::kInt && t.is_contiguous() && t.numel() == nseq, "state_indices must be a contiguous int32 tensor (nseq,)");
+        p.state_indices = t.data_ptr<int32_t>();
+    }
+    if (has_initial_state_.has_value()) {
+        const at::Tensor &t = *has_initial_state_;
+        need_cuda(t, "has_initial_state");
+        TORCH_CHECK((t.scalar_type() == at::kBool || t.scalar_type() == at::kByte) && t.is_contiguous() && t.numel() == nseq,
+                    "has_initial_state must be a contiguous bool tensor (nseq,)");
+        p.has_initial_state = reinterpret_cast<const uint8_t *>(t.data_ptr());
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    raise_on(cc1d_prefill_varlen(&p, at::cuda::getCurrentCUDAStream().stream()), "causal_conv1d_prefill_varlen");
+}
+
+// seq_idx (total_tokens,) int32 <- cu_seqlens (nseq + 1,) int32
+void seq_idx_from_cu_seqlens(const at::Tensor &cu_seqlens, at::Tensor &seq_idx) {
+    need_cuda(cu_seqlens, "cu_seqlens"); need_cuda(seq_idx, "seq_idx");
+    TORCH_CHECK(cu_seqlens.scalar_type() == at::kInt && cu_seqlens.dim() == 1 && cu_seqlens.is_contiguous() &&
+                cu_seqlens.size(0) >= 1, "cu_seqlens must be a contiguous int32 tensor (nseq + 1,)");
+    TORCH_CHECK(seq_idx.scalar_type() == at::kInt && seq_idx.is_contiguous(), "seq_idx must be a contiguous int32 tensor");
+    c10::cuda::CUDAGuard guard(seq_idx.device());
+    raise_on(cc1d_seq_idx_from_cu_seqlens(cu_seqlens.data_ptr<int32_t>(), cu_seqlens.size(0) - 1, seq_idx.numel(),
+                                          seq_idx.data_ptr<int32_t>(), at::cuda::getCurrentCUDAStream().stream()),
+             "seq_idx_from_cu_seqlens");
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("causal_conv1d_fwd", &causal_conv1d_fwd, "Causal conv1d forward");
     m.def("causal_conv1d_bwd", &causal_conv1d_bwd, "Causal conv1d backward",
@@ -270,5 +354,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("accumulate") = true);
     m.def("causal_conv1d_update", &causal_conv1d_update, "Causal conv1d update");
     m.def("causal_conv1d_varlen_states", &causal_conv1d_varlen_states, "Last tokens of each packed sequence -> conv state");
+    m.def("causal_conv1d_prefill_varlen", &causal_conv1d_prefill_varlen, "Packed varlen prefill with per-sequence conv states");
+    m.def("seq_idx_from_cu_seqlens", &seq_idx_from_cu_seqlens, "seq_idx of every packed token from cu_seqlens");
     m.def("abi_version", []() { return cc1d_abi_version(); });
 }

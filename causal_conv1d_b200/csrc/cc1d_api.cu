@@ -281,4 +281,55 @@ int cc1d_varlen_states(const cc1d_varlen_states_params *p, cc1d_stream_t stream)
     return launch_varlen_states(*p, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int cc1d_seq_idx_from_cu_seqlens(const int32_t *cu_seqlens, int64_t nseq, int64_t total_tokens, int32_t *seq_idx,
+                                 cc1d_stream_t stream) {
+    if (nseq < 0 || total_tokens < 0) return CC1D_ERR_SHAPE;
+    if (total_tokens == 0) return CC1D_OK;
+    if (cu_seqlens == nullptr || seq_idx == nullptr) return CC1D_ERR_NULL;
+    return launch_seq_idx(cu_seqlens, nseq, total_tokens, seq_idx, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cc1d_prefill_varlen(const cc1d_prefill_varlen_params *p, cc1d_stream_t stream) {
+    if (p == nullptr) return CC1D_ERR_NULL;
+    if (p->nseq < 0 || p->state_len < 0 || p->total_tokens < 0 || p->dim < 0) return CC1D_ERR_SHAPE;
+    if (bad_dtype(p->itype) || bad_dtype(p->wtype)) return CC1D_ERR_DTYPE;
+    if (p->width < 2 || p->width > 4) return CC1D_ERR_WIDTH;
+    if (p->dim % 8 != 0) return CC1D_ERR_CL_DIM;
+    const bool states = p->initial_states != nullptr || p->final_states != nullptr;
+    if (states && p->state_len < p->width - 1) return CC1D_ERR_STATE_LEN;
+    if (p->dim == 0) return CC1D_OK;
+    if (p->nseq > 0 && p->cu_seqlens == nullptr) return CC1D_ERR_NULL;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int C = vec_elems(p->itype);
+
+    if (p->total_tokens > 0 && (p->seq_idx == nullptr || p->x == nullptr || p->out == nullptr)) return CC1D_ERR_NULL;
+    if (p->total_tokens > 0 && (p->x_l_stride <= 1 || p->out_l_stride <= 1)) return CC1D_ERR_STRIDE;
+    if (states && p->nseq > 0) {
+        // the boundary kernel moves 16-byte channel vectors
+        if (p->total_tokens > 0 && (!is_aligned16(p->x) || !is_aligned16(p->out) || p->x_l_stride % C || p->out_l_stride % C))
+            return CC1D_ERR_ALIGN;
+        if (p->initial_states != nullptr && (!is_aligned16(p->initial_states) || p->initial_states_batch_stride % C ||
+                                             (p->state_len > 1 && p->initial_states_l_stride % C)))
+            return CC1D_ERR_ALIGN;
+        if (p->final_states != nullptr && (!is_aligned16(p->final_states) || p->final_states_batch_stride % C ||
+                                           (p->state_len > 1 && p->final_states_l_stride % C)))
+            return CC1D_ERR_ALIGN;
+    }
+    if (p->total_tokens > 0) {
+        // the masked channel-last forward over the whole pack, as one batch entry
+        cc1d_fwd_params f = {};
+        f.itype = p->itype; f.wtype = p->wtype; f.width = p->width; f.silu = p->silu;
+        f.batch = 1; f.dim = p->dim; f.seqlen = p->total_tokens;
+        f.x = p->x; f.x_c_stride = 1; f.x_l_stride = p->x_l_stride;
+        f.weight = p->weight; f.weight_c_stride = p->weight_c_stride; f.weight_width_stride = p->weight_width_stride;
+        f.bias = p->bias;
+        f.out = p->out; f.out_c_stride = 1; f.out_l_stride = p->out_l_stride;
+        f.seq_idx = p->seq_idx;
+        const int rc = cc1d_fwd(&f, stream);
+        if (rc != CC1D_OK) return rc;
+    }
+    if (!states || p->nseq == 0) return CC1D_OK;
+    return launch_prefill_boundary(*p, s);
+}
+
 }  // extern "C"

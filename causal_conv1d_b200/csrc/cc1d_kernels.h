@@ -40,6 +40,8 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream);
 
 int launch_update(const cc1d_update_params &p, cudaStream_t stream);
 int launch_varlen_states(const cc1d_varlen_states_params &p, cudaStream_t stream);
+int launch_seq_idx(const int32_t *cu, int64_t nseq, int64_t total, int32_t *seq_idx, cudaStream_t stream);
+int launch_prefill_boundary(const cc1d_prefill_varlen_params &p, cudaStream_t stream);
 
 // Resident CTAs per SM of a kernel (occupancy query, cached per kernel and block size):
 // persistent grid-stride kernels launch exactly sms * this many CTAs, so that no partial

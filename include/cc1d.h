@@ -211,6 +211,66 @@ typedef struct cc1d_varlen_states_params {
 
 int cc1d_varlen_states(const cc1d_varlen_states_params *p, cc1d_stream_t stream);
 
+/* ---------------------------------------------------------------------------
+ * Packed variable-length prefill with per-sequence conv states (an additive
+ * extension: the reference has no single call for it — its forward forbids
+ * seq_idx together with initial_states / final_states,
+ * causal_conv1d/causal_conv1d_interface.py:27-33, and per-sequence states come
+ * from a second pass, causal_conv1d/causal_conv1d_varlen.py:35-64).
+ *
+ * x is a channel-last pack of nseq sequences, (total_tokens, dim) with channel
+ * stride 1; sequence s owns tokens [cu_seqlens[s], cu_seqlens[s+1]).  With
+ * r = state_indices ? state_indices[s] : s  and  S = state_len:
+ *
+ *   prefix_s = has_initial_state[s] (or has_initial_state == NULL and
+ *              initial_states != NULL) ? initial_states[r] : zeros(dim, S)
+ *   out[cu[s] : cu[s+1]]  = causal conv (+ bias, + SiLU) of x[cu[s] : cu[s+1]]
+ *                           whose left context is the last width-1 entries of prefix_s
+ *                           — what causal_conv1d_ref(x_s, initial_states=...) returns;
+ *   final_states[r]       = last S entries of [prefix_s | x_s]
+ *                           — causal_conv1d_varlen_states when there is no prefix,
+ *                           the reference's final_states when S == width-1.
+ *
+ * Tokens at or after cu_seqlens[nseq] and tokens whose seq_idx is negative output
+ * zero.  A negative state index gives the sequence a zero prefix and stores no
+ * final state.  final_states may alias initial_states (in-place pool update) as
+ * long as no two sequences name the same row.
+ *
+ * seq_idx (total_tokens,) int32 must be the sequence number of every token
+ * (cc1d_seq_idx_from_cu_seqlens fills it).  Two launches on the stream: the
+ * forward kernel, then a boundary kernel that recomputes the first width-1
+ * outputs of each prefixed sequence and writes the final states.
+ * ------------------------------------------------------------------------- */
+typedef struct cc1d_prefill_varlen_params {
+    int32_t itype, wtype, width, silu;
+    int64_t total_tokens, dim, nseq, state_len;
+
+    const void *x;                  /* (total_tokens, dim), channel stride 1       */
+    int64_t x_l_stride;
+    const void *weight;
+    int64_t weight_c_stride, weight_width_stride;
+    const void *bias;
+    void *out;                      /* (total_tokens, dim), channel stride 1       */
+    int64_t out_l_stride;
+
+    const int32_t *seq_idx;         /* (total_tokens,)                             */
+    const int32_t *cu_seqlens;      /* (nseq + 1,) non-decreasing, cu[0] == 0      */
+    const int32_t *state_indices;   /* (nseq,) or NULL                             */
+    const uint8_t *has_initial_state; /* (nseq,) 0/1 or NULL                       */
+
+    const void *initial_states;     /* (rows, dim, state_len), channel stride 1, or NULL */
+    int64_t initial_states_batch_stride, initial_states_l_stride;
+    void *final_states;             /* (rows, dim, state_len), channel stride 1, or NULL */
+    int64_t final_states_batch_stride, final_states_l_stride;
+} cc1d_prefill_varlen_params;
+
+int cc1d_prefill_varlen(const cc1d_prefill_varlen_params *p, cc1d_stream_t stream);
+
+/* seq_idx[t] = s for cu_seqlens[s] <= t < cu_seqlens[s+1], -1 for t >= cu_seqlens[nseq].
+ * The reference's callers build this tensor in PyTorch (tests/test_causal_conv1d.py:437-447). */
+int cc1d_seq_idx_from_cu_seqlens(const int32_t *cu_seqlens, int64_t nseq, int64_t total_tokens,
+                                 int32_t *seq_idx, cc1d_stream_t stream);
+
 /* Human-readable text for a status code (static storage, never NULL). */
 const char *cc1d_status_str(int status);
 

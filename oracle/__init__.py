@@ -16,6 +16,7 @@ from .oracle import (  # noqa: F401
     bwd,
     update,
     varlen_states,
+    prefill_varlen,
     round_to,
     max_threads,
     set_threads,

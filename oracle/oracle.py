@@ -193,3 +193,38 @@ def update_f32_timed(x, conv_state, weight, bias, out, width, silu, repeats=1):
         f(batch, dim, seqlen, width, int(silu), state_len, _p(x), _p(conv_state), _p(weight), _p(bias),
           None, None, _p(out))
     return (time.perf_counter() - t0) / repeats
+
+
+def prefill_varlen(x, weight, bias, cu_seqlens, conv_states=None, state_indices=None,
+                   has_initial_state=None, activation=None):
+    """float64 packed-varlen prefill with per-sequence states, composed from ``fwd`` (which
+    restates causal_conv1d_ref, causal_conv1d/causal_conv1d_interface.py:132-171) one sequence
+    at a time — the loop the reference's own seq_idx test runs
+    (tests/test_causal_conv1d.py:448-454), here with ``initial_states``.
+
+    x: (total_tokens, dim); conv_states: (rows, dim, state_len) or None.
+    Returns (out (total_tokens, dim) float64, new_conv_states float64 or None); tokens at or
+    after cu_seqlens[-1] output zero.  The final state of a sequence is the last state_len
+    entries of [prefix | x_s] (for state_len == width-1 that is the reference's final_states,
+    without a prefix it is causal_conv1d_varlen_states_ref, causal_conv1d_varlen.py:67-86).
+    """
+    total, dim = x.shape
+    width = weight.shape[1]
+    cu = [int(v) for v in cu_seqlens.detach().cpu().tolist()]
+    xd = x.detach().cpu().to(torch.float64)
+    out = torch.zeros(total, dim, dtype=torch.float64)
+    new_states = None if conv_states is None else conv_states.detach().cpu().to(torch.float64).clone()
+    S = None if conv_states is None else conv_states.shape[-1]
+    for s in range(len(cu) - 1):
+        beg, end = cu[s], cu[s + 1]
+        row = s if state_indices is None else int(state_indices[s])
+        prefixed = conv_states is not None and row >= 0 and (has_initial_state is None or bool(has_initial_state[s]))
+        prefix = (conv_states[row].detach().cpu().to(torch.float64) if prefixed
+                  else (torch.zeros(dim, S, dtype=torch.float64) if S is not None else None))
+        xs = xd[beg:end].T.unsqueeze(0)   # (1, dim, len)
+        if end > beg:
+            ini = prefix[:, S - (width - 1):].unsqueeze(0) if prefixed else None
+            out[beg:end] = fwd(xs, weight, bias, initial_states=ini, activation=activation)[0].T
+        if new_states is not None and row >= 0:
+            new_states[row] = torch.cat([prefix, xs[0]], dim=1)[:, -S:]
+    return out, new_states

@@ -48,6 +48,17 @@ class VarlenParams(ctypes.Structure):
                 ("states", vp), ("states_batch_stride", i64), ("states_c_stride", i64), ("states_l_stride", i64)]
 
 
+class PrefillParams(ctypes.Structure):
+    _fields_ = [("itype", i32), ("wtype", i32), ("width", i32), ("silu", i32),
+                ("total_tokens", i64), ("dim", i64), ("nseq", i64), ("state_len", i64),
+                ("x", vp), ("x_l_stride", i64),
+                ("weight", vp), ("weight_c_stride", i64), ("weight_width_stride", i64), ("bias", vp),
+                ("out", vp), ("out_l_stride", i64),
+                ("seq_idx", vp), ("cu_seqlens", vp), ("state_indices", vp), ("has_initial_state", vp),
+                ("initial_states", vp), ("initial_states_batch_stride", i64), ("initial_states_l_stride", i64),
+                ("final_states", vp), ("final_states_batch_stride", i64), ("final_states_l_stride", i64)]
+
+
 def declared_symbols():
     """Function names declared in include/cc1d.h."""
     text = open(HEADER).read()
@@ -63,7 +74,9 @@ def load():
     lib.cc1d_bwd_workspace_bytes.argtypes = [ctypes.POINTER(BwdParams)]
     for name, st in (("cc1d_fwd", FwdParams), ("cc1d_bwd", BwdParams), ("cc1d_bwd_noalloc", BwdParams),
                      ("cc1d_update", UpdateParams),
-                     ("cc1d_varlen_states", VarlenParams)):
+                     ("cc1d_varlen_states", VarlenParams), ("cc1d_prefill_varlen", PrefillParams)):
         getattr(lib, name).argtypes = [ctypes.POINTER(st), vp]
         getattr(lib, name).restype = ctypes.c_int
+    lib.cc1d_seq_idx_from_cu_seqlens.argtypes = [vp, i64, i64, vp, vp]
+    lib.cc1d_seq_idx_from_cu_seqlens.restype = ctypes.c_int
     return lib

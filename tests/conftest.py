@@ -77,16 +77,18 @@ def check(actual, expected, itype, wtype, what=""):
 class Golden:
     def __init__(self):
         d = os.path.join(ROOT, "tests", "golden")
-        self.arrays = np.load(os.path.join(d, "golden.npz"))
-        with open(os.path.join(d, "golden.json")) as f:
-            self.meta = json.load(f)["cases"]
+        self.arrays, self.meta = {}, {}
+        for stem in ("golden", "golden_prefill"):      # one file per generating script
+            self.arrays.update(np.load(os.path.join(d, stem + ".npz")))
+            with open(os.path.join(d, stem + ".json")) as f:
+                self.meta.update(json.load(f)["cases"])
 
     def names(self, kind):
         return sorted(n for n, m in self.meta.items() if m["kind"] == kind)
 
     def get(self, case, key, dtype=None):
         k = f"{case}/{key}"
-        if k not in self.arrays.files:
+        if k not in self.arrays:
             return None
         t = torch.from_numpy(self.arrays[k])
         return t.to(dtype) if dtype is not None and t.is_floating_point() else t

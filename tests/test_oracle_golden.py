@@ -67,6 +67,20 @@ def test_varlen_states(golden, case):
     assert torch.equal(st.to(it), golden.get(case, "states", it))
 
 
+@pytest.mark.parametrize("case", golden_names("prefill_varlen"))
+def test_prefill_varlen(golden, case):
+    """Per-sequence composition of the oracle forward against the per-sequence loop over
+    causal_conv1d_ref stored by tests/golden/make_golden_prefill.py."""
+    m = golden.meta[case]
+    it = DT[m["itype"]]
+    g = lambda k, dt=None: golden.get(case, k, dt)
+    out, st = oracle.prefill_varlen(g("x", it), g("weight"), g("bias"), g("cu_seqlens"), g("conv_states", it),
+                                    g("state_indices"), g("has_initial_state"),
+                                    activation="silu" if m["silu"] else None)
+    assert_close(out.to(it), g("out", it), TOL[it], "out")
+    assert torch.equal(st.to(it), g("conv_states_out", it)), "conv states must be bit-exact"
+
+
 def test_update_padding_and_gather():
     """Negative conv_state_indices: zero output, pool untouched
     (rule of csrc/causal_conv1d_update.cu:48-54, tested at tests/test_causal_conv1d.py:317-321)."""

@@ -98,3 +98,127 @@ def batch_sharded_backward(
     dweight = dweight32.to(weight.dtype)
     dbias = dbias32.to(bias.dtype) if bias is not None else None
     return dx, dweight, dbias, dinit, packed
+
+
+# ---- sequence (context) parallel: the sequence axis is split across ranks ---------------------
+#
+# Rank r holds tokens [lo_r, hi_r) of every (batch, channel) row, channel-last.  The conv at the
+# first width-1 tokens of a shard needs the last width-1 tokens of the previous shard: each rank
+# sends that tail to rank r+1, which takes it as ``initial_states`` — the hook the reference has
+# for chunked processing (``causal_conv1d/causal_conv1d_interface.py:99-129``).  Because the
+# tail is raw input (not a conv result) all ranks run concurrently: one neighbour exchange of
+# batch * dim * (width-1) elements, then the ordinary forward.  In the backward the gradient
+# that rank r+1 computes for its ``initial_states`` belongs to the last width-1 tokens of rank
+# r's dx: one neighbour exchange the other way and an add on that slice, then the same packed
+# all-reduce of dweight / dbias as in the batch-sharded case.
+
+def sequence_shard(t: torch.Tensor, rank: int, world_size: int, dim: int = 2) -> torch.Tensor:
+    lo, hi = shard_bounds(t.shape[dim], rank, world_size)
+    return t.narrow(dim, lo, hi - lo)
+
+
+def _neighbour_exchange(send: Optional[torch.Tensor], recv: Optional[torch.Tensor], send_to: int, recv_from: int,
+                        group) -> None:
+    """Post at most one send and one receive and wait for both."""
+    ops = []
+    if send is not None:
+        ops.append(dist.P2POp(dist.isend, send, send_to, group))
+    if recv is not None:
+        ops.append(dist.P2POp(dist.irecv, recv, recv_from, group))
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+
+
+def _default_fwd():
+    from causal_conv1d_b200._ext import ext
+
+    def run(x, weight, bias, seq_idx, initial_states, out, final_states_out, silu):
+        ext.causal_conv1d_fwd(x, weight, bias, seq_idx, initial_states, out, final_states_out, silu)
+
+    return run
+
+
+def _state_buffer(batch: int, dim: int, width: int, like: torch.Tensor) -> torch.Tensor:
+    """(batch, dim, width-1) with stride(1) == 1, the layout the kernels take for states."""
+    return torch.empty(batch, width - 1, dim, device=like.device, dtype=like.dtype).transpose(1, 2)
+
+
+def sequence_parallel_forward(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    activation: Optional[str] = None,
+    initial_states: Optional[torch.Tensor] = None,
+    group: Optional[dist.ProcessGroup] = None,
+    fwd_impl: Optional[Callable] = None,
+):
+    """Forward of this rank's sequence shard ``x`` (batch, dim, local_len), channel-last
+    (``x.stride(1) == 1``), local_len >= width - 1 on every rank.  ``initial_states`` is the
+    left context of the whole sequence and is read on rank 0 only.
+    Returns (out, halo): ``halo`` is the left context this rank used (None on rank 0 without
+    initial_states); keep it for ``sequence_parallel_backward``."""
+    if activation not in (None, "silu", "swish"):
+        raise NotImplementedError("activation must be None, silu, or swish")
+    run = fwd_impl if fwd_impl is not None else _default_fwd()
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    batch, dim, seqlen = x.shape
+    width = weight.shape[1]
+    if seqlen < width - 1:
+        raise ValueError("every sequence shard must hold at least width - 1 tokens")
+    halo = initial_states if rank == 0 else _state_buffer(batch, dim, width, x)
+    tail = None
+    if rank + 1 < world:
+        tail = _state_buffer(batch, dim, width, x)
+        tail.copy_(x[:, :, seqlen - (width - 1):])
+    if world > 1:
+        ranks = dist.get_process_group_ranks(group) if group is not None else list(range(world))
+        _neighbour_exchange(tail.transpose(1, 2) if tail is not None else None,
+                            halo.transpose(1, 2) if rank > 0 else None,
+                            ranks[min(rank + 1, world - 1)], ranks[max(rank - 1, 0)], group)
+    out = torch.empty_like(x)
+    run(x, weight, bias, None, halo, out, None, activation is not None)
+    return out, halo
+
+
+def sequence_parallel_backward(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    dout: torch.Tensor,
+    halo: Optional[torch.Tensor],
+    activation: Optional[str] = None,
+    return_dinitial_states: bool = False,
+    group: Optional[dist.ProcessGroup] = None,
+    bwd_impl: Optional[Callable] = None,
+):
+    """Backward of this rank's sequence shard.  Returns (dx, dweight, dbias, dinitial_states):
+    dweight / dbias are the sums over all shards (one all-reduce of the packed fp32 buffer);
+    dinitial_states is the gradient of the whole sequence's left context, on rank 0 when asked.
+    The last width-1 positions of dx are the sum of two terms rounded separately to the I/O
+    dtype (this rank's taps, the next rank's taps)."""
+    if activation not in (None, "silu", "swish"):
+        raise NotImplementedError("activation must be None, silu, or swish")
+    run = bwd_impl if bwd_impl is not None else _default_bwd()
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    batch, dim, seqlen = x.shape
+    width = weight.shape[1]
+    dx = torch.empty_like(x)
+    packed, dweight32, dbias32 = packed_grad_buffer(dim, width, bias is not None, x.device)
+    want_dhalo = halo is not None and (rank > 0 or return_dinitial_states)
+    dhalo = _state_buffer(batch, dim, width, x) if want_dhalo else None
+    run(x, weight, bias, dout, None, halo, None, dx, dweight32, dbias32, dhalo, activation is not None)
+    if world > 1:
+        ranks = dist.get_process_group_ranks(group) if group is not None else list(range(world))
+        from_next = _state_buffer(batch, dim, width, x) if rank + 1 < world else None
+        _neighbour_exchange(dhalo.transpose(1, 2) if rank > 0 else None,
+                            from_next.transpose(1, 2) if from_next is not None else None,
+                            ranks[max(rank - 1, 0)], ranks[min(rank + 1, world - 1)], group)
+        if from_next is not None:
+            dx[:, :, seqlen - (width - 1):] += from_next
+        dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+    dweight = dweight32.to(weight.dtype)
+    dbias = dbias32.to(bias.dtype) if bias is not None else None
+    return dx, dweight, dbias, (dhalo if rank == 0 and return_dinitial_states else None)

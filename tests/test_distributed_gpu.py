@@ -1,4 +1,5 @@
-"""Batch-sharded backward and channel-sharded decode on 2 real GPUs (NCCL).  Skipped when
+"""Batch-sharded backward, channel-sharded decode and the sequence-parallel hand-off on 2 real
+GPUs (NCCL).  Skipped when
 fewer than 2 devices are visible."""
 import os
 import socket
@@ -45,6 +46,25 @@ def _worker(rank, world, port, ret):
         out_sh = causal_conv1d_update(channel_shard(xs, rank, world).contiguous(), st_sh, channel_shard(w, rank, world, dim=0),
                                       channel_shard(b, rank, world, dim=0), activation="silu")
         ok &= torch.equal(out_sh, channel_shard(out_full, rank, world)) and torch.equal(st_sh, channel_shard(st_full, rank, world))
+        # sequence parallel: halo hand-off as initial_states, dinitial_states folded back into dx
+        from causal_conv1d_b200 import causal_conv1d_fn
+        from causal_conv1d_b200.distributed import (sequence_parallel_backward, sequence_parallel_forward,
+                                                    sequence_shard)
+        xl = torch.randn(2, 777, D, dtype=torch.bfloat16).to(dev).transpose(1, 2)
+        dl = torch.randn(2, 777, D, dtype=torch.bfloat16).to(dev).transpose(1, 2)
+        xr = xl.detach().clone().requires_grad_()
+        wr, br = w.clone().requires_grad_(), b.clone().requires_grad_()
+        out_full = causal_conv1d_fn(xr, wr, br, activation="silu")
+        out_full.backward(dl)
+        xs, dsh = sequence_shard(xl, rank, world), sequence_shard(dl, rank, world)
+        out_s, halo = sequence_parallel_forward(xs, w, b, "silu")
+        ok &= torch.equal(out_s, sequence_shard(out_full, rank, world))          # same arithmetic, same bits
+        dx_s, dw_s, db_s, _ = sequence_parallel_backward(xs, w, b, dsh, halo, "silu")
+        ref_dx = sequence_shard(xr.grad, rank, world)
+        ok &= torch.equal(dx_s[:, :, : -(W - 1)], ref_dx[:, :, : -(W - 1)])      # away from the seam: identical
+        seam = (dx_s[:, :, -(W - 1):].float() - ref_dx[:, :, -(W - 1):].float()).abs()
+        ok &= bool((seam <= 1e-2 * ref_dx[:, :, -(W - 1):].float().abs().clamp(min=1.0)).all())
+        ok &= torch.allclose(dw_s, wr.grad, rtol=1e-5, atol=1e-4) and torch.allclose(db_s, br.grad, rtol=1e-5, atol=1e-4)
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()

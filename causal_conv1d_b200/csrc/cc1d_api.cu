@@ -40,6 +40,18 @@ int resident_ctas_per_sm(const void *kernel, int threads, size_t dyn_smem) {
     return n;
 }
 
+void allow_dynamic_smem(const void *kernel, size_t bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, size_t> granted;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t &have = granted[std::make_pair(kernel, dev)];
+    if (have >= bytes) return;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) == cudaSuccess) have = bytes;
+    else (void)cudaGetLastError();   // the launch that follows reports the failure
+}
+
 bool make_channel_last_tensor_map(CUtensorMap *map, int dtype, const void *base, int64_t dim, int64_t seqlen,
                                   int64_t batch, int64_t l_stride, int64_t batch_stride, int row_bytes) {
     using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,

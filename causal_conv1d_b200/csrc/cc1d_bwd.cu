@@ -1099,11 +1099,7 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
             CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
                 CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
                     auto kernel = bwd_cl_tma_kernel<T, W, kSilu, kSeqIdx>;
-                    static bool attr_set = false;   // per instantiation
-                    if (!attr_set) {
-                        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BwdTma<T>::kSmem);
-                        attr_set = true;
-                    }
+                    allow_dynamic_smem(reinterpret_cast<const void *>(kernel), BwdTma<T>::kSmem);
                     kernel<<<(unsigned)ctas, 32 * kBwdClRows, BwdTma<T>::kSmem, stream>>>(a, xmap, dmap);
                 }););););
             launched = true;

@@ -562,11 +562,7 @@ int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream) {
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
             CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
                 auto kernel = fwd_cl_tma_kernel<T, W, kSilu, kSeqIdx>;
-                static bool attr_set = false;   // per instantiation
-                if (!attr_set) {
-                    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwdTmaSmem);
-                    attr_set = true;
-                }
+                allow_dynamic_smem(reinterpret_cast<const void *>(kernel), kFwdTmaSmem);
                 kernel<<<(unsigned)tctas, 32 * kTmaWarps, kFwdTmaSmem, stream>>>(a, xmap);
             }););););
         return check_launch();

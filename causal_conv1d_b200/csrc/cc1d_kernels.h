@@ -48,6 +48,10 @@ int launch_prefill_boundary(const cc1d_prefill_varlen_params &p, cudaStream_t st
 // second wave forms.
 int resident_ctas_per_sm(const void *kernel, int threads, size_t dyn_smem);
 
+// Opt a kernel in to `bytes` of dynamic shared memory (> 48 KB needs it).  The attribute
+// belongs to the device's context, so it is set once per (kernel, device), not once per process.
+void allow_dynamic_smem(const void *kernel, size_t bytes);
+
 template <typename K>
 inline unsigned persistent_grid(K kernel, int threads, uint64_t ctas_wanted, bool persistent = true) {
     if (!persistent) return (unsigned)ctas_wanted;

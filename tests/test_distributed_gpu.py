@@ -77,3 +77,26 @@ def test_two_gpu_sharding():
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
     assert ret.get(0) is True and ret.get(1) is True
+
+
+def test_one_process_two_devices():
+    """One process driving two GPUs: per-device set-up inside the library (the shared-memory
+    opt-in of the TMA kernels, the occupancy cache) must hold on the second device too."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    sys.path.insert(0, ROOT)
+    from causal_conv1d_b200 import causal_conv1d_fn
+    torch.manual_seed(0)
+    x0 = torch.randn(2, 700, 256, dtype=torch.bfloat16)
+    w0, b0 = torch.randn(256, 4), torch.randn(256)
+    res = []
+    for d in (0, 1, 0):
+        dev = torch.device("cuda", d)
+        x = x0.to(dev).transpose(1, 2).requires_grad_()        # channel-last: TMA kernels
+        w, b = w0.to(dev).requires_grad_(), b0.to(dev).requires_grad_()
+        out = causal_conv1d_fn(x, w, b, activation="silu")
+        out.backward(torch.ones_like(out))
+        torch.cuda.synchronize(dev)
+        res.append((out.detach().cpu(), x.grad.cpu(), w.grad.cpu(), b.grad.cpu()))
+    for r in res[1:]:
+        assert all(torch.equal(a, c) for a, c in zip(res[0], r))

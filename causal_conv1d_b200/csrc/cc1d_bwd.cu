@@ -36,6 +36,7 @@ struct ReduceArgs {
 // fixed xor tree combines the lanes: the summation order never depends on timing.
 template <int W>
 __global__ void __launch_bounds__(128) reduce_partials_kernel(const ReduceArgs a) {
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t c = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (c >= a.dim) return;
@@ -66,7 +67,7 @@ __global__ void __launch_bounds__(128) reduce_partials_kernel(const ReduceArgs a
 
 static int launch_reduce(const ReduceArgs &a, int width, cudaStream_t stream) {
     const unsigned grid = (unsigned)((a.dim + 3) / 4);
-    CC1D_DISPATCH_WIDTH(width, { reduce_partials_kernel<W><<<grid, 128, 0, stream>>>(a); });
+    CC1D_DISPATCH_WIDTH(width, { launch_k(reduce_partials_kernel<W>, dim3(grid), dim3(128), 0, stream, a); });
     return check_launch();
 }
 
@@ -275,6 +276,7 @@ __device__ __forceinline__ void bwd_cf_group_pairs(
 #endif
 template <typename T, int W, bool kSilu, bool kFull, int kVecs>
 __global__ void __launch_bounds__(256, CC1D_BWD_CF_MINBLK) bwd_cf_vec_kernel(const BwdCfArgs a) {
+    pdl_wait();
     constexpr int V = Elem<T>::kVec;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
     constexpr bool kPairs = sizeof(T) == 2;
@@ -365,6 +367,7 @@ __global__ void __launch_bounds__(256, CC1D_BWD_CF_MINBLK) bwd_cf_vec_kernel(con
 // shared memory.  Partial row per tile.
 template <typename T, int W, bool kSilu>
 __global__ void __launch_bounds__(256) bwd_cf_scalar_kernel(const BwdCfArgs a) {
+    pdl_wait();
     __shared__ float red[8][W + 1];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     for (uint32_t tile = blockIdx.x; tile < a.n_units; tile += gridDim.x) {
@@ -502,12 +505,12 @@ int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream) {
                 CC1D_DISPATCH_BOOL(full, kFull, {
                     auto kernel = bwd_cf_vec_kernel<T, W, kSilu, kFull, kCfVecs>;
                     const bool persistent = CC1D_CF_BWD_PERSISTENT == 1 || (CC1D_CF_BWD_PERSISTENT == 2 && p.itype != CC1D_F32);
-                    kernel<<<persistent_grid(kernel, 256, ctas, persistent), 256, 0, stream>>>(a);
+                    launch_k(kernel, dim3(persistent_grid(kernel, 256, ctas, persistent)), dim3(256), 0, stream, a);
                 }););););
         } else {
             CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
                 auto kernel = bwd_cf_scalar_kernel<T, W, kSilu>;
-                kernel<<<persistent_grid(kernel, 256, pl.n_units), 256, 0, stream>>>(a);
+                launch_k(kernel, dim3(persistent_grid(kernel, 256, pl.n_units)), dim3(256), 0, stream, a);
             });););
         }
         if (check_launch() != CC1D_OK) return CC1D_ERR_LAUNCH;
@@ -656,6 +659,7 @@ __device__ __forceinline__ void bwd_cl_position(
 
 template <typename T, int W, bool kSilu, bool kSeqIdx>
 __global__ void __launch_bounds__(32 * kBwdClRows, CC1D_BWD_CL_MINBLK) bwd_cl_kernel(const BwdClArgs a) {
+    pdl_wait();
     constexpr int C = kBwdClC;
     constexpr int U = kBwdClUnroll;
     constexpr int kAcc = (W + 1) * C;                    // fp32 partial sums per thread
@@ -844,6 +848,7 @@ template <> __device__ __forceinline__ uint2 lds_raw<uint2>(uint32_t addr) {
 template <typename T, int W, bool kSilu, bool kSeqIdx>
 __global__ void __launch_bounds__(32 * kBwdClRows, CC1D_BWD_CL_MINBLK)
 bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap dmap) {
+    pdl_wait();
     constexpr int C = kBwdClC;
     constexpr int kAcc = (W + 1) * C;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
@@ -1100,7 +1105,7 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
                 CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
                     auto kernel = bwd_cl_tma_kernel<T, W, kSilu, kSeqIdx>;
                     allow_dynamic_smem(reinterpret_cast<const void *>(kernel), BwdTma<T>::kSmem);
-                    kernel<<<(unsigned)ctas, 32 * kBwdClRows, BwdTma<T>::kSmem, stream>>>(a, xmap, dmap);
+                    launch_k(kernel, dim3((unsigned)ctas), dim3(32 * kBwdClRows), BwdTma<T>::kSmem, stream, a, xmap, dmap);
                 }););););
             launched = true;
         }
@@ -1108,7 +1113,7 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
         if (!launched) {
             CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
                 CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
-                    bwd_cl_kernel<T, W, kSilu, kSeqIdx><<<(unsigned)ctas, 32 * kBwdClRows, 0, stream>>>(a);
+                    launch_k(bwd_cl_kernel<T, W, kSilu, kSeqIdx>, dim3((unsigned)ctas), dim3(32 * kBwdClRows), 0, stream, a);
                 }););););
         }
         if (check_launch() != CC1D_OK) return CC1D_ERR_LAUNCH;

@@ -13,6 +13,20 @@ namespace cc1d {
 
 constexpr unsigned kFullMask = 0xffffffffu;
 
+// ---- programmatic dependent launch ------------------------------------------------------
+// First statement of every kernel: wait until the kernels before this one in the stream have
+// completed (their writes visible), then let the kernel after this one be scheduled as SMs
+// free up.  Both are no-ops for a launch without the programmatic-serialisation attribute.
+#ifndef CC1D_PDL
+#define CC1D_PDL 1
+#endif
+__device__ __forceinline__ void pdl_wait() {
+#if CC1D_PDL
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+
 // ---- element traits -----------------------------------------------------------------
 template <typename T> struct Elem;
 template <> struct Elem<float> {

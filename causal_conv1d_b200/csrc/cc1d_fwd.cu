@@ -45,6 +45,7 @@ struct FwdCfArgs {
 // so no bounds check survives in the loop.
 template <typename T, int W, bool kSilu, bool kFull, int kVecs>
 __global__ void __launch_bounds__(256) fwd_cf_vec_kernel(const FwdCfArgs a) {
+    pdl_wait();
     constexpr int V = Elem<T>::kVec;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
     constexpr uint32_t kGroupElems = 32 * kVecs * V;
@@ -116,6 +117,7 @@ __global__ void __launch_bounds__(256) fwd_cf_vec_kernel(const FwdCfArgs a) {
 // Any alignment / row stride: one output element per thread, lanes along seqlen.
 template <typename T, int W, bool kSilu>
 __global__ void __launch_bounds__(256) fwd_cf_scalar_kernel(const FwdCfArgs a) {
+    pdl_wait();
     // here: vpr = 256-element tiles per row, n_units = rows * vpr
     for (uint32_t tile = blockIdx.x; tile < a.n_units; tile += gridDim.x) {
         const uint32_t row = tile / a.vpr;
@@ -175,7 +177,7 @@ int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
             CC1D_DISPATCH_BOOL(full, kFull, {
                 auto kernel = fwd_cf_vec_kernel<T, W, kSilu, kFull, kVecs>;
                 // memory-bound: fresh CTAs keep more loads in flight than a grid-stride loop does
-                kernel<<<persistent_grid(kernel, 256, ctas, CC1D_CF_FWD_PERSISTENT != 0), 256, 0, stream>>>(a);
+                launch_k(kernel, dim3(persistent_grid(kernel, 256, ctas, CC1D_CF_FWD_PERSISTENT != 0)), dim3(256), 0, stream, a);
             }););););
     } else {
         const uint64_t tpr = ((uint64_t)p.seqlen + 255) / 256;
@@ -184,7 +186,7 @@ int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
         a.vpr = (uint32_t)tpr; a.gpr = a.gpu = a.upr = 0; a.n_units = (uint32_t)n_tiles;
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
             auto kernel = fwd_cf_scalar_kernel<T, W, kSilu>;
-            kernel<<<persistent_grid(kernel, 256, n_tiles), 256, 0, stream>>>(a);
+            launch_k(kernel, dim3(persistent_grid(kernel, 256, n_tiles)), dim3(256), 0, stream, a);
         });););
     }
     return check_launch();
@@ -266,6 +268,7 @@ __device__ __forceinline__ void fwd_cl_token(const Raw<T, C> &raw, int sid, floa
 
 template <typename T, int W, bool kSilu, bool kSeqIdx>
 __global__ void __launch_bounds__(32 * kClRows, 2) fwd_cl_kernel(const FwdClArgs a) {
+    pdl_wait();
     constexpr int C = Elem<T>::kVec;  // channels per thread (one 16-byte vector)
     constexpr int U = kClUnroll;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
@@ -375,6 +378,7 @@ constexpr size_t kFwdTmaSmem = (size_t)kTmaWarps * kTmaStages * kTmaStageBytes +
 
 template <typename T, int W, bool kSilu, bool kSeqIdx>
 __global__ void __launch_bounds__(32 * kTmaWarps) fwd_cl_tma_kernel(const FwdClArgs a, const __grid_constant__ CUtensorMap xmap) {
+    pdl_wait();
     constexpr int C = Elem<T>::kVec;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
     using R = Raw<T, C>;
@@ -563,7 +567,7 @@ int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream) {
             CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
                 auto kernel = fwd_cl_tma_kernel<T, W, kSilu, kSeqIdx>;
                 allow_dynamic_smem(reinterpret_cast<const void *>(kernel), kFwdTmaSmem);
-                kernel<<<(unsigned)tctas, 32 * kTmaWarps, kFwdTmaSmem, stream>>>(a, xmap);
+                launch_k(kernel, dim3((unsigned)tctas), dim3(32 * kTmaWarps), kFwdTmaSmem, stream, a, xmap);
             }););););
         return check_launch();
     }
@@ -572,7 +576,7 @@ int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream) {
     if (ctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
     CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
         CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
-            fwd_cl_kernel<T, W, kSilu, kSeqIdx><<<(unsigned)ctas, 32 * kClRows, 0, stream>>>(a);
+            launch_k(fwd_cl_kernel<T, W, kSilu, kSeqIdx>, dim3((unsigned)ctas), dim3(32 * kClRows), 0, stream, a);
         }););););
     return check_launch();
 }

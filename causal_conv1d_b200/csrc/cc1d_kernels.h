@@ -4,6 +4,8 @@
 
 #include <cuda_runtime.h>
 
+#include <utility>
+
 #include "cc1d.h"
 
 // Compile-time tunables (overridable with -D for experiments).
@@ -57,6 +59,30 @@ inline unsigned persistent_grid(K kernel, int threads, uint64_t ctas_wanted, boo
     if (!persistent) return (unsigned)ctas_wanted;
     const uint64_t cap = (uint64_t)num_sms() * (uint64_t)resident_ctas_per_sm(reinterpret_cast<const void *>(kernel), threads, 0);
     return (unsigned)(ctas_wanted < cap ? ctas_wanted : cap);
+}
+
+// Every kernel of this library is launched with programmatic stream serialisation: the next
+// kernel of the stream may be scheduled onto SMs that the previous one has vacated while its
+// last CTAs still run.  Each kernel starts with griddepcontrol.wait (pdl_wait() in
+// cc1d_common.cuh), which returns only when the kernels before it in the stream have
+// completed and their writes are visible, so stream order is unchanged for every memory access;
+// what overlaps is launch latency, CTA scheduling and the tail of the previous kernel.
+#ifndef CC1D_PDL
+#define CC1D_PDL 1
+#endif
+template <typename... KArgs, typename... Args>
+inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = CC1D_PDL ? 1 : 0;
+    (void)cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);   // errors surface in check_launch()
 }
 
 inline int check_launch() { return cudaGetLastError() == cudaSuccess ? CC1D_OK : CC1D_ERR_LAUNCH; }

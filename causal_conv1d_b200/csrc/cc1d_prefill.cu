@@ -17,6 +17,7 @@ namespace cc1d {
 
 __global__ void __launch_bounds__(256) seq_idx_kernel(const int32_t *__restrict__ cu, int nseq, int64_t total,
                                                       int32_t *__restrict__ seq_idx) {
+    pdl_wait();
     const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (t >= total) return;
     // largest s with cu[s] <= t; empty sequences (cu[s] == cu[s+1]) are skipped by taking the last
@@ -48,6 +49,7 @@ struct PrefillArgs {
 
 template <typename T, int W, bool kSilu>
 __global__ void __launch_bounds__(128) prefill_boundary_kernel(const PrefillArgs a) {
+    pdl_wait();
     constexpr int C = Elem<T>::kVec;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
     const uint32_t cb = blockIdx.x % a.ncolblk;
@@ -141,7 +143,7 @@ int launch_seq_idx(const int32_t *cu, int64_t nseq, int64_t total, int32_t *seq_
     if (total == 0) return CC1D_OK;
     const uint64_t ctas = ((uint64_t)total + 255) / 256;
     if (ctas >= (1ull << 31) || nseq >= (1ll << 30)) return CC1D_ERR_TOO_LARGE;
-    seq_idx_kernel<<<(unsigned)ctas, 256, 0, stream>>>(cu, (int)nseq, total, seq_idx);
+    launch_k(seq_idx_kernel, dim3((unsigned)ctas), dim3(256), 0, stream, cu, (int)nseq, total, seq_idx);
     return check_launch();
 }
 
@@ -162,7 +164,7 @@ int launch_prefill_boundary(const cc1d_prefill_varlen_params &p, cudaStream_t st
     const uint64_t ctas = (uint64_t)a.ncolblk * (uint64_t)p.nseq;
     if (ctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
     CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
-        prefill_boundary_kernel<T, W, kSilu><<<(unsigned)ctas, 128, 0, stream>>>(a);
+        launch_k(prefill_boundary_kernel<T, W, kSilu>, dim3((unsigned)ctas), dim3(128), 0, stream, a);
     });););
     return check_launch();
 }

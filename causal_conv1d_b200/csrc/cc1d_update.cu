@@ -34,6 +34,7 @@ struct UpdArgs {
 // prefetched one ahead in a rolled loop.
 template <typename T, int W, bool kSilu, bool kCirc>
 __global__ void __launch_bounds__(128, 4) update_vec_kernel(const UpdArgs a) {
+    pdl_wait();
     constexpr int C = Elem<T>::kVec;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
     // flat thread index over (batch entry, channel vector), channel vectors fastest
@@ -152,6 +153,7 @@ template <> struct Bits<__half> {
 
 template <typename T, int W, bool kSilu, int S>
 __global__ void __launch_bounds__(128, 4) update_cfstate_kernel(const UpdArgs a) {
+    pdl_wait();
     constexpr int C = Elem<T>::kVec;
     constexpr int kRegs = S * 4;   // C * S elements in 32-bit registers
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
@@ -201,6 +203,7 @@ __global__ void __launch_bounds__(128, 4) update_cfstate_kernel(const UpdArgs a)
 
 template <typename T, int W, bool kSilu, bool kCirc>
 __global__ void __launch_bounds__(128) update_generic_kernel(const UpdArgs a) {
+    pdl_wait();
     const int64_t c = (int64_t)(blockIdx.x % a.ncolblk) * 128 + threadIdx.x;
     const int32_t b = blockIdx.x / a.ncolblk;
     if (c >= a.dim) return;
@@ -292,7 +295,7 @@ int launch_update(const cc1d_update_params &p, cudaStream_t stream) {
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
             CC1D_DISPATCH_BOOL(s_is_w, kSW, {
                 if constexpr (W - 1 + (kSW ? 1 : 0) >= 2) {
-                    update_cfstate_kernel<T, W, kSilu, W - 1 + (kSW ? 1 : 0)><<<(unsigned)ctas, 128, 0, stream>>>(a);
+                    launch_k(update_cfstate_kernel<T, W, kSilu, W - 1 + (kSW ? 1 : 0)>, dim3((unsigned)ctas), dim3(128), 0, stream, a);
                 }
             }););););
         return check_launch();
@@ -304,7 +307,7 @@ int launch_update(const cc1d_update_params &p, cudaStream_t stream) {
         if (ctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
             CC1D_DISPATCH_BOOL(circ, kCirc, {
-                update_vec_kernel<T, W, kSilu, kCirc><<<(unsigned)ctas, 128, 0, stream>>>(a);
+                launch_k(update_vec_kernel<T, W, kSilu, kCirc>, dim3((unsigned)ctas), dim3(128), 0, stream, a);
             }););););
     } else {
         a.ncols = 0;
@@ -313,7 +316,7 @@ int launch_update(const cc1d_update_params &p, cudaStream_t stream) {
         if (ctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
             CC1D_DISPATCH_BOOL(circ, kCirc, {
-                update_generic_kernel<T, W, kSilu, kCirc><<<(unsigned)ctas, 128, 0, stream>>>(a);
+                launch_k(update_generic_kernel<T, W, kSilu, kCirc>, dim3((unsigned)ctas), dim3(128), 0, stream, a);
             }););););
     }
     return check_launch();

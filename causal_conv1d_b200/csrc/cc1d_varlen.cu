@@ -26,6 +26,7 @@ __device__ __forceinline__ int64_t load_cu(const void *cu, int64_t i, int is64) 
 // otherwise one element with arbitrary strides.  grid = (ncolblk * state_len, batch).
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(128) varlen_states_kernel(const VarlenArgs a) {
+    pdl_wait();
     constexpr int C = kVec ? Elem<T>::kVec : 1;
     const uint32_t cb = blockIdx.x % a.ncolblk;
     const int64_t k = blockIdx.x / a.ncolblk;          // state slot
@@ -66,7 +67,7 @@ int launch_varlen_states(const cc1d_varlen_states_params &p, cudaStream_t stream
     if (gx >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
     const dim3 grid((unsigned)gx, (unsigned)p.batch);
     CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_BOOL(vec, kVec, {
-        varlen_states_kernel<T, kVec><<<grid, 128, 0, stream>>>(a);
+        launch_k(varlen_states_kernel<T, kVec>, dim3(grid), dim3(128), 0, stream, a);
     }););
     return check_launch();
 }

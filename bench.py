@@ -514,13 +514,15 @@ def run_secondary(args):
         b = (torch.rand(D) - 0.5).to(dev, bf)
         idx = torch.randperm(POOL)[:B].int().to(dev)
         res = {}
-        for name, cl in (("channel_last_state", True), ("contiguous_state", False)):
+
+        def time_update(cl, Lx, S_, circ):
             sets = []
             for _ in range(nsets):
-                x = torch.randn(B, D, 1, device=dev, dtype=bf)
-                st = torch.randn(POOL, S, D, device=dev, dtype=bf).transpose(1, 2) if cl else torch.randn(POOL, D, S, device=dev, dtype=bf)
+                x = torch.randn(B, Lx, D, device=dev, dtype=bf).transpose(1, 2) if (cl and Lx > 1) else torch.randn(B, D, Lx, device=dev, dtype=bf)
+                st = torch.randn(POOL, S_, D, device=dev, dtype=bf).transpose(1, 2) if cl else torch.randn(POOL, D, S_, device=dev, dtype=bf)
                 sets.append((x, st, torch.empty_like(x)))
-            run = lambda i: ext.causal_conv1d_update(sets[i][0], sets[i][1], w, b, sets[i][2], True, None, idx)
+            cache = torch.randint(0, 10000, (B,), dtype=torch.int32, device=dev) if circ else None
+            run = lambda i: ext.causal_conv1d_update(sets[i][0], sets[i][1], w, b, sets[i][2], True, cache, idx)
             t_stream = _time_steps(torch, run, nsets, args.steps, args.warmup)
             g, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
             with torch.cuda.stream(side):
@@ -531,7 +533,22 @@ def run_secondary(args):
                     for i in range(nsets):
                         run(i)
             t_graph = _time_steps(torch, lambda i: g.replay(), 1, max(3, args.steps // nsets), 3) / nsets
-            res[name] = {"us_stream": round(t_stream * 1e3, 3), "us_graph": round(t_graph * 1e3, 3)}
+            return {"us_stream": round(t_stream * 1e3, 3), "us_graph": round(t_graph * 1e3, 3)}
+
+        for name, cl in (("channel_last_state", True), ("contiguous_state", False)):
+            res[name] = time_update(cl, 1, S, False)
+        # the other variants the configuration names: 4 tokens per step, and the circular pool of 8 slots
+        variants = {}
+        for name, cl in (("channel_last_state", True), ("contiguous_state", False)):
+            for Lx, S_, circ in ((4, 3, False), (1, 8, True), (4, 8, True)):
+                r = time_update(cl, Lx, S_, circ)
+                alg = B * D * ELEM * (2 * Lx + (W - 1) + Lx) if circ else B * D * ELEM * (2 * Lx + max(W - 1, S_ - Lx) + S_)
+                r["algorithmic_bytes"] = alg + 4 * B * (2 if circ else 1)
+                r["lower_bound_us"] = round(r["algorithmic_bytes"] / peak / 1e3, 3)
+                if circ and not cl:
+                    # rows of 16 bytes: every 32-byte sector of a touched state block is read and written back whole
+                    r["sector_bytes"] = B * D * ELEM * (2 * Lx + 2 * S_)
+                variants[f"{name}, seqlen {Lx}, state_len {S_}, {'circular' if circ else 'linear'}"] = r
         byts = B * D * ELEM * (2 + (W - 1) + S) + 4 * B
         best = min(r["us_graph"] for r in res.values())
         line = {"metric": "decode update us per step, batch 256, dim 5376, bf16, pool of 512 states (state_len 3), gathered by conv_state_indices",
@@ -539,7 +556,7 @@ def run_secondary(args):
                 "ms_per_step": round(best * 1e-3, 6), "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": "C4 decode update, seqlen 1, SiLU, seed 3", "l2": f"{nsets} rotating x/state/out sets (> 2x L2)",
                            "timing": "us_stream: back-to-back launches; us_graph: CUDA-graph replay of the same launches"},
-                "layouts": res,
+                "layouts": res, "variants": variants,
                 "roofline": {"bound": "hbm", "kernel": "update_vec_kernel / update_cfstate_kernel", "achieved": round(byts / best / 1e3, 1),
                              "peak": peak, "unit": UNIT, "frac": round(byts / best / 1e3 / peak, 4), "traffic": None,
                              "peak_source": peak_src, "algorithmic_bytes_per_launch": byts,

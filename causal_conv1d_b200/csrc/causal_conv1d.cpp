@@ -356,5 +356,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("causal_conv1d_varlen_states", &causal_conv1d_varlen_states, "Last tokens of each packed sequence -> conv state");
     m.def("causal_conv1d_prefill_varlen", &causal_conv1d_prefill_varlen, "Packed varlen prefill with per-sequence conv states");
     m.def("seq_idx_from_cu_seqlens", &seq_idx_from_cu_seqlens, "seq_idx of every packed token from cu_seqlens");
+    m.def("wait_expired", []() { return cc1d_wait_expired(); }, "Health check: non-zero if a bounded wait in a kernel ran out (synchronises)");
     m.def("abi_version", []() { return cc1d_abi_version(); });
 }

@@ -137,7 +137,13 @@ using namespace cc1d;
 
 extern "C" {
 
-int cc1d_abi_version(void) { return 1; }
+int cc1d_abi_version(void) { return 2; }
+
+int cc1d_wait_expired(void) {
+    const int f = fwd_wait_expired(), b = bwd_wait_expired();
+    if (f < 0 || b < 0) return -1;
+    return (f != 0 ? 1 : 0) | (b != 0 ? 2 : 0);
+}
 
 const char *cc1d_status_str(int status) {
     switch (status) {

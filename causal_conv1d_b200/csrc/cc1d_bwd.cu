@@ -1132,4 +1132,6 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
     return launch_reduce(r, p.width, stream);
 }
 
+int bwd_wait_expired() { return read_and_clear_wait_expired(); }
+
 }  // namespace cc1d

@@ -581,4 +581,6 @@ int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream) {
     return check_launch();
 }
 
+int fwd_wait_expired() { return read_and_clear_wait_expired(); }
+
 }  // namespace cc1d

@@ -40,6 +40,8 @@ size_t bwd_workspace_bytes_channel_last(const cc1d_bwd_params &p);
 int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream);
 int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream);
 
+int fwd_wait_expired();   // bounded-wait flags of the TMA kernels, per translation unit (synchronise)
+int bwd_wait_expired();
 int launch_update(const cc1d_update_params &p, cudaStream_t stream);
 int launch_varlen_states(const cc1d_varlen_states_params &p, cudaStream_t stream);
 int launch_seq_idx(const int32_t *cu, int64_t nseq, int64_t total, int32_t *seq_idx, cudaStream_t stream);

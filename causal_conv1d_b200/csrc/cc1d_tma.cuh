@@ -20,7 +20,17 @@ constexpr int kTmaStageBytes = kTmaRows * kTmaRowBytes;
 constexpr uint32_t kTmaSpinLimit = 1u << 22;   // bounded wait: try_wait attempts before giving up
 
 // Set by a kernel of this translation unit whose bounded mbarrier wait ran out (never expected).
+// One copy per translation unit; read_and_clear_wait_expired() (below) is how the host sees it.
 static __device__ int g_tma_wait_expired;
+
+// Host: value of this translation unit's flag on the current device, reset to 0.  Synchronises.
+static inline int read_and_clear_wait_expired() {
+    int v = 0;
+    const int zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tma_wait_expired, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) (void)cudaMemcpyToSymbol(g_tma_wait_expired, &zero, sizeof(int));
+    return v;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -274,7 +274,15 @@ int cc1d_seq_idx_from_cu_seqlens(const int32_t *cu_seqlens, int64_t nseq, int64_
 /* Human-readable text for a status code (static storage, never NULL). */
 const char *cc1d_status_str(int status);
 
-/* Library ABI version: bumped when a parameter block changes layout. */
+/* Health check (no reference counterpart).  The TMA kernels wait on shared-memory barriers
+ * with an iteration limit instead of forever; a wait that runs out makes the kernel stop early
+ * and raise a device-side flag.  This call SYNCHRONISES the current device, returns 0 when no
+ * wait has run out since the last call (bit 0: forward, bit 1: backward; -1: the flags could
+ * not be read) and clears the flags.  A non-zero answer means outputs written since the last
+ * call are incomplete.  Never expected in practice; not for the hot path. */
+int cc1d_wait_expired(void);
+
+/* Library ABI version: bumped when a parameter block changes layout or entry points are added. */
 int cc1d_abi_version(void);
 
 #ifdef __cplusplus

@@ -77,6 +77,8 @@ def load():
                      ("cc1d_varlen_states", VarlenParams), ("cc1d_prefill_varlen", PrefillParams)):
         getattr(lib, name).argtypes = [ctypes.POINTER(st), vp]
         getattr(lib, name).restype = ctypes.c_int
+    lib.cc1d_wait_expired.argtypes = []
+    lib.cc1d_wait_expired.restype = ctypes.c_int
     lib.cc1d_seq_idx_from_cu_seqlens.argtypes = [vp, i64, i64, vp, vp]
     lib.cc1d_seq_idx_from_cu_seqlens.restype = ctypes.c_int
     return lib

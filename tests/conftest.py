@@ -28,6 +28,15 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+@pytest.fixture(scope="session", autouse=True)
+def no_kernel_gave_up_waiting():
+    """After the last test of a GPU session: no kernel of the library ran out of a bounded wait."""
+    yield
+    if torch.cuda.is_available():
+        from causal_conv1d_b200._ext import ext
+        assert ext.wait_expired() == 0, "a TMA kernel gave up a bounded barrier wait during this session"
+
+
 def assert_close(actual, expected, tol, what=""):
     """|a - b| <= tol * max(1, |b|) elementwise, compared in float64."""
     a = actual.detach().double().cpu()

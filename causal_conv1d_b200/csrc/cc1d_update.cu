@@ -32,7 +32,7 @@ struct UpdArgs {
 // dependent load chain, no barrier): every load that does not depend on the state row index
 // (taps, first token, cache_seqlens) is issued before the index arrives; later tokens are
 // prefetched one ahead in a rolled loop.
-template <typename T, int W, bool kSilu, bool kCirc>
+template <typename T, int W, bool kSilu, bool kCirc, int kTok>
 __global__ void __launch_bounds__(128, 4) update_vec_kernel(const UpdArgs a) {
     pdl_wait();
     constexpr int C = Elem<T>::kVec;
@@ -87,38 +87,87 @@ __global__ void __launch_bounds__(128, 4) update_vec_kernel(const UpdArgs a) {
     #pragma unroll
     for (int k = 0; k < W - 1; ++k) unpack<T>(winraw[k], win[k]);
 
-    #pragma unroll 1
-    for (int i = 0; i < L; ++i) {
-        uint4 next = make_uint4(0, 0, 0, 0);
-        if (i + 1 < L) next = ld_stream(xp + (i + 1) * a.x_ls);
-        if (kCirc) {
-            *reinterpret_cast<uint4 *>(sp + wr * a.s_ls) = raw;
-            wr = wr + 1 >= S ? 0 : wr + 1;
-        } else if (!in_regs) {
-            const int r = S - L + i;
-            if (r >= 0) *reinterpret_cast<uint4 *>(sp + r * a.s_ls) = raw;
-        }
-        float cur[C], o[C];
-        unpack<T>(raw, cur);
-        #pragma unroll
-        for (int c = 0; c < C; ++c) {
-            float acc = bv[c];
+    if constexpr (kTok > 1) {
+        // tokens in chunks of kTok: all loads of a chunk are requested together (one round trip to
+        // memory per chunk instead of one per token); token 0 is already here.  kTok == 1 is the
+        // single-token decode step, which wants the smaller register footprint.
+        #pragma unroll 1
+        for (int i0 = 0; i0 < L; i0 += kTok) {
+            uint4 tok[kTok];
             #pragma unroll
-            for (int k = 0; k < W - 1; ++k) acc = fmaf(wv[k][c], win[k][c], acc);
-            acc = fmaf(wv[W - 1][c], cur[c], acc);
-            o[c] = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
-        }
-        st_stream(op + i * a.o_ls, pack<T>(o));
-        #pragma unroll
-        for (int k = 0; k < W - 2; ++k) {
+            for (int j = 0; j < kTok; ++j) {
+                tok[j] = raw;
+                if ((j > 0 || i0 > 0) && i0 + j < L) tok[j] = ld_stream(xp + (i0 + j) * a.x_ls);
+            }
             #pragma unroll
-            for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
-            winraw[k] = winraw[k + 1];
+            for (int j = 0; j < kTok; ++j) {
+                const int i = i0 + j;
+                if (i < L) {
+                    const uint4 cur_raw = tok[j];
+                    if (kCirc) {
+                        *reinterpret_cast<uint4 *>(sp + wr * a.s_ls) = cur_raw;
+                        wr = wr + 1 >= S ? 0 : wr + 1;
+                    } else if (!in_regs) {
+                        const int r = S - L + i;
+                        if (r >= 0) *reinterpret_cast<uint4 *>(sp + r * a.s_ls) = cur_raw;
+                    }
+                    float cur[C], o[C];
+                    unpack<T>(cur_raw, cur);
+                    #pragma unroll
+                    for (int c = 0; c < C; ++c) {
+                        float acc = bv[c];
+                        #pragma unroll
+                        for (int k = 0; k < W - 1; ++k) acc = fmaf(wv[k][c], win[k][c], acc);
+                        acc = fmaf(wv[W - 1][c], cur[c], acc);
+                        o[c] = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
+                    }
+                    st_stream(op + i * a.o_ls, pack<T>(o));
+                    #pragma unroll
+                    for (int k = 0; k < W - 2; ++k) {
+                        #pragma unroll
+                        for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
+                        winraw[k] = winraw[k + 1];
+                    }
+                    #pragma unroll
+                    for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
+                    winraw[W - 2] = cur_raw;   // bit-exact copy for the state write-back
+                }
+            }
         }
-        #pragma unroll
-        for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
-        winraw[W - 2] = raw;   // bit-exact copy for the state write-back
-        raw = next;
+    } else {
+        #pragma unroll 1
+        for (int i = 0; i < L; ++i) {
+            uint4 next = make_uint4(0, 0, 0, 0);
+            if (i + 1 < L) next = ld_stream(xp + (i + 1) * a.x_ls);
+            if (kCirc) {
+                *reinterpret_cast<uint4 *>(sp + wr * a.s_ls) = raw;
+                wr = wr + 1 >= S ? 0 : wr + 1;
+            } else if (!in_regs) {
+                const int r = S - L + i;
+                if (r >= 0) *reinterpret_cast<uint4 *>(sp + r * a.s_ls) = raw;
+            }
+            float cur[C], o[C];
+            unpack<T>(raw, cur);
+            #pragma unroll
+            for (int c = 0; c < C; ++c) {
+                float acc = bv[c];
+                #pragma unroll
+                for (int k = 0; k < W - 1; ++k) acc = fmaf(wv[k][c], win[k][c], acc);
+                acc = fmaf(wv[W - 1][c], cur[c], acc);
+                o[c] = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
+            }
+            st_stream(op + i * a.o_ls, pack<T>(o));
+            #pragma unroll
+            for (int k = 0; k < W - 2; ++k) {
+                #pragma unroll
+                for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
+                winraw[k] = winraw[k + 1];
+            }
+            #pragma unroll
+            for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
+            winraw[W - 2] = raw;   // bit-exact copy for the state write-back
+            raw = next;
+        }
     }
     if (in_regs) {
         #pragma unroll
@@ -307,7 +356,8 @@ int launch_update(const cc1d_update_params &p, cudaStream_t stream) {
         if (ctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
             CC1D_DISPATCH_BOOL(circ, kCirc, {
-                launch_k(update_vec_kernel<T, W, kSilu, kCirc>, dim3((unsigned)ctas), dim3(128), 0, stream, a);
+                if (p.seqlen == 1) launch_k(update_vec_kernel<T, W, kSilu, kCirc, 1>, dim3((unsigned)ctas), dim3(128), 0, stream, a);
+                else launch_k(update_vec_kernel<T, W, kSilu, kCirc, 4>, dim3((unsigned)ctas), dim3(128), 0, stream, a);
             }););););
     } else {
         a.ncols = 0;

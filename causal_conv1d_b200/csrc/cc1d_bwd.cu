@@ -87,12 +87,12 @@ struct BwdCfArgs {
     uint32_t vpr, gpr, gpu, upr, n_units;   // see FwdCfArgs
 };
 
-// g = dout * silu'(y) for one element; `y_or_h` is the pre-activation computed with the taps
-// scaled as the chosen SiLU form wants them (y, or y/2 for the tanh form).
+// g = dout * silu'(y) for one element, times ActGrad<kTanh>::kGScale; `v` is the pre-activation
+// computed with the taps scaled by ActGrad<kTanh>::kPre (y, or -y/2 for the tanh form).
 template <bool kSilu, bool kTanh>
-__device__ __forceinline__ float grad_through_act(float dout, float y_or_h) {
+__device__ __forceinline__ float grad_through_act(float dout, float v) {
     if (!kSilu) return dout;
-    return dout * (kTanh ? dsilu_half_arg(y_or_h) : dsilu_f(y_or_h));
+    return kTanh ? act_grad_neg_half_arg(v, dout) : dout * dsilu_f(v);
 }
 
 // Shared by both group bodies: g of the first width-1 elements AFTER the unit, recomputed from
@@ -197,13 +197,21 @@ __device__ __forceinline__ void bwd_cf_group_pairs(
     float2 &db2, T *__restrict__ dxr, uint32_t e0, uint32_t L, int lane) {
     constexpr int V = Elem<T>::kVec;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
-    float2 gg[kVecs / 2][V];
+    if (seed) seed_right_halo<T, W, kSilu, kTanh>(xraw[kVecs - 1], xedge, dedge, wy, by, ge);   // warp-uniform
+    const int dst_lane = (lane + 1) & 31;
+    // Vector pairs are walked from the last to the first, g and dx of a pair in one go: dx needs
+    // g of the width-1 elements after each vector, which are the first elements of the next
+    // lane's vector, or (lane 31) of lane 0's next vector — the other half of the pair, the
+    // pair done just before (kept in gfirst), or the group after this one (ge).
+    float gfirst[W - 1];
     #pragma unroll
-    for (int jp = 0; jp < kVecs / 2; ++jp) {
+    for (int k = 0; k < W - 1; ++k) gfirst[k] = 0.f;
+    #pragma unroll
+    for (int jp = kVecs / 2 - 1; jp >= 0; --jp) {
         const int j0 = 2 * jp, j1 = 2 * jp + 1;
         const uint4 prev0 = prev_vector_tail<V, W>(xraw[j0], j0 > 0 ? xraw[j0 - 1] : carry, lane);
         const uint4 prev1 = prev_vector_tail<V, W>(xraw[j1], xraw[j0], lane);
-        float2 xx[W - 1 + V];
+        float2 xx[W - 1 + V], gx[V + W - 1];
         {
             float p0[V], p1[V], a0[V], a1[V], d0[V], d1[V];
             unpack<T>(prev0, p0); unpack<T>(prev1, p1);
@@ -212,7 +220,7 @@ __device__ __forceinline__ void bwd_cf_group_pairs(
             #pragma unroll
             for (int k = 0; k < W - 1; ++k) xx[k] = make_float2(p0[V - (W - 1) + k], p1[V - (W - 1) + k]);
             #pragma unroll
-            for (int i = 0; i < V; ++i) { xx[W - 1 + i] = make_float2(a0[i], a1[i]); gg[jp][i] = make_float2(d0[i], d1[i]); }
+            for (int i = 0; i < V; ++i) { xx[W - 1 + i] = make_float2(a0[i], a1[i]); gx[i] = make_float2(d0[i], d1[i]); }
         }
         #pragma unroll
         for (int i = 0; i < V; ++i) {
@@ -220,34 +228,20 @@ __device__ __forceinline__ void bwd_cf_group_pairs(
                 float2 y = splat2(by);
                 #pragma unroll
                 for (int k = 0; k < W; ++k) y = fma2(splat2(wy[k]), xx[i + k], y);
-                gg[jp][i] = mul2(gg[jp][i], dsilu_pair<kTanh>(y));
+                gx[i] = act_grad_pair<kTanh>(y, gx[i]);
             }
-            db2 = add2(db2, gg[jp][i]);
+            db2 = add2(db2, gx[i]);
             #pragma unroll
-            for (int k = 0; k < W; ++k) dw2[k] = fma2(xx[i + k], gg[jp][i], dw2[k]);
+            for (int k = 0; k < W; ++k) dw2[k] = fma2(xx[i + k], gx[i], dw2[k]);
         }
-    }
-    auto gval = [&](int j, int i) -> float { return (j & 1) ? gg[j >> 1][i].y : gg[j >> 1][i].x; };
-    if (seed) seed_right_halo<T, W, kSilu, kTanh>(xraw[kVecs - 1], xedge, dedge, wy, by, ge);   // warp-uniform
-
-    const int dst_lane = (lane + 1) & 31;
-    #pragma unroll
-    for (int jp = 0; jp < kVecs / 2; ++jp) {
-        float2 gx[V + W - 1];
-        #pragma unroll
-        for (int i = 0; i < V; ++i) gx[i] = gg[jp][i];
         #pragma unroll
         for (int k = 0; k < W - 1; ++k) {
-            // lane l takes lane l+1's g[j][k]; lane 31 takes lane 0's g[j+1][k]
-            float r[2];
-            #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int j = 2 * jp + h;
-                const float send = (lane == 0 && j + 1 < kVecs) ? gval(j + 1 < kVecs ? j + 1 : j, k) : gval(j, k);
-                r[h] = __shfl_sync(kFullMask, send, dst_lane);
-                if (j == kVecs - 1 && lane == 31) r[h] = ge[k];
-            }
-            gx[V + k] = make_float2(r[0], r[1]);
+            // lane l takes lane l+1's first elements; lane 31 takes lane 0's next vector
+            const float r0 = __shfl_sync(kFullMask, lane == 0 ? gx[k].y : gx[k].x, dst_lane);
+            float r1 = __shfl_sync(kFullMask, (lane == 0 && j1 + 1 < kVecs) ? gfirst[k] : gx[k].y, dst_lane);
+            if (j1 == kVecs - 1 && lane == 31) r1 = ge[k];
+            gx[V + k] = make_float2(r0, r1);
+            gfirst[k] = gx[k].x;
         }
         float o0[V], o1[V];
         #pragma unroll
@@ -261,8 +255,9 @@ __device__ __forceinline__ void bwd_cf_group_pairs(
         if (kFull || ea < L) store_row_vec<T, kFull>(dxr, ea, L, o0);
         if (kFull || eb < L) store_row_vec<T, kFull>(dxr, eb, L, o1);
     }
+    // the next (lower) group's right halo is this group's first elements, in lane 0
     #pragma unroll
-    for (int k = 0; k < W - 1; ++k) ge[k] = __shfl_sync(kFullMask, gg[0][k].x, 0);
+    for (int k = 0; k < W - 1; ++k) ge[k] = __shfl_sync(kFullMask, gfirst[k], 0);
 }
 
 // A warp unit is `gpu` consecutive groups of 32 * kVecs vectors of one row, walked BACK to
@@ -297,12 +292,14 @@ __global__ void __launch_bounds__(256, CC1D_BWD_CF_MINBLK) bwd_cf_vec_kernel(con
         const uint32_t g0 = seg * a.gpu;
         const uint32_t g1 = g0 + a.gpu < a.gpr ? g0 + a.gpu : a.gpr;
 
-        float wv[W], wy[W];   // taps, and taps scaled for the pre-activation recompute
-        const float pre = kTanh ? 0.5f : 1.f;
+        // taps scaled for dx (g is carried times kGScale) and for the pre-activation recompute
+        float wv[W], wy[W];
+        constexpr float pre = ActGrad<kTanh>::kPre, post = 1.f / ActGrad<kTanh>::kGScale;
         #pragma unroll
         for (int k = 0; k < W; ++k) {
-            wv[k] = load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype);
-            wy[k] = pre * wv[k];
+            const float w = load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype);
+            wv[k] = post * w;
+            wy[k] = pre * w;
         }
         const float by = a.bias != nullptr ? pre * load_w(a.bias, c, a.wtype) : 0.f;
 
@@ -348,6 +345,9 @@ __global__ void __launch_bounds__(256, CC1D_BWD_CF_MINBLK) bwd_cf_vec_kernel(con
             #pragma unroll
             for (int k = 0; k < W; ++k) dw[k] = dw2[k].x + dw2[k].y;
         }
+        db *= post;                      // the sums were taken over kGScale * g
+        #pragma unroll
+        for (int k = 0; k < W; ++k) dw[k] *= post;
         #pragma unroll
         for (int off = 16; off > 0; off >>= 1) {
             #pragma unroll
@@ -562,17 +562,47 @@ constexpr int kBwdClRows = CC1D_BWD_CL_ROWS;       // token chunks per CTA
 constexpr int kBwdClUnroll = CC1D_BWD_CL_UNROLL;   // positions per block (x and dout loads of the next block in flight)
 constexpr int kBwdClC = 4;        // channels per thread: 8-byte vectors for 16-bit I/O, 16-byte for fp32
 
+// wy = kPre * w and bv = kPre * bias (pre-activation recompute), wv = w / kGScale (dx): see ActGrad.
+template <int W, int C, bool kTanh>
+__device__ __forceinline__ void scale_taps_for_backward(float2 (&wv)[W][C / 2], float2 (&wy)[W][C / 2], float2 (&bv)[C / 2]) {
+    constexpr float pre = ActGrad<kTanh>::kPre, post = 1.f / ActGrad<kTanh>::kGScale;
+    #pragma unroll
+    for (int c = 0; c < C / 2; ++c) {
+        #pragma unroll
+        for (int k = 0; k < W; ++k) {
+            wy[k][c] = make_float2(pre * wv[k][c].x, pre * wv[k][c].y);
+            wv[k][c] = make_float2(post * wv[k][c].x, post * wv[k][c].y);
+        }
+        bv[c] = make_float2(pre * bv[c].x, pre * bv[c].y);
+    }
+}
+
+// the sums were taken over kGScale * g
+template <int W, int C, bool kTanh>
+__device__ __forceinline__ void unscale_sums(float2 (&dw)[C / 2][W + 1]) {
+    if (!kTanh) return;
+    constexpr float post = 1.f / ActGrad<kTanh>::kGScale;
+    #pragma unroll
+    for (int c = 0; c < C / 2; ++c) {
+        #pragma unroll
+        for (int k = 0; k <= W; ++k) dw[c][k] = make_float2(post * dw[c][k].x, post * dw[c][k].y);
+    }
+}
+
 // One position `pos` of the backward sliding window (channel-last):
 //   g[pos]   = dout[pos] * act'(y[pos])            (y recomputed from the x window)
 //   dweight += x window * g[pos], dbias += g[pos]   (only while pos is inside the thread's chunk)
 //   dx[q]    = sum_m w[W-1-m] * g[q+m],  q = pos-(W-1)   (stored when q is inside the chunk;
 //              for q < 0 the same sum is dinitial_states[q+W-1])
 // All arithmetic is on fp32 pairs of adjacent channels (FFMA2: two FMAs per issue slot).
+// `wy`, `bv` are the taps and bias scaled by ActGrad::kPre for the pre-activation, `wv` the taps
+// divided by ActGrad::kGScale for dx; g (gc, gwin, and through it dw) carries the factor kGScale.
 template <typename T, int W, int C, bool kSilu, bool kMask, bool kTanh>
 __device__ __forceinline__ void bwd_cl_position_impl(
     const Raw<T, C> &xraw, const Raw<T, C> &draw, int sid, bool accumulate, bool store_dx, bool store_dinit,
     float2 (&xwin)[W - 1][C / 2], float2 (&gwin)[W - 1][C / 2], int (&swin)[W - 1], const float2 (&wv)[W][C / 2],
-    const float2 (&bv)[C / 2], float2 (&dw)[C / 2][W + 1], const T *dfin_ptr, int64_t df_cs, char *dx_ptr, T *dinit_ptr) {
+    const float2 (&wy)[W][C / 2], const float2 (&bv)[C / 2], float2 (&dw)[C / 2][W + 1], const T *dfin_ptr, int64_t df_cs,
+    char *dx_ptr, T *dinit_ptr) {
     constexpr int P = C / 2;
     float2 xc[P], gc[P];
     unpack_pairs<T>(xraw, xc);
@@ -583,11 +613,10 @@ __device__ __forceinline__ void bwd_cl_position_impl(
             float2 y = bv[c];
             #pragma unroll
             for (int k = 0; k < W - 1; ++k) {
-                if (!kMask || swin[k] == sid) y = fma2(wv[k][c], xwin[k][c], y);
+                if (!kMask || swin[k] == sid) y = fma2(wy[k][c], xwin[k][c], y);
             }
-            y = fma2(wv[W - 1][c], xc[c], y);
-            if (kTanh) y = mul2(y, splat2(0.5f));
-            gc[c] = mul2(gc[c], dsilu_pair<kTanh>(y));
+            y = fma2(wy[W - 1][c], xc[c], y);
+            gc[c] = act_grad_pair<kTanh>(y, gc[c]);
         }
         if (kMask && sid < 0) gc[c] = make_float2(0.f, 0.f);   // padded token: out == 0 identically
     }
@@ -642,19 +671,20 @@ template <typename T, int W, int C, bool kSilu, bool kSeqIdx, bool kTanh>
 __device__ __forceinline__ void bwd_cl_position(
     const Raw<T, C> &xraw, const Raw<T, C> &draw, int sid, bool accumulate, bool store_dx, bool store_dinit,
     float2 (&xwin)[W - 1][C / 2], float2 (&gwin)[W - 1][C / 2], int (&swin)[W - 1], const float2 (&wv)[W][C / 2],
-    const float2 (&bv)[C / 2], float2 (&dw)[C / 2][W + 1], const T *dfin_ptr, int64_t df_cs, char *dx_ptr, T *dinit_ptr) {
+    const float2 (&wy)[W][C / 2], const float2 (&bv)[C / 2], float2 (&dw)[C / 2][W + 1], const T *dfin_ptr, int64_t df_cs,
+    char *dx_ptr, T *dinit_ptr) {
     if (kSeqIdx) {
         bool same = sid >= 0;
         #pragma unroll
         for (int k = 0; k < W - 1; ++k) same = same && swin[k] == sid;
         if (same) {
             bwd_cl_position_impl<T, W, C, kSilu, false, kTanh>(xraw, draw, sid, accumulate, store_dx, store_dinit, xwin, gwin,
-                                                                 swin, wv, bv, dw, dfin_ptr, df_cs, dx_ptr, dinit_ptr);
+                                                                 swin, wv, wy, bv, dw, dfin_ptr, df_cs, dx_ptr, dinit_ptr);
             return;
         }
     }
     bwd_cl_position_impl<T, W, C, kSilu, kSeqIdx, kTanh>(xraw, draw, sid, accumulate, store_dx, store_dinit, xwin, gwin, swin,
-                                                           wv, bv, dw, dfin_ptr, df_cs, dx_ptr, dinit_ptr);
+                                                           wv, wy, bv, dw, dfin_ptr, df_cs, dx_ptr, dinit_ptr);
 }
 
 template <typename T, int W, bool kSilu, bool kSeqIdx>
@@ -727,8 +757,9 @@ __global__ void __launch_bounds__(32 * kBwdClRows, CC1D_BWD_CL_MINBLK) bwd_cl_ke
             #pragma unroll
             for (int c = 0; c < C / 2; ++c) gwin[k][c] = make_float2(0.f, 0.f);
         }
-        float2 wv[W][C / 2], bv[C / 2];
+        float2 wv[W][C / 2], wy[W][C / 2], bv[C / 2];
         load_taps_pairs<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, 1.f);
+        scale_taps_for_backward<W, C, kTanh>(wv, wy, bv);
 
         const bool want_dinit = a.dinit != nullptr && t0 == 0;
         const T *dfin_base = a.dfin != nullptr ? reinterpret_cast<const T *>(a.dfin) + b * a.df_bs + (int64_t)col * C * a.df_cs : nullptr;
@@ -758,7 +789,7 @@ __global__ void __launch_bounds__(32 * kBwdClRows, CC1D_BWD_CL_MINBLK) bwd_cl_ke
                 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     bwd_cl_position<T, W, C, kSilu, kSeqIdx, kTanh>(
-                        xr[u], dr[u], sid[u], true, true, false, xwin, gwin, swin, wv, bv, dw, nullptr, 0,
+                        xr[u], dr[u], sid[u], true, true, false, xwin, gwin, swin, wv, wy, bv, dw, nullptr, 0,
                         optr + u * os, nullptr);
                 }
             } else {
@@ -772,7 +803,7 @@ __global__ void __launch_bounds__(32 * kBwdClRows, CC1D_BWD_CL_MINBLK) bwd_cl_ke
                         const T *df = (dfin_base != nullptr && q >= L - (W - 1)) ? dfin_base + (q - (L - (W - 1))) * a.df_ls : nullptr;
                         T *di = st_di ? dinit_base + (q + (W - 1)) * a.di_ls : nullptr;
                         bwd_cl_position<T, W, C, kSilu, kSeqIdx, kTanh>(
-                            xr[u], dr[u], sid[u], i < n_in, st_dx, st_di, xwin, gwin, swin, wv, bv, dw, df, a.df_cs,
+                            xr[u], dr[u], sid[u], i < n_in, st_dx, st_di, xwin, gwin, swin, wv, wy, bv, dw, df, a.df_cs,
                             optr + u * os, di);
                     }
                 }
@@ -788,6 +819,7 @@ __global__ void __launch_bounds__(32 * kBwdClRows, CC1D_BWD_CL_MINBLK) bwd_cl_ke
     // in ascending row order and writes the CTA's partial row
     // channel c of the thread lives in pair c/2, component c%2
     auto dwv = [&](int c, int k) -> float & { return (c & 1) ? dw[c >> 1][k].y : dw[c >> 1][k].x; };
+    unscale_sums<W, C, kTanh>(dw);
     if (ty > 0) {
         float *r = s_red + ((ty - 1) * 32 + tx) * kAcc;
         #pragma unroll
@@ -926,7 +958,7 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
             #pragma unroll
             for (int c = 0; c < C / 2; ++c) gwin[k][c] = make_float2(0.f, 0.f);
         }
-        float2 wv[W][C / 2], bv[C / 2];
+        float2 wv[W][C / 2], wy[W][C / 2], bv[C / 2];
         if (lane_ok) {
             load_taps_pairs<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, 1.f);
         } else {
@@ -937,6 +969,7 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
                 for (int k = 0; k < W; ++k) wv[k][c] = make_float2(0.f, 0.f);
             }
         }
+        scale_taps_for_backward<W, C, kTanh>(wv, wy, bv);
         const bool want_dinit = a.dinit != nullptr && t0 == 0 && lane_ok;
         const T *dfin_base = (a.dfin != nullptr && lane_ok) ? reinterpret_cast<const T *>(a.dfin) + b * a.df_bs + (int64_t)col * C * a.df_cs : nullptr;
         T *dinit_base = want_dinit ? reinterpret_cast<T *>(a.dinit) + b * a.di_bs + (int64_t)col * C : nullptr;
@@ -977,14 +1010,14 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
                 for (int r = 0; r < kTmaRows; ++r) {
                     const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = lds_raw<R>(dsrc + r * kRowBytes);
                     bwd_cl_position_impl<T, W, C, kSilu, false, kTanh>(
-                        xr, dr, sid[r], true, lane_ok, false, xwin, gwin, swin, wv, bv, dw, nullptr, 0, optr + r * os, nullptr);
+                        xr, dr, sid[r], true, lane_ok, false, xwin, gwin, swin, wv, wy, bv, dw, nullptr, 0, optr + r * os, nullptr);
                 }
             } else if (steady) {
                 #pragma unroll
                 for (int r = 0; r < kTmaRows; ++r) {
                     const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = lds_raw<R>(dsrc + r * kRowBytes);
                     bwd_cl_position_impl<T, W, C, kSilu, kSeqIdx, kTanh>(
-                        xr, dr, sid[r], true, lane_ok, false, xwin, gwin, swin, wv, bv, dw, nullptr, 0, optr + r * os, nullptr);
+                        xr, dr, sid[r], true, lane_ok, false, xwin, gwin, swin, wv, wy, bv, dw, nullptr, 0, optr + r * os, nullptr);
                 }
             } else {
                 #pragma unroll
@@ -998,7 +1031,7 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
                         const T *df = (dfin_base != nullptr && q >= L - (W - 1)) ? dfin_base + (q - (L - (W - 1))) * a.df_ls : nullptr;
                         T *di = st_di ? dinit_base + (q + (W - 1)) * a.di_ls : nullptr;
                         bwd_cl_position<T, W, C, kSilu, kSeqIdx, kTanh>(
-                            xr, dr, sid[r], i < n_in, st_dx, st_di, xwin, gwin, swin, wv, bv, dw, df, a.df_cs, optr + r * os, di);
+                            xr, dr, sid[r], i < n_in, st_dx, st_di, xwin, gwin, swin, wv, wy, bv, dw, df, a.df_cs, optr + r * os, di);
                     }
                 }
             }
@@ -1016,6 +1049,7 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
 
     // fixed-order sum over the CTA's token chunks (see bwd_cl_kernel)
     auto dwv = [&](int c, int k) -> float & { return (c & 1) ? dw[c >> 1][k].y : dw[c >> 1][k].x; };
+    unscale_sums<W, C, kTanh>(dw);
     if (ty > 0) {
         float *r = s_red + ((ty - 1) * 32 + tx) * kAcc;
         #pragma unroll

@@ -239,24 +239,35 @@ __device__ __forceinline__ float tanh_approx(float x) {
 }
 // silu(2h) = h + h * tanh(h)
 __device__ __forceinline__ float silu_half_arg(float h) { return fmaf(h, tanh_approx(h), h); }
-// silu'(2h) = 0.5 * (1 + t + h * (1 - t^2)),  t = tanh(h)
-__device__ __forceinline__ float dsilu_half_arg(float h) {
-    const float t = tanh_approx(h);
-    return fmaf(0.5f, fmaf(h, fmaf(-t, t, 1.f), t), 0.5f);
-}
-// pair forms: kTanh takes h = y/2 (see above), otherwise y
+// pair form of the forward: kTanh takes h = y/2 (see above), otherwise y
 template <bool kTanh> __device__ __forceinline__ float2 silu_pair(float2 v) {
     if (kTanh) return fma2(v, make_float2(tanh_approx(v.x), tanh_approx(v.y)), v);
     return make_float2(silu_f(v.x), silu_f(v.y));
 }
-template <bool kTanh> __device__ __forceinline__ float2 dsilu_pair(float2 v) {
-    if (kTanh) {
-        const float2 t = make_float2(tanh_approx(v.x), tanh_approx(v.y));
-        const float2 q = fma2(make_float2(-t.x, -t.y), t, splat2(1.f));
-        return fma2(splat2(0.5f), fma2(v, q, t), splat2(0.5f));
-    }
-    return make_float2(dsilu_f(v.x), dsilu_f(v.y));
+// Backward, tanh form without a negation: callers scale the taps of the pre-activation by -1/2
+// (free), which gives hn = -y/2 and tn = tanh(hn) = -tanh(y/2); then
+//     2 * silu'(y) = (1 - tn) + hn * (tn^2 - 1).
+// These return dout * 2 * silu'(y): g is carried with the factor ActGrad::kGScale = 2, which
+// callers take back out of the taps used for dx and out of the dweight / dbias sums (both free).
+__device__ __forceinline__ float act_grad_neg_half_arg(float hn, float dout) {
+    const float tn = tanh_approx(hn);
+    return dout * fmaf(hn, fmaf(tn, tn, -1.f), 1.f - tn);
 }
+// pair form: kTanh takes hn = -y/2 and returns 2 * g (see above), otherwise y and g
+template <bool kTanh> __device__ __forceinline__ float2 act_grad_pair(float2 v, float2 dout) {
+    if (kTanh) {
+        const float2 tn = make_float2(tanh_approx(v.x), tanh_approx(v.y));
+        const float2 m = fma2(tn, tn, splat2(-1.f));
+        const float2 u = fma2(tn, splat2(-1.f), splat2(1.f));
+        return mul2(dout, fma2(v, m, u));
+    }
+    return make_float2(dout.x * dsilu_f(v.x), dout.y * dsilu_f(v.y));
+}
+// scale of the taps that produce the backward's pre-activation argument, and of the g it carries
+template <bool kTanh> struct ActGrad {
+    static constexpr float kPre = kTanh ? -0.5f : 1.f;
+    static constexpr float kGScale = kTanh ? 2.f : 1.f;
+};
 #ifndef CC1D_TANH_SILU_FP16
 #define CC1D_TANH_SILU_FP16 1
 #endif

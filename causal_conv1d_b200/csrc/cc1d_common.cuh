@@ -1,5 +1,5 @@
 // Shared device helpers for the sm_100a causal conv1d kernels: element traits, 16-byte
-// streaming loads/stores, fp32 conversion, SiLU, weight staging.
+// streaming loads/stores, fp32 conversion, SiLU, tap loading.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -239,11 +239,6 @@ __device__ __forceinline__ float tanh_approx(float x) {
 }
 // silu(2h) = h + h * tanh(h)
 __device__ __forceinline__ float silu_half_arg(float h) { return fmaf(h, tanh_approx(h), h); }
-// pair form of the forward: kTanh takes h = y/2 (see above), otherwise y
-template <bool kTanh> __device__ __forceinline__ float2 silu_pair(float2 v) {
-    if (kTanh) return fma2(v, make_float2(tanh_approx(v.x), tanh_approx(v.y)), v);
-    return make_float2(silu_f(v.x), silu_f(v.y));
-}
 // Backward, tanh form without a negation: callers scale the taps of the pre-activation by -1/2
 // (free), which gives hn = -y/2 and tn = tanh(hn) = -tanh(y/2); then
 //     2 * silu'(y) = (1 - tn) + hn * (tn^2 - 1).
@@ -383,24 +378,6 @@ __device__ __forceinline__ void load_taps_pairs(float2 (&wv2)[W][C / 2], float2 
     }
     #pragma unroll
     for (int c = 0; c < C / 2; ++c) bv2[c] = make_float2(bv[2 * c], bv[2 * c + 1]);
-}
-
-// Stage weight taps and bias of `nch` consecutive channels starting at c0 into shared memory
-// as fp32: s_w[k * nch + c] for tap k < W, s_w[W * nch + c] = bias (0 without bias, 0 past dim).
-template <int W>
-__device__ __forceinline__ void stage_weights(float *s_w, int nch, int64_t c0, int64_t dim,
-                                              const void *weight, int64_t w_cs, int64_t w_ws,
-                                              const void *bias, int wtype, int tid, int nthreads) {
-    for (int i = tid; i < (W + 1) * nch; i += nthreads) {
-        const int k = i / nch;
-        const int64_t c = c0 + (i - k * nch);
-        float v = 0.f;
-        if (c < dim) {
-            if (k < W) v = load_w(weight, c * w_cs + k * w_ws, wtype);
-            else if (bias != nullptr) v = load_w(bias, c, wtype);
-        }
-        s_w[i] = v;
-    }
 }
 
 }  // namespace cc1d

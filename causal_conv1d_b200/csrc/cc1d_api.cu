@@ -294,7 +294,7 @@ int cc1d_varlen_states(const cc1d_varlen_states_params *p, cc1d_stream_t stream)
     if (bad_dtype(p->itype)) return CC1D_ERR_DTYPE;
     if (p->total_tokens < 0 || p->dim < 0 || p->batch < 0 || p->state_len < 0) return CC1D_ERR_SHAPE;
     if (p->batch == 0 || p->dim == 0 || p->state_len == 0) return CC1D_OK;
-    if (p->x == nullptr || p->cu_seqlens == nullptr || p->states == nullptr) return CC1D_ERR_NULL;
+    if ((p->x == nullptr && p->total_tokens > 0) || p->cu_seqlens == nullptr || p->states == nullptr) return CC1D_ERR_NULL;
     if (!elem_aligned(p->x, p->itype) || !elem_aligned(p->states, p->itype)) return CC1D_ERR_ALIGN;
     return launch_varlen_states(*p, reinterpret_cast<cudaStream_t>(stream));
 }

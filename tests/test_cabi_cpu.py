@@ -104,3 +104,42 @@ def test_varlen_rejects(lib):
 def test_status_strings(lib):
     assert lib.cc1d_status_str(0) == b"ok"
     assert b"unknown" in lib.cc1d_status_str(999)
+
+
+def _prefill(**kw):
+    p = cabi.PrefillParams(itype=cabi.BF16, wtype=cabi.F32, width=4, silu=1, total_tokens=64, dim=64, nseq=2, state_len=3,
+                           x=FAKE, x_l_stride=64, weight=FAKE, weight_c_stride=4, weight_width_stride=1,
+                           out=FAKE, out_l_stride=64, seq_idx=FAKE, cu_seqlens=FAKE,
+                           initial_states=FAKE, initial_states_batch_stride=192, initial_states_l_stride=64,
+                           final_states=FAKE, final_states_batch_stride=192, final_states_l_stride=64)
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+@pytest.mark.parametrize("kw,code", [
+    (dict(width=1), 3),
+    (dict(itype=9), 2),
+    (dict(dim=60), 6),                       # channel-last rule: dim % 8 == 0
+    (dict(state_len=2), 10),                 # shorter than width - 1
+    (dict(nseq=-1), 4),
+    (dict(cu_seqlens=0), 1),
+    (dict(seq_idx=0), 1),
+    (dict(x_l_stride=1), 5),
+    (dict(final_states_l_stride=63), 12),    # state vectors are moved 16 bytes at a time
+    (dict(initial_states=FAKE + 2), 12),
+])
+def test_prefill_varlen_rejects(lib, kw, code):
+    p = _prefill(**kw)
+    assert lib.cc1d_prefill_varlen(ctypes.byref(p), None) == code
+
+
+def test_prefill_varlen_empty_problems_are_ok(lib):
+    assert lib.cc1d_prefill_varlen(ctypes.byref(_prefill(dim=0)), None) == 0
+    assert lib.cc1d_seq_idx_from_cu_seqlens(None, 0, 0, None, None) == 0
+    assert lib.cc1d_seq_idx_from_cu_seqlens(None, 3, 10, None, None) == 1
+    assert lib.cc1d_seq_idx_from_cu_seqlens(None, -1, 10, None, None) == 4
+
+
+def test_struct_size_of_prefill_block():
+    assert ctypes.sizeof(cabi.PrefillParams) == 16 + 4 * 8 + 2 * 8 + 4 * 8 + 2 * 8 + 4 * 8 + 3 * 8 + 3 * 8

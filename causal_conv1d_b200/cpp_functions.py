@@ -82,8 +82,14 @@ def causal_conv1d_fwd_function(
     initial_states: torch.Tensor | None,
     final_states_out: torch.Tensor | None,
     silu_activation: bool,
+    out: torch.Tensor | None = None,
 ) -> torch.Tensor:
-    out = torch.empty_like(x)
+    """``out`` (not in the reference's signature): a caller-provided result buffer of x's shape,
+    dtype and layout class with any batch / row strides — e.g. a slice of the buffer the next
+    op reads — the forward counterpart of the ``dx`` hook of the backward wrapper
+    (``causal_conv1d/cpp_functions.py:125,132``).  Saves the copy a caller would otherwise make."""
+    if out is None:
+        out = torch.empty_like(x)
     fn = _causal_conv1d_fwd_cpp if _compiling() else _ext.causal_conv1d_fwd
     fn(x, weight, bias, seq_idx, initial_states, out, final_states_out, silu_activation)
     return out

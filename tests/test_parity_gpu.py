@@ -443,3 +443,38 @@ def test_registered_custom_ops():
     torch.ops.cc1d_b200._causal_conv1d_update_cpp(x[:, :, :1].contiguous(), st, w, b, o1, True, None, None)
     o2 = _api().causal_conv1d_update(x[:, :, 0].contiguous(), st2, w, b, activation="silu")
     assert torch.equal(o1.squeeze(-1), o2) and torch.equal(st, st2)
+
+
+@pytest.mark.parametrize("channel_last", [False, True])
+def test_strided_slices_in_and_out(channel_last):
+    """The op between two layout ops of a caller: x is a slice of a wider projection output, the
+    result goes straight into a slice of the buffer the next op reads (the `out` hook of
+    causal_conv1d_fwd_function), dx into a slice of the projection's gradient (the `dx` hook,
+    causal_conv1d/cpp_functions.py:125,132 of the reference).  Same bits as with dense tensors."""
+    from causal_conv1d_b200.cpp_functions import causal_conv1d_bwd_function, causal_conv1d_fwd_function
+    torch.manual_seed(7)
+    B, D, L, W = 2, 256, 520, 4
+    it = torch.bfloat16
+    w, b = torch.randn(D, W, device=DEV, dtype=it), torch.randn(D, device=DEV, dtype=it)
+    if channel_last:      # (B, L, 2D + 64) projection output, x = channels [D, 2D)
+        proj = torch.randn(B, L, 2 * D + 64, device=DEV, dtype=it)
+        nxt, dproj = torch.zeros_like(proj), torch.zeros_like(proj)
+        sl = lambda t: t[:, :, D:2 * D].transpose(1, 2)
+    else:                 # (B, 2D, L) projection output, x = first half of the channels
+        proj = torch.randn(B, 2 * D, L, device=DEV, dtype=it)
+        nxt, dproj = torch.zeros_like(proj), torch.zeros_like(proj)
+        sl = lambda t: t[:, :D]
+    x, dout = sl(proj), sl(torch.randn_like(proj))
+    out = causal_conv1d_fwd_function(x, w, b, None, None, None, True, out=sl(nxt))
+    assert out.data_ptr() == sl(nxt).data_ptr()
+    dense = causal_conv1d_fwd_function(x.contiguous() if not channel_last else x.transpose(1, 2).contiguous().transpose(1, 2),
+                                       w, b, None, None, None, True)
+    assert torch.equal(out, dense)
+    untouched = nxt.clone()
+    sl(untouched).zero_()
+    assert not untouched.any(), "nothing outside the slice is written"
+    dx, dw, db, _ = causal_conv1d_bwd_function(x, w, b, dout, None, None, None, sl(dproj), False, True)
+    dx2, dw2, db2, _ = causal_conv1d_bwd_function(x, w, b, dout, None, None, None, None, False, True)
+    assert dx.data_ptr() == sl(dproj).data_ptr() and torch.equal(dx, dx2) and torch.equal(dw, dw2) and torch.equal(db, db2)
+    ref = oracle.fwd(x, w, b, activation="silu")
+    assert_close(out, ref.to(it), TOL[it], "out")

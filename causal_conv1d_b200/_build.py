@@ -26,7 +26,7 @@ LIB_CC1D = os.path.join(PKG, "libcc1d.so")
 LIB_TORCH = os.path.join(PKG, "_cc1d_torch.so")
 
 CU_SOURCES = ["cc1d_api.cu", "cc1d_fwd.cu", "cc1d_bwd.cu", "cc1d_update.cu", "cc1d_varlen.cu",
-              "cc1d_prefill.cu"]
+              "cc1d_prefill.cu", "cc1d_peer.cu"]
 CU_HEADERS = ["cc1d_common.cuh", "cc1d_kernels.h", "cc1d_tma.cuh", os.path.join(INCLUDE, "cc1d.h")]
 
 NVCC_FLAGS = [

@@ -9,6 +9,7 @@
 #include <torch/extension.h>
 
 #include <optional>
+#include <vector>
 
 #include "cc1d.h"
 
@@ -345,6 +346,23 @@ void seq_idx_from_cu_seqlens(const at::Tensor &cu_seqlens, at::Tensor &seq_idx) 
              "seq_idx_from_cu_seqlens");
 }
 
+// One-shot peer all-reduce of a small fp32 vector (cc1d_peer_allreduce); peer_ptrs[r] is rank r's
+// exchange buffer as mapped on this device.
+void peer_allreduce(at::Tensor &buf, const std::vector<int64_t> &peer_ptrs, int64_t rank, int64_t epoch, at::Tensor &status) {
+    need_cuda(buf, "buf"); need_cuda(status, "status");
+    TORCH_CHECK(buf.scalar_type() == at::kFloat && buf.is_contiguous(), "buf must be a contiguous float32 tensor");
+    TORCH_CHECK(status.scalar_type() == at::kInt && status.numel() >= 1, "status must be an int32 tensor");
+    TORCH_CHECK(peer_ptrs.size() >= 1 && peer_ptrs.size() <= CC1D_MAX_PEERS, "1..", CC1D_MAX_PEERS, " peers");
+    cc1d_peer_allreduce_params p = {};
+    p.world = (int32_t)peer_ptrs.size(); p.rank = (int32_t)rank; p.epoch = (uint32_t)epoch;
+    p.count = buf.numel();
+    p.src = buf.data_ptr<float>(); p.dst = buf.data_ptr<float>();
+    for (size_t r = 0; r < peer_ptrs.size(); ++r) p.peer_base[r] = reinterpret_cast<void *>(peer_ptrs[r]);
+    p.status = status.data_ptr<int32_t>();
+    c10::cuda::CUDAGuard guard(buf.device());
+    raise_on(cc1d_peer_allreduce(&p, at::cuda::getCurrentCUDAStream().stream()), "peer_allreduce");
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("causal_conv1d_fwd", &causal_conv1d_fwd, "Causal conv1d forward");
     m.def("causal_conv1d_bwd", &causal_conv1d_bwd, "Causal conv1d backward",
@@ -356,6 +374,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("causal_conv1d_varlen_states", &causal_conv1d_varlen_states, "Last tokens of each packed sequence -> conv state");
     m.def("causal_conv1d_prefill_varlen", &causal_conv1d_prefill_varlen, "Packed varlen prefill with per-sequence conv states");
     m.def("seq_idx_from_cu_seqlens", &seq_idx_from_cu_seqlens, "seq_idx of every packed token from cu_seqlens");
+    m.def("peer_allreduce", &peer_allreduce, "One-shot all-reduce of a small fp32 vector over peer memory");
+    m.def("peer_allreduce_buffer_bytes", [](int64_t world, int64_t count) { return (int64_t)cc1d_peer_allreduce_buffer_bytes((int32_t)world, count); });
     m.def("wait_expired", []() { return cc1d_wait_expired(); }, "Health check: non-zero if a bounded wait in a kernel ran out (synchronises)");
     m.def("abi_version", []() { return cc1d_abi_version(); });
 }

@@ -139,6 +139,23 @@ extern "C" {
 
 int cc1d_abi_version(void) { return 2; }
 
+size_t cc1d_peer_allreduce_buffer_bytes(int32_t world, int64_t count) { return peer_allreduce_buffer_bytes(world, count); }
+
+int cc1d_peer_allreduce(const cc1d_peer_allreduce_params *p, cc1d_stream_t stream) {
+    if (p == nullptr) return CC1D_ERR_NULL;
+    if (p->world < 1 || p->world > CC1D_MAX_PEERS || p->rank < 0 || p->rank >= p->world || p->count < 0 || p->epoch == 0)
+        return CC1D_ERR_SHAPE;
+    if (p->count % 4 != 0) return CC1D_ERR_ALIGN;
+    if (p->status == nullptr) return CC1D_ERR_NULL;
+    if (p->count > 0 && (p->src == nullptr || p->dst == nullptr)) return CC1D_ERR_NULL;
+    if (!is_aligned16(p->src) || !is_aligned16(p->dst)) return CC1D_ERR_ALIGN;
+    for (int r = 0; r < p->world; ++r) {
+        if (p->peer_base[r] == nullptr) return CC1D_ERR_NULL;
+        if (!is_aligned16(p->peer_base[r])) return CC1D_ERR_ALIGN;
+    }
+    return launch_peer_allreduce(*p, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int cc1d_wait_expired(void) {
     const int f = fwd_wait_expired(), b = bwd_wait_expired();
     if (f < 0 || b < 0) return -1;

@@ -40,6 +40,8 @@ size_t bwd_workspace_bytes_channel_last(const cc1d_bwd_params &p);
 int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream);
 int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream);
 
+size_t peer_allreduce_buffer_bytes(int world, int64_t count);
+int launch_peer_allreduce(const cc1d_peer_allreduce_params &p, cudaStream_t stream);
 int fwd_wait_expired();   // bounded-wait flags of the TMA kernels, per translation unit (synchronise)
 int bwd_wait_expired();
 int launch_update(const cc1d_update_params &p, cudaStream_t stream);

@@ -8,7 +8,7 @@ with a single all-reduce, in fp32 and before the cast to the weight dtype, so th
 result does not depend on the number of ranks beyond fp32 rounding.
 
 The reference has no distributed code; this module is the multi-GPU wrapper the hot path
-needs.  Nothing here reads another GPU's memory directly.
+needs.  Nothing here reads another GPU's memory; ``PeerGradReducer`` writes into peers' buffers.
 """
 from __future__ import annotations
 
@@ -72,9 +72,11 @@ def batch_sharded_backward(
     return_dinitial_states: bool = False,
     group: Optional[dist.ProcessGroup] = None,
     bwd_impl: Optional[Callable] = None,
+    reducer: Optional["PeerGradReducer"] = None,
 ):
     """Backward of this rank's batch shard followed by the single all-reduce of the packed
-    fp32 weight gradients.  ``x`` / ``dout`` / states are the LOCAL shards; weight and bias
+    fp32 weight gradients (NCCL/gloo ``all_reduce``, or ``reducer.reduce_`` when a
+    ``PeerGradReducer`` is given).  ``x`` / ``dout`` / states are the LOCAL shards; weight and bias
     are replicated.  Returns (dx, dweight, dbias, dinitial_states, packed_fp32) with
     dweight/dbias cast to the weight dtype after the reduction.
 
@@ -93,7 +95,9 @@ def batch_sharded_backward(
         dinit = torch.empty(x.shape[0], width - 1, dim, device=x.device, dtype=x.dtype).transpose(1, 2)
     run(x, weight, bias, dout, seq_idx, initial_states, dfinal_states, dx, dweight32, dbias32, dinit,
         activation is not None)
-    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+    if reducer is not None:
+        reducer.reduce_(packed)
+    elif dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
     dweight = dweight32.to(weight.dtype)
     dbias = dbias32.to(bias.dtype) if bias is not None else None
@@ -222,3 +226,58 @@ def sequence_parallel_backward(
     dweight = dweight32.to(weight.dtype)
     dbias = dbias32.to(bias.dtype) if bias is not None else None
     return dx, dweight, dbias, (dhalo if rank == 0 and return_dinitial_states else None)
+
+
+# ---- one-shot all-reduce of the packed gradient buffer over NVLink peer memory ------------------
+class PeerGradReducer:
+    """Sum of the packed fp32 gradient buffer over the ranks of ``group`` in ONE kernel per rank
+    (``cc1d_peer_allreduce``): every rank stores its vector into every peer's exchange buffer
+    over NVLink, flags it, waits (bounded) for the others and adds them in rank order — the same
+    bits on every rank, a few microseconds instead of a ring's latency.  The exchange buffers are
+    peer-mapped allocations of PyTorch's symmetric memory; only plain peer stores cross NVLink
+    (no multicast, no peer loads).
+
+    ``reduce_(buf)`` sums ``buf`` in place (float32, numel <= count).  A peer that never shows up
+    makes the kernel give up after about half a second and set a status word instead of hanging;
+    ``check()`` (synchronises) raises if that ever happened.
+    """
+
+    def __init__(self, count: int, group: Optional[dist.ProcessGroup] = None, device=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from causal_conv1d_b200._ext import ext
+
+        self._ext = ext
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.count = (int(count) + 3) // 4 * 4
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        nbytes = ext.peer_allreduce_buffer_bytes(self.world, self.count)
+        self._exchange = symm_mem.empty(nbytes // 4, dtype=torch.float32, device=device)
+        self._exchange.zero_()
+        self._handle = symm_mem.rendezvous(self._exchange, self.group)
+        self._peer_ptrs = [int(p) for p in self._handle.buffer_ptrs]
+        self._staging = torch.zeros(self.count, dtype=torch.float32, device=device)
+        self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)          # every rank's buffer is zeroed before anyone writes into it
+
+    def reduce_(self, buf: torch.Tensor) -> torch.Tensor:
+        n = buf.numel()
+        if buf.dtype != torch.float32 or n > self.count:
+            raise ValueError("buf must be float32 with at most `count` elements")
+        self._epoch += 1
+        direct = n == self.count and buf.is_contiguous() and buf.data_ptr() % 16 == 0
+        work = buf if direct else self._staging
+        if not direct:
+            work[:n].copy_(buf.reshape(-1))
+        self._ext.peer_allreduce(work, self._peer_ptrs, self.rank, self._epoch, self._status)
+        if not direct:
+            buf.copy_(work[:n].view_as(buf))
+        return buf
+
+    def check(self) -> None:
+        if int(self._status.item()) != 0:
+            raise RuntimeError("cc1d_peer_allreduce: a rank did not arrive within the wait limit")

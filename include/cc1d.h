@@ -274,6 +274,38 @@ int cc1d_seq_idx_from_cu_seqlens(const int32_t *cu_seqlens, int64_t nseq, int64_
 /* Human-readable text for a status code (static storage, never NULL). */
 const char *cc1d_status_str(int status);
 
+/* ---------------------------------------------------------------------------
+ * One-shot all-reduce (sum) of a small fp32 vector over NVLink peer memory — the
+ * exchange step of the batch-sharded backward (dweight | dbias of all ranks).  No
+ * counterpart in the reference, which has no multi-GPU code.
+ *
+ * Every rank calls it with the same world, count and epoch (1, 2, 3, ... one per
+ * collective, never 0) and its own rank.  peer_base[r] is the address, valid on THIS
+ * device, of rank r's exchange buffer: cc1d_peer_allreduce_buffer_bytes(world, count)
+ * bytes of peer-mapped device memory per rank, zero-filled once before the first call
+ * and not touched by anything else.  The kernel stores this rank's vector into every
+ * rank's buffer, raises per-slice flags, waits (bounded) for all ranks' flags in its own
+ * buffer and adds the vectors in rank order, so all ranks end with the same bits.
+ * dst may equal src.  count must be a multiple of 4; src and dst 16-byte aligned.
+ * If a wait runs out (a peer never arrived) *status is set to 1 and dst keeps its old
+ * contents; the call itself still returns CC1D_OK (it cannot know).  Calls of one
+ * communicator must be ordered on each rank.
+ * ------------------------------------------------------------------------- */
+#define CC1D_MAX_PEERS 16
+typedef struct cc1d_peer_allreduce_params {
+    int32_t world, rank;
+    uint32_t epoch;
+    int32_t reserved0;
+    int64_t count;
+    const float *src;
+    float *dst;
+    void *peer_base[CC1D_MAX_PEERS];
+    int32_t *status;              /* device int32, zero-filled by the caller */
+} cc1d_peer_allreduce_params;
+
+size_t cc1d_peer_allreduce_buffer_bytes(int32_t world, int64_t count);
+int cc1d_peer_allreduce(const cc1d_peer_allreduce_params *p, cc1d_stream_t stream);
+
 /* Health check (no reference counterpart).  The TMA kernels wait on shared-memory barriers
  * with an iteration limit instead of forever; a wait that runs out makes the kernel stop early
  * and raise a device-side flag.  This call SYNCHRONISES the current device, returns 0 when no

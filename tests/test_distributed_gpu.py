@@ -65,6 +65,24 @@ def _worker(rank, world, port, ret):
         seam = (dx_s[:, :, -(W - 1):].float() - ref_dx[:, :, -(W - 1):].float()).abs()
         ok &= bool((seam <= 1e-2 * ref_dx[:, :, -(W - 1):].float().abs().clamp(min=1.0)).all())
         ok &= torch.allclose(dw_s, wr.grad, rtol=1e-5, atol=1e-4) and torch.allclose(db_s, br.grad, rtol=1e-5, atol=1e-4)
+        # one-shot all-reduce over peer memory against NCCL, several epochs (both parities)
+        from causal_conv1d_b200.distributed import PeerGradReducer
+        red = PeerGradReducer(D * W + D)
+        for step in range(5):
+            torch.manual_seed(100 + step * world + rank)
+            part = torch.randn(D * W + D, device=dev)
+            want = part.clone()
+            dist.all_reduce(want)
+            got = red.reduce_(part.clone())
+            ok &= torch.allclose(got, want, rtol=1e-6, atol=1e-6)
+            both = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(both, got)
+            ok &= all(torch.equal(both[0], g) for g in both)                     # same bits on every rank
+        red.check()
+        dx_p, dw_p, db_p, _, _ = batch_sharded_backward(batch_shard(x, rank, world), w, b, batch_shard(dout, rank, world),
+                                                        activation="silu", reducer=red)
+        ok &= torch.equal(dx_p, dx) and torch.allclose(dw_p, dw, rtol=1e-6, atol=1e-6) and torch.allclose(db_p, db, rtol=1e-6, atol=1e-6)
+        red.check()
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()

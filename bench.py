@@ -240,6 +240,10 @@ def run_b200(args):
     # two packed gradient buffers: the all-reduce of step i runs (async) under step i+1's kernels
     grads = [packed_grad_buffer(DIM, WIDTH, True, dev) for _ in range(2)]
     pending = [None, None]
+    reducer = None
+    if world > 1 and args.allreduce == "peer":
+        from causal_conv1d_b200.distributed import PeerGradReducer
+        reducer = PeerGradReducer(grads[0][0].numel())
 
     def step(i, evs=None):
         x, dout, out, dx = sets[i % nsets]
@@ -255,7 +259,9 @@ def run_b200(args):
         ext.causal_conv1d_bwd(x, weight, bias, dout, None, None, None, dx, dweight, dbias, None, True, False)
         if evs is not None:
             evs[2].record()
-        if world > 1:
+        if reducer is not None:
+            reducer.reduce_(packed)          # one kernel in the same stream
+        elif world > 1:
             pending[i % 2] = dist.all_reduce(packed, async_op=True)
 
     def drain():
@@ -375,6 +381,37 @@ def run_b200(args):
     h2d = hx.numel() * ELEM + hdout.numel() * ELEM
     d2h = hout.numel() * ELEM + hdx.numel() * ELEM + hdw.numel() * ELEM + hdb.numel() * ELEM
 
+    # ---- the exchange step alone: NCCL all-reduce vs the one-shot peer-memory kernel --------------
+    allreduce_us = None
+    if world > 1:
+        allreduce_us = {"bytes": grads[0][0].numel() * 4}
+        probe = torch.randn(grads[0][0].numel(), device=dev)
+
+        def timed(fn, n=200):
+            for _ in range(10):
+                fn()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / n * 1e3], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return round(float(t.item()), 2)
+
+        allreduce_us["nccl"] = timed(lambda: dist.all_reduce(probe))
+        try:
+            from causal_conv1d_b200.distributed import PeerGradReducer
+            red = reducer if reducer is not None else PeerGradReducer(probe.numel())
+            allreduce_us["peer_memory_kernel"] = timed(lambda: red.reduce_(probe))
+            red.check()
+        except Exception as e:   # symmetric memory unavailable on this box: report, keep the bench line
+            allreduce_us["peer_memory_kernel"] = None
+            allreduce_us["peer_memory_kernel_error"] = f"{type(e).__name__}: {e}"[:200]
+
     if rank == 0:
         peak, peak_src = measured_peak()
         bwd_gbs = bwd_b / (bwd_ms * 1e-3) / 1e9
@@ -397,6 +434,8 @@ def run_b200(args):
                         "bwd": {"gbs": round(bwd_gbs, 1), "ms": round(bwd_ms, 5), "frac": round(bwd_gbs / peak, 4)}},
             "tokens_per_s": round(B * world * SEQLEN / (ms_per_step * 1e-3), 1),
         }
+        if allreduce_us is not None:
+            line["allreduce_us"] = allreduce_us
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line), flush=True)
@@ -574,6 +613,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the ~12 s CPU-port timing")
     ap.add_argument("--buffer-sets", type=int, default=3, help="rotating input/output sets (profiling: 1)")
     ap.add_argument("--skip-e2e", action="store_true", help="kernel loop only (for ncu captures)")
+    ap.add_argument("--allreduce", default="nccl", choices=["nccl", "peer"],
+                    help="N > 1: NCCL all-reduce overlapped with the next step (default), or the one-shot peer-memory kernel in-stream")
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c3p", "c4"],
                     help="c2 (default, the headline line); c3: packed varlen channel-last prefill fwd+bwd; "
                          "c3p: the same pack as a serving prefill with per-sequence conv states; c4: decode update")

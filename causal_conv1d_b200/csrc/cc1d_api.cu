@@ -143,7 +143,7 @@ size_t cc1d_peer_allreduce_buffer_bytes(int32_t world, int64_t count) { return p
 
 int cc1d_peer_allreduce(const cc1d_peer_allreduce_params *p, cc1d_stream_t stream) {
     if (p == nullptr) return CC1D_ERR_NULL;
-    if (p->world < 1 || p->world > CC1D_MAX_PEERS || p->rank < 0 || p->rank >= p->world || p->count < 0 || p->epoch == 0)
+    if (p->world < 1 || p->world > CC1D_MAX_PEERS || p->rank < 0 || p->rank >= p->world || p->count < 0)
         return CC1D_ERR_SHAPE;
     if (p->count % 4 != 0) return CC1D_ERR_ALIGN;
     if (p->status == nullptr) return CC1D_ERR_NULL;

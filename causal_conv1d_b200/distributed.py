@@ -260,7 +260,6 @@ class PeerGradReducer:
         self._peer_ptrs = [int(p) for p in self._handle.buffer_ptrs]
         self._staging = torch.zeros(self.count, dtype=torch.float32, device=device)
         self._status = torch.zeros(1, dtype=torch.int32, device=device)
-        self._epoch = 0
         torch.cuda.synchronize(device)
         dist.barrier(self.group)          # every rank's buffer is zeroed before anyone writes into it
 
@@ -268,12 +267,12 @@ class PeerGradReducer:
         n = buf.numel()
         if buf.dtype != torch.float32 or n > self.count:
             raise ValueError("buf must be float32 with at most `count` elements")
-        self._epoch += 1
         direct = n == self.count and buf.is_contiguous() and buf.data_ptr() % 16 == 0
         work = buf if direct else self._staging
         if not direct:
             work[:n].copy_(buf.reshape(-1))
-        self._ext.peer_allreduce(work, self._peer_ptrs, self.rank, self._epoch, self._status)
+        # epoch 0: the kernel numbers the collectives itself, so the call can be replayed in a CUDA graph
+        self._ext.peer_allreduce(work, self._peer_ptrs, self.rank, 0, self._status)
         if not direct:
             buf.copy_(work[:n].view_as(buf))
         return buf

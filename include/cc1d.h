@@ -279,17 +279,19 @@ const char *cc1d_status_str(int status);
  * exchange step of the batch-sharded backward (dweight | dbias of all ranks).  No
  * counterpart in the reference, which has no multi-GPU code.
  *
- * Every rank calls it with the same world, count and epoch (1, 2, 3, ... one per
- * collective, never 0) and its own rank.  peer_base[r] is the address, valid on THIS
+ * Every rank calls it with the same world and count, its own rank, and either the same
+ * explicit epoch (1, 2, 3, ... one per collective) or epoch 0 on every call: then the
+ * kernel numbers the collectives itself with a counter in the rank's exchange buffer,
+ * which makes a captured CUDA graph replayable (do not mix the two modes on one buffer).  peer_base[r] is the address, valid on THIS
  * device, of rank r's exchange buffer: cc1d_peer_allreduce_buffer_bytes(world, count)
  * bytes of peer-mapped device memory per rank, zero-filled once before the first call
- * and not touched by anything else.  The kernel stores this rank's vector into every
- * rank's buffer, raises per-slice flags, waits (bounded) for all ranks' flags in its own
- * buffer and adds the vectors in rank order, so all ranks end with the same bits.
+ * and not touched by anything else.  The kernel stores this rank's vector, stamped with
+ * the epoch, into every rank's buffer, polls (bounded) its own buffer for all ranks'
+ * vectors and adds them in rank order, so all ranks end with the same bits.
  * dst may equal src.  count must be a multiple of 4; src and dst 16-byte aligned.
- * If a wait runs out (a peer never arrived) *status is set to 1 and dst keeps its old
- * contents; the call itself still returns CC1D_OK (it cannot know).  Calls of one
- * communicator must be ordered on each rank.
+ * If a poll runs out (a peer never arrived) *status is set to 1 and dst is not valid;
+ * the call itself still returns CC1D_OK (it cannot know).  Calls of one communicator
+ * must be ordered on each rank.
  * ------------------------------------------------------------------------- */
 #define CC1D_MAX_PEERS 16
 typedef struct cc1d_peer_allreduce_params {

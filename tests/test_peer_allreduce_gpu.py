@@ -7,7 +7,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-FLAG_BYTES, MAX_PEERS, CTAS = 4096, 16, 8
+HEADER_BYTES, CTAS = 4096, 8
 
 
 def _ext():
@@ -17,16 +17,17 @@ def _ext():
 
 def _buffer(world, count):
     n = _ext().peer_allreduce_buffer_bytes(world, count)
-    assert n == FLAG_BYTES + 2 * world * count * 4
+    assert n == HEADER_BYTES + 2 * world * count * 8      # 16-byte lines of two values and two stamps
     return torch.zeros(n // 4, dtype=torch.float32, device="cuda")
 
 
 def _deliver(buf, world, count, parity, from_rank, vec, epoch):
     """What rank `from_rank`'s kernel leaves in a peer's exchange buffer."""
-    slots = buf[FLAG_BYTES // 4:].view(2, world, count)
-    slots[parity, from_rank] = vec
-    flags = buf[:FLAG_BYTES // 4].view(torch.int32)[: 2 * MAX_PEERS * CTAS].view(2, MAX_PEERS, CTAS)
-    flags[parity, from_rank] = epoch
+    lines = buf[HEADER_BYTES // 4:].view(torch.int32).view(2, world, count // 2, 4)
+    lines[parity, from_rank, :, 0] = vec[0::2].view(torch.int32)
+    lines[parity, from_rank, :, 2] = vec[1::2].view(torch.int32)
+    lines[parity, from_rank, :, 1] = epoch
+    lines[parity, from_rank, :, 3] = epoch
 
 
 @pytest.mark.parametrize("count", [4, 1000, 25600, 40964])
@@ -39,6 +40,27 @@ def test_world_of_one_is_identity(count):
         ext.peer_allreduce(v, [buf.data_ptr()], 0, epoch, status)
         assert torch.equal(v, want)
     assert int(status.item()) == 0
+
+
+def test_device_side_epoch_and_graph_replay():
+    """epoch 0: the kernel counts the collectives itself, so a captured graph can be replayed."""
+    ext = _ext()
+    count = 4096
+    buf, status = _buffer(1, count), torch.zeros(1, dtype=torch.int32, device="cuda")
+    v = torch.randn(count, device="cuda")
+    want = v.clone()
+    g, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(3):
+                ext.peer_allreduce(v, [buf.data_ptr()], 0, 0, status)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(4):
+        g.replay()
+    torch.cuda.synchronize()
+    calls = buf[: HEADER_BYTES // 4].view(torch.int32)[:CTAS]
+    assert calls.tolist() == [12] * CTAS and torch.equal(v, want) and int(status.item()) == 0
 
 
 def test_two_ranks_emulated_on_one_device():
@@ -64,7 +86,7 @@ def test_two_ranks_emulated_on_one_device():
 
 def test_wait_runs_out_instead_of_hanging():
     """A peer that never delivers: the kernel gives up after its bounded wait (about half a
-    second), raises the status word and leaves the destination untouched."""
+    second) and raises the status word (nothing of that peer arrived, so nothing is written)."""
     ext = _ext()
     world, count = 2, 1024
     bufs = [_buffer(world, count), _buffer(world, count)]
@@ -88,7 +110,5 @@ def test_rejects_bad_arguments():
     buf = _buffer(1, 8)
     with pytest.raises(RuntimeError):
         ext.peer_allreduce(torch.zeros(6, device="cuda"), [buf.data_ptr()], 0, 1, status)      # count % 4
-    with pytest.raises(RuntimeError):
-        ext.peer_allreduce(torch.zeros(8, device="cuda"), [buf.data_ptr()], 0, 0, status)      # epoch 0
     with pytest.raises(RuntimeError):
         ext.peer_allreduce(torch.zeros(8, device="cuda"), [buf.data_ptr()], 1, 1, status)      # rank >= world

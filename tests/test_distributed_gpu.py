@@ -118,3 +118,49 @@ def test_one_process_two_devices():
         res.append((out.detach().cpu(), x.grad.cpu(), w.grad.cpu(), b.grad.cpu()))
     for r in res[1:]:
         assert all(torch.equal(a, c) for a, c in zip(res[0], r))
+
+
+def _peer_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from causal_conv1d_b200.distributed import PeerGradReducer
+        ok = True
+        for count in (25600, 26880, 1000):          # C2 and C3 gradient buffers, and one that needs staging
+            red = PeerGradReducer(count)
+            for step in range(4):
+                torch.manual_seed(7 * step + rank)
+                part = torch.randn(count, device=dev)
+                want = part.clone()
+                dist.all_reduce(want)
+                got = red.reduce_(part.clone())
+                ok &= torch.allclose(got, want, rtol=1e-5, atol=1e-5)
+                every = [torch.empty_like(got) for _ in range(world)]
+                dist.all_gather(every, got)
+                ok &= all(torch.equal(every[0], g) for g in every)
+                # the fixed rank order of the additions, reproduced on the host
+                parts = [torch.empty_like(part) for _ in range(world)]
+                dist.all_gather(parts, part)
+                acc = parts[0].clone()
+                for p in parts[1:]:
+                    acc += p
+                ok &= torch.equal(got, acc)
+            red.check()
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_allreduce_on_all_visible_gpus():
+    """As many ranks as there are GPUs (2 to 8): same result as NCCL within fp32 rounding, the
+    same bits on every rank, and exactly the sum taken in rank order."""
+    world = min(torch.cuda.device_count(), 8)
+    if world < 2:
+        pytest.skip("needs 2 GPUs")
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ret = mp.Manager().dict()
+    mp.spawn(_peer_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert all(ret.get(r) is True for r in range(world))

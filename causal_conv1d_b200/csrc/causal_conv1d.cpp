@@ -125,7 +125,8 @@ void causal_conv1d_fwd(const at::Tensor &x, const at::Tensor &weight, const OptT
 void causal_conv1d_bwd(const at::Tensor &x, const at::Tensor &weight, const OptTensor &bias_, at::Tensor &dout,
                        const OptTensor &seq_idx_, const OptTensor &initial_states_, const OptTensor &dfinal_states_,
                        at::Tensor &dx, at::Tensor &dweight, OptTensor &dbias_, OptTensor &dinitial_states_,
-                       bool silu_activation, bool accumulate) {
+                       bool silu_activation, bool accumulate, const std::vector<int64_t> &peer_ptrs, int64_t peer_rank,
+                       int64_t peer_capacity, const OptTensor &peer_status_) {
     need_cuda(x, "x"); need_cuda(weight, "weight"); need_cuda(dout, "dout"); need_cuda(dx, "dx"); need_cuda(dweight, "dweight");
     TORCH_CHECK(bias_.has_value() == dbias_.has_value(), "dbias must be given exactly when bias is");
     const ConvDims d = conv_dims(x, weight);
@@ -193,6 +194,17 @@ void causal_conv1d_bwd(const at::Tensor &x, const at::Tensor &weight, const OptT
     at::Tensor ws = at::empty({(int64_t)ws_bytes}, x.options().dtype(at::kByte));
     p.workspace = ws.data_ptr();
     p.workspace_bytes = ws_bytes;
+    // ranks of a batch-sharded backward: the finishing kernel also sums dweight / dbias over them
+    cc1d_peer_group peers = {};
+    if (!peer_ptrs.empty()) {
+        TORCH_CHECK(peer_ptrs.size() <= CC1D_MAX_PEERS, "at most ", CC1D_MAX_PEERS, " peers");
+        TORCH_CHECK(peer_status_.has_value() && peer_status_->is_cuda() && peer_status_->scalar_type() == at::kInt,
+                    "peer_status must be an int32 CUDA tensor");
+        peers.world = (int32_t)peer_ptrs.size(); peers.rank = (int32_t)peer_rank; peers.capacity = peer_capacity;
+        for (size_t r = 0; r < peer_ptrs.size(); ++r) peers.peer_base[r] = reinterpret_cast<void *>(peer_ptrs[r]);
+        peers.status = peer_status_->data_ptr<int32_t>();
+        p.peers = &peers;
+    }
     raise_on(cc1d_bwd(&p, at::cuda::getCurrentCUDAStream().stream()), "causal_conv1d_bwd");
 }
 
@@ -369,7 +381,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("x"), py::arg("weight"), py::arg("bias"), py::arg("dout"), py::arg("seq_idx"),
           py::arg("initial_states"), py::arg("dfinal_states"), py::arg("dx"), py::arg("dweight"),
           py::arg("dbias"), py::arg("dinitial_states"), py::arg("silu_activation"),
-          py::arg("accumulate") = true);
+          py::arg("accumulate") = true, py::arg("peer_ptrs") = std::vector<int64_t>(), py::arg("peer_rank") = 0,
+          py::arg("peer_capacity") = 0, py::arg("peer_status") = py::none());
     m.def("causal_conv1d_update", &causal_conv1d_update, "Causal conv1d update");
     m.def("causal_conv1d_varlen_states", &causal_conv1d_varlen_states, "Last tokens of each packed sequence -> conv state");
     m.def("causal_conv1d_prefill_varlen", &causal_conv1d_prefill_varlen, "Packed varlen prefill with per-sequence conv states");

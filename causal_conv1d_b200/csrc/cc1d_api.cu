@@ -137,7 +137,7 @@ using namespace cc1d;
 
 extern "C" {
 
-int cc1d_abi_version(void) { return 2; }
+int cc1d_abi_version(void) { return 3; }
 
 size_t cc1d_peer_allreduce_buffer_bytes(int32_t world, int64_t count) { return peer_allreduce_buffer_bytes(world, count); }
 
@@ -223,6 +223,16 @@ static int check_bwd(const cc1d_bwd_params *p, bool *cl) {
     if (!*cl && (p->seq_idx || p->initial_states || p->dfinal_states || p->dinitial_states)) return CC1D_ERR_LAYOUT;
     if (p->initial_states && p->initial_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
     if (p->dinitial_states && p->dinitial_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
+    if (p->peers != nullptr) {
+        const cc1d_peer_group *g = p->peers;
+        if (g->world < 1 || g->world > CC1D_MAX_PEERS || g->rank < 0 || g->rank >= g->world) return CC1D_ERR_SHAPE;
+        if (g->capacity < p->dim * (int64_t)(p->width + 1)) return CC1D_ERR_SHAPE;
+        if (g->status == nullptr) return CC1D_ERR_NULL;
+        for (int r = 0; r < g->world; ++r) {
+            if (g->peer_base[r] == nullptr) return CC1D_ERR_NULL;
+            if (!is_aligned16(g->peer_base[r])) return CC1D_ERR_ALIGN;
+        }
+    }
     return CC1D_OK;
 }
 

@@ -30,6 +30,11 @@ struct ReduceArgs {
     int64_t n_inner, inner_stride;   // e.g. units per row
     int64_t chan_stride;
     int accumulate;
+    // exchange over peer memory (world == 0: none)
+    char *peer_base[CC1D_MAX_PEERS];
+    int *peer_status;
+    int64_t peer_capacity;
+    int world, rank;
 };
 
 // One warp per channel.  Lane l sums partial rows l, l+32, ... in ascending order, then a
@@ -65,9 +70,99 @@ __global__ void __launch_bounds__(128) reduce_partials_kernel(const ReduceArgs a
     }
 }
 
+// The same finishing reduction fused with the exchange between the ranks of a batch-sharded
+// backward: lane k of a channel's warp owns output k of that channel (taps 0..W-1, then the
+// bias); it stores {value, epoch} as one 8-byte line into slot [epoch & 1][rank] of EVERY rank's
+// exchange buffer (plain peer stores), then polls the world's slots in its own buffer until the
+// stamp equals the epoch (bounded) and adds the values in rank order.  No flag, no fence, no
+// read from peer memory.  The epoch of an element is one more than the newest stamp this rank
+// left at that element, so nothing has to count calls and a captured graph can be replayed.
+// Buffer: [header 4096 B][uint2 lines[2][world][capacity]].
+constexpr size_t kPeerHeaderBytesBwd = 4096;
+constexpr uint32_t kPeerSpinLimitBwd = 1u << 21;
+
+__device__ __forceinline__ uint2 *peer_lines8(char *base, uint32_t parity, int from_rank, int world, int64_t capacity) {
+    return reinterpret_cast<uint2 *>(base + kPeerHeaderBytesBwd) + ((int64_t)parity * world + from_rank) * capacity;
+}
+__device__ __forceinline__ uint2 ld_line8(const uint2 *p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_line8(uint2 *p, uint32_t value, uint32_t stamp) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" :: "l"(p), "r"(value), "r"(stamp) : "memory");
+}
+
+template <int W>
+__global__ void __launch_bounds__(128) reduce_partials_exchange_kernel(const ReduceArgs a) {
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t c = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (c >= a.dim) return;
+    float acc[W + 1];
+    #pragma unroll
+    for (int k = 0; k <= W; ++k) acc[k] = 0.f;
+    const int64_t n = a.n_outer * a.n_inner;
+    for (int64_t i = lane; i < n; i += 32) {
+        const int64_t o = i / a.n_inner, j = i - o * a.n_inner;
+        const float *p = a.ws + o * a.outer_stride + c * a.chan_stride + j * a.inner_stride;
+        #pragma unroll
+        for (int k = 0; k <= W; ++k) acc[k] += p[k];
+    }
+    #pragma unroll
+    for (int k = 0; k <= W; ++k) {
+        #pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc[k] += __shfl_xor_sync(kFullMask, acc[k], off);
+    }
+    if (lane > W) return;
+    float mine = acc[0];
+    #pragma unroll
+    for (int k = 1; k <= W; ++k) mine = lane == k ? acc[k] : mine;
+    const int64_t idx = c * (W + 1) + lane;
+
+    const uint32_t last0 = ld_line8(peer_lines8(a.peer_base[a.rank], 0, a.rank, a.world, a.peer_capacity) + idx).y;
+    const uint32_t last1 = ld_line8(peer_lines8(a.peer_base[a.rank], 1, a.rank, a.world, a.peer_capacity) + idx).y;
+    const uint32_t epoch = (last0 > last1 ? last0 : last1) + 1;
+    const uint32_t parity = epoch & 1u;
+    for (int r = 0; r < a.world; ++r)
+        st_line8(peer_lines8(a.peer_base[r], parity, a.rank, a.world, a.peer_capacity) + idx, __float_as_uint(mine), epoch);
+    float sum = 0.f;
+    for (int r = 0; r < a.world; ++r) {
+        const uint2 *p = peer_lines8(a.peer_base[a.rank], parity, r, a.world, a.peer_capacity) + idx;
+        uint2 line = ld_line8(p);
+        for (uint32_t it = 0; line.y != epoch && it < kPeerSpinLimitBwd; ++it) {
+            __nanosleep(it < 64 ? 20 : 250);
+            line = ld_line8(p);
+        }
+        if (line.y != epoch) {        // the peer never delivered: report and stop
+            *a.peer_status = 1;
+            return;
+        }
+        sum = r == 0 ? __uint_as_float(line.x) : sum + __uint_as_float(line.x);
+    }
+    if (lane < W) {
+        float *d = a.dweight + c * a.dw_cs + lane * a.dw_ws;
+        *d = a.accumulate ? *d + sum : sum;
+    } else if (a.dbias != nullptr) {
+        a.dbias[c] = a.accumulate ? a.dbias[c] + sum : sum;
+    }
+}
+
+static void set_peers(ReduceArgs &r, const cc1d_peer_group *g) {
+    r.world = 0; r.rank = 0; r.peer_status = nullptr; r.peer_capacity = 0;
+    for (int i = 0; i < CC1D_MAX_PEERS; ++i) r.peer_base[i] = nullptr;
+    if (g == nullptr) return;
+    r.world = g->world; r.rank = g->rank; r.peer_status = g->status; r.peer_capacity = g->capacity;
+    for (int i = 0; i < g->world && i < CC1D_MAX_PEERS; ++i) r.peer_base[i] = reinterpret_cast<char *>(g->peer_base[i]);
+}
+
 static int launch_reduce(const ReduceArgs &a, int width, cudaStream_t stream) {
     const unsigned grid = (unsigned)((a.dim + 3) / 4);
-    CC1D_DISPATCH_WIDTH(width, { launch_k(reduce_partials_kernel<W>, dim3(grid), dim3(128), 0, stream, a); });
+    if (a.world > 0) {
+        CC1D_DISPATCH_WIDTH(width, { launch_k(reduce_partials_exchange_kernel<W>, dim3(grid), dim3(128), 0, stream, a); });
+    } else {
+        CC1D_DISPATCH_WIDTH(width, { launch_k(reduce_partials_kernel<W>, dim3(grid), dim3(128), 0, stream, a); });
+    }
     return check_launch();
 }
 
@@ -524,6 +619,7 @@ int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream) {
     r.n_inner = (int64_t)pl.upr; r.inner_stride = p.width + 1;
     r.chan_stride = (int64_t)pl.upr * (p.width + 1);
     r.accumulate = p.accumulate;
+    set_peers(r, p.peers);
     if (p.dim == 0) return CC1D_OK;
     return launch_reduce(r, p.width, stream);
 }
@@ -1161,6 +1257,7 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
     r.n_inner = 1; r.inner_stride = 0;
     r.chan_stride = p.width + 1;
     r.accumulate = p.accumulate;
+    set_peers(r, p.peers);
     if (p.dim == 0) return CC1D_OK;
     if (p.seqlen == 0) r.n_outer = 0;
     return launch_reduce(r, p.width, stream);

@@ -52,9 +52,9 @@ def packed_grad_buffer(dim: int, width: int, has_bias: bool, device) -> tuple[to
 def _default_bwd():
     from causal_conv1d_b200._ext import ext
 
-    def run(x, weight, bias, dout, seq_idx, initial_states, dfinal_states, dx, dweight, dbias, dinitial_states, silu):
+    def run(x, weight, bias, dout, seq_idx, initial_states, dfinal_states, dx, dweight, dbias, dinitial_states, silu, **peer):
         ext.causal_conv1d_bwd(x, weight, bias, dout, seq_idx, initial_states, dfinal_states, dx, dweight, dbias,
-                              dinitial_states, silu, False)
+                              dinitial_states, silu, False, **peer)
 
     return run
 
@@ -75,8 +75,9 @@ def batch_sharded_backward(
     reducer: Optional["PeerGradReducer"] = None,
 ):
     """Backward of this rank's batch shard followed by the single all-reduce of the packed
-    fp32 weight gradients (NCCL/gloo ``all_reduce``, or ``reducer.reduce_`` when a
-    ``PeerGradReducer`` is given).  ``x`` / ``dout`` / states are the LOCAL shards; weight and bias
+    fp32 weight gradients (NCCL/gloo ``all_reduce``; ``reducer.reduce_`` when a
+    ``PeerGradReducer`` is given; inside the backward's own finishing kernel when that reducer
+    was created with ``fused=True``).  ``x`` / ``dout`` / states are the LOCAL shards; weight and bias
     are replicated.  Returns (dx, dweight, dbias, dinitial_states, packed_fp32) with
     dweight/dbias cast to the weight dtype after the reduction.
 
@@ -93,9 +94,14 @@ def batch_sharded_backward(
     dinit = None
     if return_dinitial_states:
         dinit = torch.empty(x.shape[0], width - 1, dim, device=x.device, dtype=x.dtype).transpose(1, 2)
+    fused = reducer is not None and reducer.fused
+    if fused and bwd_impl is not None:
+        raise ValueError("a fused reducer needs the CUDA extension's backward")
     run(x, weight, bias, dout, seq_idx, initial_states, dfinal_states, dx, dweight32, dbias32, dinit,
-        activation is not None)
-    if reducer is not None:
+        activation is not None, **(reducer.backward_args() if fused else {}))
+    if fused:
+        pass                                 # dweight32 / dbias32 already hold the sum over all ranks
+    elif reducer is not None:
         reducer.reduce_(packed)
     elif dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
@@ -242,12 +248,15 @@ class PeerGradReducer:
     ``check()`` (synchronises) raises if that ever happened.
     """
 
-    def __init__(self, count: int, group: Optional[dist.ProcessGroup] = None, device=None):
+    def __init__(self, count: int, group: Optional[dist.ProcessGroup] = None, device=None, fused: bool = False):
         import torch.distributed._symmetric_memory as symm_mem
 
         from causal_conv1d_b200._ext import ext
 
         self._ext = ext
+        # fused: the exchange happens inside the backward's finishing kernel (see
+        # batch_sharded_backward); the buffer then belongs to that kernel and reduce_ is not available
+        self.fused = bool(fused)
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -263,7 +272,15 @@ class PeerGradReducer:
         torch.cuda.synchronize(device)
         dist.barrier(self.group)          # every rank's buffer is zeroed before anyone writes into it
 
+    def backward_args(self) -> dict:
+        """Keyword arguments that make ``ext.causal_conv1d_bwd`` sum dweight / dbias over the ranks."""
+        if not self.fused:
+            raise RuntimeError("this reducer was not created with fused=True")
+        return dict(peer_ptrs=self._peer_ptrs, peer_rank=self.rank, peer_capacity=self.count, peer_status=self._status)
+
     def reduce_(self, buf: torch.Tensor) -> torch.Tensor:
+        if self.fused:
+            raise RuntimeError("a fused reducer exchanges inside the backward kernel; use batch_sharded_backward")
         n = buf.numel()
         if buf.dtype != torch.float32 or n > self.count:
             raise ValueError("buf must be float32 with at most `count` elements")

@@ -83,6 +83,20 @@ typedef struct cc1d_fwd_params {
 
 int cc1d_fwd(const cc1d_fwd_params *p, cc1d_stream_t stream);
 
+/* Ranks that exchange their weight gradients inside cc1d_bwd (see cc1d_bwd_params.peers).
+ * peer_base[r]: address, valid on THIS device, of rank r's exchange buffer —
+ * cc1d_peer_allreduce_buffer_bytes(world, capacity) bytes of peer-mapped device memory per
+ * rank, zero-filled once, used by nothing else (in particular not by cc1d_peer_allreduce:
+ * the two lay their lines out differently).  capacity >= dim * (width + 1).  *status is set
+ * to 1 when a bounded wait for a peer runs out (dweight / dbias are then invalid). */
+#define CC1D_MAX_PEERS 16
+typedef struct cc1d_peer_group {
+    int32_t world, rank;
+    int64_t capacity;
+    void *peer_base[CC1D_MAX_PEERS];
+    int32_t *status;              /* device int32, zero-filled by the caller */
+} cc1d_peer_group;
+
 /* ---------------------------------------------------------------------------
  * Backward.  Replaces causal_conv1d_bwd() (csrc/causal_conv1d.cpp:260-463) and
  * its kernels (csrc/causal_conv1d_bwd.cu:53-259 channel-first, :329-589
@@ -126,6 +140,12 @@ typedef struct cc1d_bwd_params {
 
     void *workspace;          /* >= cc1d_bwd_workspace_bytes() bytes, 16-B aligned, need not be zeroed */
     size_t workspace_bytes;
+
+    /* NULL, or the ranks of a batch-sharded backward: the finishing kernel then also sums
+     * dweight / dbias over all ranks through peer memory (one kernel does the last local
+     * reduction and the exchange), every rank ending with the same bits.  No counterpart in
+     * the reference. */
+    const cc1d_peer_group *peers;
 } cc1d_bwd_params;
 
 /* Bytes of scratch cc1d_bwd needs for this problem (host-only arithmetic).
@@ -293,7 +313,6 @@ const char *cc1d_status_str(int status);
  * the call itself still returns CC1D_OK (it cannot know).  Calls of one communicator
  * must be ordered on each rank.
  * ------------------------------------------------------------------------- */
-#define CC1D_MAX_PEERS 16
 typedef struct cc1d_peer_allreduce_params {
     int32_t world, rank;
     uint32_t epoch;

@@ -31,7 +31,12 @@ class BwdParams(ctypes.Structure):
                 [("dweight", vp), ("dweight_c_stride", i64), ("dweight_width_stride", i64), ("dbias", vp),
                  ("accumulate", i32), ("reserved0", i32), ("seq_idx", vp), ("initial_states", vp)] +
                 _s3("initial_states") + [("dfinal_states", vp)] + _s3("dfinal_states") +
-                [("dinitial_states", vp)] + _s3("dinitial_states") + [("workspace", vp), ("workspace_bytes", sz)])
+                [("dinitial_states", vp)] + _s3("dinitial_states") + [("workspace", vp), ("workspace_bytes", sz),
+                                                                       ("peers", vp)])
+
+
+class PeerGroup(ctypes.Structure):
+    _fields_ = [("world", i32), ("rank", i32), ("capacity", i64), ("peer_base", vp * 16), ("status", vp)]
 
 
 class UpdateParams(ctypes.Structure):

@@ -22,7 +22,7 @@ def test_exports_every_declared_symbol(lib):
             "cc1d_status_str", "cc1d_abi_version"} <= set(names)
     for n in names:
         assert hasattr(lib, n), f"libcc1d.so does not export {n}"
-    assert lib.cc1d_abi_version() >= 1
+    assert lib.cc1d_abi_version() >= 3
 
 
 def test_struct_sizes_match_header():

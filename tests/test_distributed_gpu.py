@@ -83,6 +83,13 @@ def _worker(rank, world, port, ret):
                                                         activation="silu", reducer=red)
         ok &= torch.equal(dx_p, dx) and torch.allclose(dw_p, dw, rtol=1e-6, atol=1e-6) and torch.allclose(db_p, db, rtol=1e-6, atol=1e-6)
         red.check()
+        # the same exchange inside the backward's finishing kernel: one kernel less, same bits as the two-kernel path
+        fused = PeerGradReducer(D * W + D, fused=True)
+        for _ in range(3):
+            dx_f, dw_f, db_f, _, packed_f = batch_sharded_backward(batch_shard(x, rank, world), w, b, batch_shard(dout, rank, world),
+                                                                   activation="silu", reducer=fused)
+            ok &= torch.equal(dx_f, dx) and torch.equal(dw_f, dw_p) and torch.equal(db_f, db_p)
+        fused.check()
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()

@@ -112,3 +112,79 @@ def test_rejects_bad_arguments():
         ext.peer_allreduce(torch.zeros(6, device="cuda"), [buf.data_ptr()], 0, 1, status)      # count % 4
     with pytest.raises(RuntimeError):
         ext.peer_allreduce(torch.zeros(8, device="cuda"), [buf.data_ptr()], 1, 1, status)      # rank >= world
+
+
+# ---- the exchange fused into the backward's finishing kernel (cc1d_bwd_params.peers) --------------
+def _bwd_inputs(channel_last, B=3, D=72, L=257, W=4, dtype=torch.bfloat16):
+    mk = (lambda: torch.randn(B, L, D, device="cuda", dtype=dtype).transpose(1, 2)) if channel_last else \
+         (lambda: torch.randn(B, D, L, device="cuda", dtype=dtype))
+    return mk(), mk(), torch.randn(D, W, device="cuda"), torch.randn(D, device="cuda")
+
+
+def _bwd(x, dout, w, b, **peer):
+    dx = torch.empty_like(x)
+    dw, db = torch.empty_like(w), torch.empty_like(b)
+    _ext().causal_conv1d_bwd(x, w, b, dout, None, None, None, dx, dw, db, None, True, False, **peer)
+    return dx, dw, db
+
+
+def _lines8(buf, world, capacity):
+    return buf[HEADER_BYTES // 4:].view(torch.int32).view(2, world, capacity, 2)
+
+
+@pytest.mark.parametrize("channel_last", [False, True])
+def test_fused_exchange_world_of_one_is_the_plain_backward(channel_last):
+    torch.manual_seed(3)
+    x, dout, w, b = _bwd_inputs(channel_last)
+    cap = w.numel() + b.numel()
+    buf, status = _buffer(1, (cap + 3) // 4 * 4), torch.zeros(1, dtype=torch.int32, device="cuda")
+    peer = dict(peer_ptrs=[buf.data_ptr()], peer_rank=0, peer_capacity=(cap + 3) // 4 * 4, peer_status=status)
+    want = _bwd(x, dout, w, b)
+    for call in range(3):                              # the epoch advances by itself
+        got = _bwd(x, dout, w, b, **peer)
+        assert all(torch.equal(a, c) for a, c in zip(got, want)), f"call {call}"
+    stamps = _lines8(buf, 1, (cap + 3) // 4 * 4)[:, 0, :cap, 1]
+    assert sorted(stamps.max(dim=1).values.tolist()) == [2, 3] and int(status.item()) == 0
+    # replayable in a CUDA graph
+    g, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    outs = []
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            outs = _bwd(x, dout, w, b, **peer)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, c) for a, c in zip(outs, want)) and int(status.item()) == 0
+
+
+def test_fused_exchange_adds_what_a_peer_delivered():
+    torch.manual_seed(4)
+    x, dout, w, b = _bwd_inputs(False)
+    D, W = w.shape
+    cap = D * (W + 1)
+    bufs = [_buffer(2, cap), _buffer(2, cap)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    other = torch.randn(D, W + 1, device="cuda")       # rank 1's partial: taps 0..W-1, then the bias gradient
+    lines = _lines8(bufs[0], 2, cap)
+    lines[1, 1, :, 0] = other.reshape(-1).view(torch.int32)   # first collective: epoch 1, parity 1
+    lines[1, 1, :, 1] = 1
+    _, dw0, db0 = _bwd(x, dout, w, b)
+    _, dw, db = _bwd(x, dout, w, b, peer_ptrs=[bf.data_ptr() for bf in bufs], peer_rank=0, peer_capacity=cap, peer_status=status)
+    assert torch.equal(dw, dw0 + other[:, :W]) and torch.equal(db, db0 + other[:, W]) and int(status.item()) == 0
+    # what this rank left in the peer's buffer is its own partial, stamped 1
+    sent = _lines8(bufs[1], 2, cap)[1, 0]
+    assert torch.equal(sent[:, 0].view(torch.float32).view(D, W + 1)[:, :W], dw0) and (sent[:, 1] == 1).all()
+
+
+def test_fused_exchange_gives_up_when_the_peer_never_delivers():
+    torch.manual_seed(5)
+    x, dout, w, b = _bwd_inputs(True, B=1, D=64, L=40)
+    cap = w.numel() + b.numel()
+    bufs = [_buffer(2, cap), _buffer(2, cap)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    dx, _, _ = _bwd(x, dout, w, b, peer_ptrs=[bf.data_ptr() for bf in bufs], peer_rank=0, peer_capacity=cap, peer_status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1
+    assert torch.equal(dx, _bwd(x, dout, w, b)[0]), "dx does not depend on the exchange"

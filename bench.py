@@ -190,15 +190,20 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus):
+ALLREDUCE_TEXT = {
+    "nccl": "one NCCL all-reduce of packed fp32 dweight|dbias per step (async, overlapped with the next step's kernels)",
+    "peer": "one cc1d_peer_allreduce kernel per step on the packed fp32 dweight|dbias (NVLink peer stores, in-stream)",
+    "fused": "dweight|dbias exchanged through NVLink peer memory inside the backward's finishing kernel",
+}
+
+
+def workload_config(n_gpus, allreduce="nccl"):
     return {
         "workload": "C2 Mamba-1 2.8B-shape prefill fwd+bwd: x (8,5120,2048) bf16 channel-first per GPU, "
                     "weight (5120,4)+bias bf16, SiLU, dout N(0,1), seed 1",
         "batch_per_gpu": BATCH_PER_GPU, "global_batch": BATCH_PER_GPU * n_gpus, "dim": DIM, "seq_len": SEQLEN,
         "width": WIDTH, "activation": "silu",
-        "parallelism": f"batch-sharded dp{n_gpus}, one NCCL all-reduce of packed fp32 dweight|dbias per step "
-                       "(async, overlapped with the next step's kernels)"
-                       if n_gpus > 1 else "single GPU",
+        "parallelism": f"batch-sharded dp{n_gpus}, {ALLREDUCE_TEXT[allreduce]}" if n_gpus > 1 else "single GPU",
         "l2": "inputs larger than L2: 3 rotating buffer sets of 671 MB (x, dout, out, dx) per GPU",
     }
 
@@ -240,10 +245,14 @@ def run_b200(args):
     # two packed gradient buffers: the all-reduce of step i runs (async) under step i+1's kernels
     grads = [packed_grad_buffer(DIM, WIDTH, True, dev) for _ in range(2)]
     pending = [None, None]
-    reducer = None
+    reducer, peer_args = None, {}
     if world > 1 and args.allreduce == "peer":
         from causal_conv1d_b200.distributed import PeerGradReducer
         reducer = PeerGradReducer(grads[0][0].numel())
+    elif world > 1 and args.allreduce == "fused":
+        from causal_conv1d_b200.distributed import PeerGradReducer
+        fused_reducer = PeerGradReducer(grads[0][0].numel(), fused=True)
+        peer_args = fused_reducer.backward_args()    # the backward's finishing kernel does the exchange
 
     def step(i, evs=None):
         x, dout, out, dx = sets[i % nsets]
@@ -256,11 +265,13 @@ def run_b200(args):
         ext.causal_conv1d_fwd(x, weight, bias, None, None, out, None, True)
         if evs is not None:
             evs[1].record()
-        ext.causal_conv1d_bwd(x, weight, bias, dout, None, None, None, dx, dweight, dbias, None, True, False)
+        ext.causal_conv1d_bwd(x, weight, bias, dout, None, None, None, dx, dweight, dbias, None, True, False, **peer_args)
         if evs is not None:
             evs[2].record()
         if reducer is not None:
             reducer.reduce_(packed)          # one kernel in the same stream
+        elif peer_args:
+            pass                             # already summed over the ranks
         elif world > 1:
             pending[i % 2] = dist.all_reduce(packed, async_op=True)
 
@@ -406,6 +417,7 @@ def run_b200(args):
         try:
             from causal_conv1d_b200.distributed import PeerGradReducer
             red = reducer if reducer is not None else PeerGradReducer(probe.numel())
+            allreduce_us["mode_of_the_timed_steps"] = args.allreduce
             allreduce_us["peer_memory_kernel"] = timed(lambda: red.reduce_(probe))
             red.check()
         except Exception as e:   # symmetric memory unavailable on this box: report, keep the bench line
@@ -419,7 +431,7 @@ def run_b200(args):
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(Wm, 3),
             "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(world, args.allreduce),
             "clocks": clocks.summary(),
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": k_e2e, "api": "causal_conv1d_fn + autograd backward, pinned host tensors; copy-in / kernels / copy-out of "
@@ -613,8 +625,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the ~12 s CPU-port timing")
     ap.add_argument("--buffer-sets", type=int, default=3, help="rotating input/output sets (profiling: 1)")
     ap.add_argument("--skip-e2e", action="store_true", help="kernel loop only (for ncu captures)")
-    ap.add_argument("--allreduce", default="nccl", choices=["nccl", "peer"],
-                    help="N > 1: NCCL all-reduce overlapped with the next step (default), or the one-shot peer-memory kernel in-stream")
+    ap.add_argument("--allreduce", default="nccl", choices=["nccl", "peer", "fused"],
+                    help="N > 1: NCCL all-reduce overlapped with the next step (default); the one-shot peer-memory kernel "
+                         "in-stream; or the exchange fused into the backward's finishing kernel")
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c3p", "c4"],
                     help="c2 (default, the headline line); c3: packed varlen channel-last prefill fwd+bwd; "
                          "c3p: the same pack as a serving prefill with per-sequence conv states; c4: decode update")

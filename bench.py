@@ -33,7 +33,7 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch of the backward kernel from the ncu capture summarised in
 # profiles/ (None until captured).
-BWD_KERNEL_DRAM_TRAFFIC_BYTES = 335623424 + 125170432   # dram__bytes_read.sum + dram__bytes_write.sum (write-back of
+BWD_KERNEL_DRAM_TRAFFIC_BYTES = 335684096 + 133846016   # dram__bytes_read.sum + dram__bytes_write.sum (write-back of
 # the last ~42 MB of dx is still pending in L2 when the counter stops)
 
 
@@ -205,6 +205,7 @@ def workload_config(n_gpus, allreduce="nccl"):
         "width": WIDTH, "activation": "silu",
         "parallelism": f"batch-sharded dp{n_gpus}, {ALLREDUCE_TEXT[allreduce]}" if n_gpus > 1 else "single GPU",
         "l2": "inputs larger than L2: 3 rotating buffer sets of 671 MB (x, dout, out, dx) per GPU",
+        "kernel_split": "CUDA events around the forward and the backward launches on every 8th step of the timed region",
     }
 
 
@@ -290,7 +291,12 @@ def run_b200(args):
     for i in range(max(Wm, 3)):
         step(i)
     barrier()
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    # Per-kernel durations come from events inside the timed region, on every EVENT_EVERY-th step
+    # only: an event record between two launches keeps the second kernel from being scheduled
+    # under the first one's tail (programmatic dependent launch), so instrumenting every step would
+    # slow down the very thing being timed.
+    EVENT_EVERY = 8
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] if i % EVENT_EVERY == 0 else None for i in range(K)]
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         start.record()
@@ -300,8 +306,9 @@ def run_b200(args):
         end.record()
         barrier()
     total_ms = start.elapsed_time(end)
-    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / K
-    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / K
+    sampled = [e for e in evs if e is not None]
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in sampled) / len(sampled)
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in sampled) / len(sampled)
     if world > 1:
         t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -192,7 +192,8 @@ def run_reference(args):
 
 ALLREDUCE_TEXT = {
     "nccl": "one NCCL all-reduce of packed fp32 dweight|dbias per step (async, overlapped with the next step's kernels)",
-    "peer": "one cc1d_peer_allreduce kernel per step on the packed fp32 dweight|dbias (NVLink peer stores, in-stream)",
+    "peer": "one cc1d_peer_allreduce kernel per step on the packed fp32 dweight|dbias (NVLink peer stores, on a side "
+            "stream beside the next step's kernels)",
     "fused": "dweight|dbias exchanged through NVLink peer memory inside the backward's finishing kernel",
 }
 
@@ -247,9 +248,11 @@ def run_b200(args):
     grads = [packed_grad_buffer(DIM, WIDTH, True, dev) for _ in range(2)]
     pending = [None, None]
     reducer, peer_args = None, {}
+    side, side_done = None, [None, None]
     if world > 1 and args.allreduce == "peer":
         from causal_conv1d_b200.distributed import PeerGradReducer
         reducer = PeerGradReducer(grads[0][0].numel())
+        side = torch.cuda.Stream()           # the exchange runs beside the next step's kernels, like the NCCL one
     elif world > 1 and args.allreduce == "fused":
         from causal_conv1d_b200.distributed import PeerGradReducer
         fused_reducer = PeerGradReducer(grads[0][0].numel(), fused=True)
@@ -261,6 +264,9 @@ def run_b200(args):
         if pending[i % 2] is not None:       # the buffer's previous all-reduce must be done before it is rewritten
             pending[i % 2].wait()
             pending[i % 2] = None
+        if side_done[i % 2] is not None:
+            torch.cuda.current_stream().wait_event(side_done[i % 2])
+            side_done[i % 2] = None
         if evs is not None:
             evs[0].record()
         ext.causal_conv1d_fwd(x, weight, bias, None, None, out, None, True)
@@ -270,7 +276,13 @@ def run_b200(args):
         if evs is not None:
             evs[2].record()
         if reducer is not None:
-            reducer.reduce_(packed)          # one kernel in the same stream
+            ready = torch.cuda.Event()
+            ready.record()
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                reducer.reduce_(packed)      # one kernel, on the side stream
+                side_done[i % 2] = torch.cuda.Event()
+                side_done[i % 2].record()
         elif peer_args:
             pass                             # already summed over the ranks
         elif world > 1:
@@ -278,6 +290,9 @@ def run_b200(args):
 
     def drain():
         for j in range(2):
+            if side_done[j] is not None:
+                torch.cuda.current_stream().wait_event(side_done[j])
+                side_done[j] = None
             if pending[j] is not None:
                 pending[j].wait()
                 pending[j] = None

@@ -416,7 +416,7 @@ def run_b200(args):
 
     # ---- the exchange step alone: NCCL all-reduce vs the one-shot peer-memory kernel --------------
     allreduce_us = None
-    if world > 1:
+    if world > 1 and (args.measure_allreduce or args.allreduce != "nccl"):
         allreduce_us = {"bytes": grads[0][0].numel() * 4}
         probe = torch.randn(grads[0][0].numel(), device=dev)
 
@@ -650,6 +650,8 @@ def main():
     ap.add_argument("--allreduce", default="nccl", choices=["nccl", "peer", "fused"],
                     help="N > 1: NCCL all-reduce overlapped with the next step (default); the one-shot peer-memory kernel "
                          "in-stream; or the exchange fused into the backward's finishing kernel")
+    ap.add_argument("--measure-allreduce", action="store_true",
+                    help="N > 1: also time the exchange step alone, NCCL against the peer-memory kernel (sets up symmetric memory)")
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c3p", "c4"],
                     help="c2 (default, the headline line); c3: packed varlen channel-last prefill fwd+bwd; "
                          "c3p: the same pack as a serving prefill with per-sequence conv states; c4: decode update")

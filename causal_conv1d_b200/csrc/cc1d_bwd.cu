@@ -753,11 +753,12 @@ __device__ __forceinline__ void bwd_cl_position_impl(
     for (int k = 0; k < W - 2; ++k) {
         #pragma unroll
         for (int c = 0; c < P; ++c) { xwin[k][c] = xwin[k + 1][c]; gwin[k][c] = gwin[k + 1][c]; }
-        swin[k] = swin[k + 1];
+        if (kMask) swin[k] = swin[k + 1];
     }
     #pragma unroll
     for (int c = 0; c < P; ++c) { xwin[W - 2][c] = xc[c]; gwin[W - 2][c] = gc[c]; }
-    swin[W - 2] = sid;
+    // unmasked code only ever runs when every id in the window already equals sid (or there are no ids)
+    if (kMask) swin[W - 2] = sid;
 }
 
 // seq_idx depends on (batch, token) only, so it is uniform across a warp.  Sequence
@@ -1070,20 +1071,18 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
         const T *dfin_base = (a.dfin != nullptr && lane_ok) ? reinterpret_cast<const T *>(a.dfin) + b * a.df_bs + (int64_t)col * C * a.df_cs : nullptr;
         T *dinit_base = want_dinit ? reinterpret_cast<T *>(a.dinit) + b * a.di_bs + (int64_t)col * C : nullptr;
 
-        int nsid[kTmaRows];   // sequence ids one stage ahead; -2 beyond the sequence (matches nothing)
-        #pragma unroll
-        for (int r = 0; r < kTmaRows; ++r) nsid[r] = (kSeqIdx && r < n_ld) ? sp[r] : -2;
+        // sequence ids one stage ahead, one per lane: lane l holds the id of row l % kTmaRows of the
+        // stage; -2 beyond the sequence (matches nothing)
+        const int myrow = tx & (kTmaRows - 1);
+        int next_id = (kSeqIdx && myrow < n_ld) ? sp[myrow] : -2;
 
         for (int st = 0; st < nst; ++st) {
             const int s = st % kBwdTmaStages;
             const int base = st * kTmaRows;
-            int sid[kTmaRows];
-            #pragma unroll
-            for (int r = 0; r < kTmaRows; ++r) {
-                sid[r] = nsid[r];
-                nsid[r] = (kSeqIdx && base + kTmaRows + r < n_ld) ? sp[kTmaRows + r] : -2;
-            }
-            if (!mbar_wait(bars + 8 * s, (uint32_t)(st / kBwdTmaStages) & 1u)) {
+            const int my_id = next_id;
+            next_id = (kSeqIdx && base + kTmaRows + myrow < n_ld) ? sp[kTmaRows + myrow] : -2;
+            // the warp decides together (the votes and shuffles below need all 32 lanes)
+            if (!__all_sync(kFullMask, mbar_wait(bars + 8 * s, (uint32_t)(st / kBwdTmaStages) & 1u))) {
                 g_tma_wait_expired = 1;     // never expected; stop consuming, still join the block reduction
                 break;
             }
@@ -1095,18 +1094,23 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
             // the stage carry the same non-negative sequence id, nothing is masked (warp-uniform)
             bool plain = steady;
             if (kSeqIdx) {
-                plain = plain && sid[0] >= 0;
+                const int first = __shfl_sync(kFullMask, my_id, 0);
+                bool same = my_id == first && first >= 0;
                 #pragma unroll
-                for (int k = 0; k < W - 1; ++k) plain = plain && swin[k] == sid[0];
+                for (int k = 0; k < W - 1; ++k) same = same && swin[k] == first;
+                plain = __all_sync(kFullMask, same) && plain;
+            }
+            int sid[kTmaRows];       // per-row ids: only the masked paths look at them
+            if (!plain) {
                 #pragma unroll
-                for (int r = 1; r < kTmaRows; ++r) plain = plain && sid[r] == sid[0];
+                for (int r = 0; r < kTmaRows; ++r) sid[r] = kSeqIdx ? __shfl_sync(kFullMask, my_id, r) : 0;
             }
             if (plain) {
                 #pragma unroll
                 for (int r = 0; r < kTmaRows; ++r) {
                     const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = lds_raw<R>(dsrc + r * kRowBytes);
                     bwd_cl_position_impl<T, W, C, kSilu, false, kTanh>(
-                        xr, dr, sid[r], true, lane_ok, false, xwin, gwin, swin, wv, wy, bv, dw, nullptr, 0, optr + r * os, nullptr);
+                        xr, dr, 0, true, lane_ok, false, xwin, gwin, swin, wv, wy, bv, dw, nullptr, 0, optr + r * os, nullptr);
                 }
             } else if (steady) {
                 #pragma unroll

@@ -241,11 +241,12 @@ __device__ __forceinline__ void fwd_cl_token_impl(const Raw<T, C> &raw, int sid,
     for (int k = 0; k < W - 2; ++k) {
         #pragma unroll
         for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
-        sw[k] = sw[k + 1];
+        if (kSeqIdx) sw[k] = sw[k + 1];
     }
     #pragma unroll
     for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
-    sw[W - 2] = sid;
+    // unmasked code only ever runs when every id in the window already equals sid (or there are no ids)
+    if (kSeqIdx) sw[W - 2] = sid;
 }
 
 // seq_idx depends on (batch, token) only, so it is uniform across a warp.  Sequence
@@ -448,20 +449,16 @@ __global__ void __launch_bounds__(32 * kTmaWarps) fwd_cl_tma_kernel(const FwdClA
         }
     }
 
-    // sequence ids of a box are fetched one box ahead, so that their latency hides behind a box
-    int nsid[kTmaRows];
-    #pragma unroll
-    for (int r = 0; r < kTmaRows; ++r) nsid[r] = (kSeqIdx && r < n) ? sp[r] : 0;
+    // sequence ids of a box are fetched one box ahead, so that their latency hides behind a box;
+    // one id per lane: lane l holds the id of row l % kTmaRows (-2 past the chunk: matches nothing)
+    const int myrow = lane & (kTmaRows - 1);
+    int next_id = (kSeqIdx && myrow < n) ? sp[myrow] : -2;
     for (int st = 0; st < nst; ++st) {
         const int s = st % kTmaStages;
         const int rows = n - st * kTmaRows;            // >= kTmaRows except in the last box
-        int sid[kTmaRows];
-        #pragma unroll
-        for (int r = 0; r < kTmaRows; ++r) {
-            sid[r] = nsid[r];
-            nsid[r] = (kSeqIdx && kTmaRows + r < rows) ? sp[kTmaRows + r] : 0;
-        }
-        if (!mbar_wait(bars + 8 * s, (uint32_t)(st / kTmaStages) & 1u)) {
+        const int my_id = next_id;
+        next_id = (kSeqIdx && kTmaRows + myrow < rows) ? sp[kTmaRows + myrow] : -2;
+        if (!__all_sync(kFullMask, mbar_wait(bars + 8 * s, (uint32_t)(st / kTmaStages) & 1u))) {   // the warp decides together
             g_tma_wait_expired = 1;                    // never expected; leave without touching more memory
             return;
         }
@@ -470,17 +467,22 @@ __global__ void __launch_bounds__(32 * kTmaWarps) fwd_cl_tma_kernel(const FwdClA
         // same non-negative sequence id needs no masking at all (warp-uniform branch)
         bool plain = rows >= kTmaRows;
         if (kSeqIdx) {
-            plain = plain && sid[0] >= 0;
+            const int first = __shfl_sync(kFullMask, my_id, 0);
+            bool same = my_id == first && first >= 0;
             #pragma unroll
-            for (int k = 0; k < W - 1; ++k) plain = plain && sw[k] == sid[0];
+            for (int k = 0; k < W - 1; ++k) same = same && sw[k] == first;
+            plain = __all_sync(kFullMask, same) && plain;
+        }
+        int sid[kTmaRows];       // per-row ids: only the masked paths look at them
+        if (!plain) {
             #pragma unroll
-            for (int r = 1; r < kTmaRows; ++r) plain = plain && sid[r] == sid[0];
+            for (int r = 0; r < kTmaRows; ++r) sid[r] = kSeqIdx ? __shfl_sync(kFullMask, my_id, r) : 0;
         }
         if (plain) {
             #pragma unroll
             for (int r = 0; r < kTmaRows; ++r) {
                 const R raw = lds128(src + r * kTmaRowBytes);
-                fwd_cl_token_impl<T, W, C, kSilu, false, kTanh>(raw, sid[r], win, sw, wv, bv, optr + r * os, lane_ok);
+                fwd_cl_token_impl<T, W, C, kSilu, false, kTanh>(raw, 0, win, sw, wv, bv, optr + r * os, lane_ok);
             }
         } else if (rows >= kTmaRows) {
             #pragma unroll

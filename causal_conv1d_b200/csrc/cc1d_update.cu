@@ -27,6 +27,21 @@ struct UpdArgs {
     uint32_t ncols, ncolblk;
 };
 
+// element c of a 16-byte vector as fp32
+template <typename T> __device__ __forceinline__ float elem_f(const uint4 &v, int c);
+template <> __device__ __forceinline__ float elem_f<float>(const uint4 &v, int c) {
+    return __uint_as_float(c == 0 ? v.x : c == 1 ? v.y : c == 2 ? v.z : v.w);
+}
+template <> __device__ __forceinline__ float elem_f<__nv_bfloat16>(const uint4 &v, int c) {
+    const uint32_t w = (c >> 1) == 0 ? v.x : (c >> 1) == 1 ? v.y : (c >> 1) == 2 ? v.z : v.w;
+    return __uint_as_float((c & 1) ? (w & 0xffff0000u) : (w << 16));
+}
+template <> __device__ __forceinline__ float elem_f<__half>(const uint4 &v, int c) {
+    const uint32_t w = (c >> 1) == 0 ? v.x : (c >> 1) == 1 ? v.y : (c >> 1) == 2 ? v.z : v.w;
+    const unsigned short h = (unsigned short)((c & 1) ? (w >> 16) : (w & 0xffffu));
+    return __half2float(*reinterpret_cast<const __half *>(&h));
+}
+
 // One thread: one 16-byte vector of channels of one batch entry.  The kernel is kept small
 // and straight (a decode step is latency-bound: instruction fetch, one index -> state-row
 // dependent load chain, no barrier): every load that does not depend on the state row index
@@ -83,11 +98,10 @@ __global__ void __launch_bounds__(128, 4) update_vec_kernel(const UpdArgs a) {
             *reinterpret_cast<uint4 *>(sp + i * a.s_ls) = v;
         }
     }
-    float win[W - 1][C];
-    #pragma unroll
-    for (int k = 0; k < W - 1; ++k) unpack<T>(winraw[k], win[k]);
-
     if constexpr (kTok > 1) {
+        float win[W - 1][C];
+        #pragma unroll
+        for (int k = 0; k < W - 1; ++k) unpack<T>(winraw[k], win[k]);
         // tokens in chunks of kTok: all loads of a chunk are requested together (one round trip to
         // memory per chunk instead of one per token); token 0 is already here.  kTok == 1 is the
         // single-token decode step, which wants the smaller register footprint.
@@ -135,39 +149,23 @@ __global__ void __launch_bounds__(128, 4) update_vec_kernel(const UpdArgs a) {
             }
         }
     } else {
-        #pragma unroll 1
-        for (int i = 0; i < L; ++i) {
-            uint4 next = make_uint4(0, 0, 0, 0);
-            if (i + 1 < L) next = ld_stream(xp + (i + 1) * a.x_ls);
-            if (kCirc) {
-                *reinterpret_cast<uint4 *>(sp + wr * a.s_ls) = raw;
-                wr = wr + 1 >= S ? 0 : wr + 1;
-            } else if (!in_regs) {
-                const int r = S - L + i;
-                if (r >= 0) *reinterpret_cast<uint4 *>(sp + r * a.s_ls) = raw;
-            }
-            float cur[C], o[C];
-            unpack<T>(raw, cur);
+        // the single-token decode step (seqlen == 1): straight code, window elements converted where
+        // they are used, so that the thread holds the window only as raw vectors
+        if (kCirc) *reinterpret_cast<uint4 *>(sp + wr * a.s_ls) = raw;
+        else if (!in_regs) *reinterpret_cast<uint4 *>(sp + (S - 1) * a.s_ls) = raw;
+        float o[C];
+        #pragma unroll
+        for (int c = 0; c < C; ++c) {
+            float acc = bv[c];
             #pragma unroll
-            for (int c = 0; c < C; ++c) {
-                float acc = bv[c];
-                #pragma unroll
-                for (int k = 0; k < W - 1; ++k) acc = fmaf(wv[k][c], win[k][c], acc);
-                acc = fmaf(wv[W - 1][c], cur[c], acc);
-                o[c] = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
-            }
-            st_stream(op + i * a.o_ls, pack<T>(o));
-            #pragma unroll
-            for (int k = 0; k < W - 2; ++k) {
-                #pragma unroll
-                for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
-                winraw[k] = winraw[k + 1];
-            }
-            #pragma unroll
-            for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
-            winraw[W - 2] = raw;   // bit-exact copy for the state write-back
-            raw = next;
+            for (int k = 0; k < W - 1; ++k) acc = fmaf(wv[k][c], elem_f<T>(winraw[k], c), acc);
+            acc = fmaf(wv[W - 1][c], elem_f<T>(raw, c), acc);
+            o[c] = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
         }
+        st_stream(op, pack<T>(o));
+        #pragma unroll
+        for (int k = 0; k < W - 2; ++k) winraw[k] = winraw[k + 1];
+        winraw[W - 2] = raw;   // bit-exact copies for the state write-back
     }
     if (in_regs) {
         #pragma unroll

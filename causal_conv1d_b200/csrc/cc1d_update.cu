@@ -48,7 +48,7 @@ template <> __device__ __forceinline__ float elem_f<__half>(const uint4 &v, int 
 // (taps, first token, cache_seqlens) is issued before the index arrives; later tokens are
 // prefetched one ahead in a rolled loop.
 template <typename T, int W, bool kSilu, bool kCirc, int kTok>
-__global__ void __launch_bounds__(128, 4) update_vec_kernel(const UpdArgs a) {
+__global__ void __launch_bounds__(128, kTok == 1 ? 4 : 5) update_vec_kernel(const UpdArgs a) {
     pdl_wait();
     constexpr int C = Elem<T>::kVec;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
@@ -99,9 +99,6 @@ __global__ void __launch_bounds__(128, 4) update_vec_kernel(const UpdArgs a) {
         }
     }
     if constexpr (kTok > 1) {
-        float win[W - 1][C];
-        #pragma unroll
-        for (int k = 0; k < W - 1; ++k) unpack<T>(winraw[k], win[k]);
         // tokens in chunks of kTok: all loads of a chunk are requested together (one round trip to
         // memory per chunk instead of one per token); token 0 is already here.  kTok == 1 is the
         // single-token decode step, which wants the smaller register footprint.
@@ -125,25 +122,19 @@ __global__ void __launch_bounds__(128, 4) update_vec_kernel(const UpdArgs a) {
                         const int r = S - L + i;
                         if (r >= 0) *reinterpret_cast<uint4 *>(sp + r * a.s_ls) = cur_raw;
                     }
-                    float cur[C], o[C];
-                    unpack<T>(cur_raw, cur);
+                    // the window stays in raw vectors; elements are converted where they are used
+                    float o[C];
                     #pragma unroll
                     for (int c = 0; c < C; ++c) {
                         float acc = bv[c];
                         #pragma unroll
-                        for (int k = 0; k < W - 1; ++k) acc = fmaf(wv[k][c], win[k][c], acc);
-                        acc = fmaf(wv[W - 1][c], cur[c], acc);
+                        for (int k = 0; k < W - 1; ++k) acc = fmaf(wv[k][c], elem_f<T>(winraw[k], c), acc);
+                        acc = fmaf(wv[W - 1][c], elem_f<T>(cur_raw, c), acc);
                         o[c] = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
                     }
                     st_stream(op + i * a.o_ls, pack<T>(o));
                     #pragma unroll
-                    for (int k = 0; k < W - 2; ++k) {
-                        #pragma unroll
-                        for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
-                        winraw[k] = winraw[k + 1];
-                    }
-                    #pragma unroll
-                    for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
+                    for (int k = 0; k < W - 2; ++k) winraw[k] = winraw[k + 1];
                     winraw[W - 2] = cur_raw;   // bit-exact copy for the state write-back
                 }
             }

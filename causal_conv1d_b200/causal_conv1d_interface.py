@@ -1,6 +1,8 @@
 """Public API: ``causal_conv1d_fn``, ``CausalConv1dFn`` and ``causal_conv1d_update`` with
 the signatures, argument normalisation and error behaviour of the reference
-(``causal_conv1d/causal_conv1d_interface.py:9-129,174-202``)."""
+(``causal_conv1d/causal_conv1d_interface.py:9-129,174-202``).  ``causal_conv1d_ref`` and
+``causal_conv1d_update_ref`` (``:132-171,205-242``), the PyTorch statements callers compare
+against, are re-exported from ``torch_reference``; the CUDA entry points never call them."""
 import torch
 
 from causal_conv1d_b200.cpp_functions import (
@@ -8,6 +10,7 @@ from causal_conv1d_b200.cpp_functions import (
     causal_conv1d_fwd_function,
     causal_conv1d_update_function,
 )
+from causal_conv1d_b200.torch_reference import causal_conv1d_ref, causal_conv1d_update_ref  # noqa: F401
 
 _ACTIVATIONS = (None, "silu", "swish")
 

@@ -1,5 +1,6 @@
 """``causal_conv1d_varlen_states`` — same signature as the reference's Triton-backed
-function (``causal_conv1d/causal_conv1d_varlen.py:35-64``), served by a CUDA kernel."""
+function (``causal_conv1d/causal_conv1d_varlen.py:35-64``), served by a CUDA kernel.
+``causal_conv1d_varlen_states_ref`` (``:67-86``) is re-exported from ``torch_reference``."""
 from torch import Tensor
 
 from causal_conv1d_b200.cpp_functions import (
@@ -7,6 +8,7 @@ from causal_conv1d_b200.cpp_functions import (
     causal_conv1d_varlen_states_function,
     seq_idx_from_cu_seqlens_function,
 )
+from causal_conv1d_b200.torch_reference import causal_conv1d_varlen_states_ref  # noqa: F401
 
 
 def causal_conv1d_varlen_states(x: Tensor, cu_seqlens: Tensor, state_len: int) -> Tensor:

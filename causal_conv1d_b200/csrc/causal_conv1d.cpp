@@ -126,7 +126,8 @@ void causal_conv1d_bwd(const at::Tensor &x, const at::Tensor &weight, const OptT
                        const OptTensor &seq_idx_, const OptTensor &initial_states_, const OptTensor &dfinal_states_,
                        at::Tensor &dx, at::Tensor &dweight, OptTensor &dbias_, OptTensor &dinitial_states_,
                        bool silu_activation, bool accumulate, const std::vector<int64_t> &peer_ptrs, int64_t peer_rank,
-                       int64_t peer_capacity, const OptTensor &peer_status_) {
+                       int64_t peer_capacity, const OptTensor &peer_status_, int64_t peer_spin_limit, int64_t phase,
+                       const OptTensor &workspace_) {
     need_cuda(x, "x"); need_cuda(weight, "weight"); need_cuda(dout, "dout"); need_cuda(dx, "dx"); need_cuda(dweight, "dweight");
     TORCH_CHECK(bias_.has_value() == dbias_.has_value(), "dbias must be given exactly when bias is");
     const ConvDims d = conv_dims(x, weight);
@@ -189,11 +190,23 @@ void causal_conv1d_bwd(const at::Tensor &x, const at::Tensor &weight, const OptT
         p.dinitial_states_batch_stride = s.stride(0); p.dinitial_states_c_stride = s.stride(1); p.dinitial_states_l_stride = s.stride(2);
     }
     c10::cuda::CUDAGuard guard(x.device());
-    // scratch for the fixed-order dweight/dbias reduction, from torch's caching allocator
+    // scratch for the fixed-order dweight/dbias reduction: the caller's (it must outlive a
+    // backward split into phases), else from torch's caching allocator
+    TORCH_CHECK(phase >= 0 && phase <= 2, "phase must be 0, 1 or 2");
+    TORCH_CHECK(phase == 0 || workspace_.has_value(), "a backward split into phases needs a caller-provided workspace");
     const size_t ws_bytes = cc1d_bwd_workspace_bytes(&p);
-    at::Tensor ws = at::empty({(int64_t)ws_bytes}, x.options().dtype(at::kByte));
+    at::Tensor ws;
+    if (workspace_.has_value()) {
+        ws = *workspace_;
+        need_cuda(ws, "workspace");
+        TORCH_CHECK(ws.is_contiguous() && (size_t)ws.nbytes() >= ws_bytes, "workspace must be contiguous and hold ",
+                    ws_bytes, " bytes");
+    } else {
+        ws = at::empty({(int64_t)ws_bytes}, x.options().dtype(at::kByte));
+    }
     p.workspace = ws.data_ptr();
-    p.workspace_bytes = ws_bytes;
+    p.workspace_bytes = (size_t)ws.nbytes();
+    p.phase = (int32_t)phase;
     // ranks of a batch-sharded backward: the finishing kernel also sums dweight / dbias over them
     cc1d_peer_group peers = {};
     if (!peer_ptrs.empty()) {
@@ -203,6 +216,8 @@ void causal_conv1d_bwd(const at::Tensor &x, const at::Tensor &weight, const OptT
         peers.world = (int32_t)peer_ptrs.size(); peers.rank = (int32_t)peer_rank; peers.capacity = peer_capacity;
         for (size_t r = 0; r < peer_ptrs.size(); ++r) peers.peer_base[r] = reinterpret_cast<void *>(peer_ptrs[r]);
         peers.status = peer_status_->data_ptr<int32_t>();
+        TORCH_CHECK(peer_spin_limit >= 0 && peer_spin_limit <= 0xffffffffll, "peer_spin_limit out of range");
+        peers.spin_limit = (uint32_t)peer_spin_limit;
         p.peers = &peers;
     }
     raise_on(cc1d_bwd(&p, at::cuda::getCurrentCUDAStream().stream()), "causal_conv1d_bwd");
@@ -360,13 +375,16 @@ void seq_idx_from_cu_seqlens(const at::Tensor &cu_seqlens, at::Tensor &seq_idx) 
 
 // One-shot peer all-reduce of a small fp32 vector (cc1d_peer_allreduce); peer_ptrs[r] is rank r's
 // exchange buffer as mapped on this device.
-void peer_allreduce(at::Tensor &buf, const std::vector<int64_t> &peer_ptrs, int64_t rank, int64_t epoch, at::Tensor &status) {
+void peer_allreduce(at::Tensor &buf, const std::vector<int64_t> &peer_ptrs, int64_t rank, int64_t epoch, at::Tensor &status,
+                    int64_t spin_limit) {
     need_cuda(buf, "buf"); need_cuda(status, "status");
     TORCH_CHECK(buf.scalar_type() == at::kFloat && buf.is_contiguous(), "buf must be a contiguous float32 tensor");
     TORCH_CHECK(status.scalar_type() == at::kInt && status.numel() >= 1, "status must be an int32 tensor");
     TORCH_CHECK(peer_ptrs.size() >= 1 && peer_ptrs.size() <= CC1D_MAX_PEERS, "1..", CC1D_MAX_PEERS, " peers");
     cc1d_peer_allreduce_params p = {};
     p.world = (int32_t)peer_ptrs.size(); p.rank = (int32_t)rank; p.epoch = (uint32_t)epoch;
+    TORCH_CHECK(spin_limit >= 0 && spin_limit <= 0xffffffffll, "spin_limit out of range");
+    p.spin_limit = (uint32_t)spin_limit;
     p.count = buf.numel();
     p.src = buf.data_ptr<float>(); p.dst = buf.data_ptr<float>();
     for (size_t r = 0; r < peer_ptrs.size(); ++r) p.peer_base[r] = reinterpret_cast<void *>(peer_ptrs[r]);
@@ -382,12 +400,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("initial_states"), py::arg("dfinal_states"), py::arg("dx"), py::arg("dweight"),
           py::arg("dbias"), py::arg("dinitial_states"), py::arg("silu_activation"),
           py::arg("accumulate") = true, py::arg("peer_ptrs") = std::vector<int64_t>(), py::arg("peer_rank") = 0,
-          py::arg("peer_capacity") = 0, py::arg("peer_status") = py::none());
+          py::arg("peer_capacity") = 0, py::arg("peer_status") = py::none(), py::arg("peer_spin_limit") = 0,
+          py::arg("phase") = 0, py::arg("workspace") = py::none());
+    m.def("bwd_workspace_bytes", [](int64_t batch, int64_t dim, int64_t seqlen, int64_t width, int64_t elem_bytes, bool channel_last) {
+        cc1d_bwd_params q = {};
+        q.itype = elem_bytes == 4 ? CC1D_F32 : CC1D_BF16; q.wtype = CC1D_F32; q.width = (int32_t)width;
+        q.batch = batch; q.dim = dim; q.seqlen = seqlen;
+        q.x_c_stride = channel_last ? 1 : seqlen; q.x_l_stride = channel_last ? dim : 1;
+        return (int64_t)cc1d_bwd_workspace_bytes(&q);
+    }, "Bytes of scratch a backward of this shape needs (cc1d_bwd_workspace_bytes)");
     m.def("causal_conv1d_update", &causal_conv1d_update, "Causal conv1d update");
     m.def("causal_conv1d_varlen_states", &causal_conv1d_varlen_states, "Last tokens of each packed sequence -> conv state");
     m.def("causal_conv1d_prefill_varlen", &causal_conv1d_prefill_varlen, "Packed varlen prefill with per-sequence conv states");
     m.def("seq_idx_from_cu_seqlens", &seq_idx_from_cu_seqlens, "seq_idx of every packed token from cu_seqlens");
-    m.def("peer_allreduce", &peer_allreduce, "One-shot all-reduce of a small fp32 vector over peer memory");
+    m.def("peer_allreduce", &peer_allreduce, "One-shot all-reduce of a small fp32 vector over peer memory",
+          py::arg("buf"), py::arg("peer_ptrs"), py::arg("rank"), py::arg("epoch"), py::arg("status"), py::arg("spin_limit") = 0);
     m.def("peer_allreduce_buffer_bytes", [](int64_t world, int64_t count) { return (int64_t)cc1d_peer_allreduce_buffer_bytes((int32_t)world, count); });
     m.def("wait_expired", []() { return cc1d_wait_expired(); }, "Health check: non-zero if a bounded wait in a kernel ran out (synchronises)");
     m.def("abi_version", []() { return cc1d_abi_version(); });

@@ -13,12 +13,17 @@
 namespace cc1d {
 
 int num_sms() {
+    static std::mutex mu;
     static int cached[64] = {0};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::lock_guard<std::mutex> lock(mu);
     if (cached[dev] == 0) {
         int n = 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = 148;
+        }
         cached[dev] = n;
     }
     return cached[dev];
@@ -137,7 +142,7 @@ using namespace cc1d;
 
 extern "C" {
 
-int cc1d_abi_version(void) { return 3; }
+int cc1d_abi_version(void) { return 4; }
 
 size_t cc1d_peer_allreduce_buffer_bytes(int32_t world, int64_t count) { return peer_allreduce_buffer_bytes(world, count); }
 
@@ -180,6 +185,10 @@ const char *cc1d_status_str(int status) {
         case CC1D_ERR_TOO_LARGE: return "problem size exceeds an internal index range";
         case CC1D_ERR_LAUNCH: return "CUDA kernel launch failed";
         case CC1D_ERR_SCRATCH_LIMIT: return "problem needs more scratch than cc1d_bwd_noalloc has built in (CC1D_NOALLOC_SCRATCH_BYTES); use cc1d_bwd with a caller workspace";
+        case CC1D_ERR_SCRATCH_ADDRESS: return "cc1d_bwd_noalloc could not look up the address of its built-in scratch on this device";
+        case CC1D_ERR_CAPTURE: return "the first cc1d_bwd_noalloc call on a device must be made outside stream capture";
+        case CC1D_ERR_SEQ_IDX_STATES: return "seq_idx cannot be combined with initial_states / final_states (packed sequences with states: cc1d_prefill_varlen)";
+        case CC1D_ERR_PHASE: return "cc1d_bwd_params.phase must be 0 (whole backward), 1 (main kernel) or 2 (finishing kernel)";
         default: return "unknown cc1d status";
     }
 }
@@ -196,6 +205,7 @@ int cc1d_fwd(const cc1d_fwd_params *p, cc1d_stream_t stream) {
     rc = check_same_layout(cl, p->out_batch_stride, p->out_c_stride, p->out_l_stride, p->seqlen, p->dim, p->batch);
     if (rc != CC1D_OK) return rc;
     if (!cl && (p->seq_idx || p->initial_states || p->final_states)) return CC1D_ERR_LAYOUT;
+    if (p->seq_idx && (p->initial_states || p->final_states)) return CC1D_ERR_SEQ_IDX_STATES;
     if (p->initial_states && p->initial_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
     if (p->final_states && p->final_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -221,6 +231,8 @@ static int check_bwd(const cc1d_bwd_params *p, bool *cl) {
     rc = check_same_layout(*cl, p->dx_batch_stride, p->dx_c_stride, p->dx_l_stride, p->seqlen, p->dim, p->batch);
     if (rc != CC1D_OK) return rc;
     if (!*cl && (p->seq_idx || p->initial_states || p->dfinal_states || p->dinitial_states)) return CC1D_ERR_LAYOUT;
+    if (p->seq_idx && (p->initial_states || p->dfinal_states || p->dinitial_states)) return CC1D_ERR_SEQ_IDX_STATES;
+    if (p->phase < 0 || p->phase > 2) return CC1D_ERR_PHASE;
     if (p->initial_states && p->initial_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
     if (p->dinitial_states && p->dinitial_states_c_stride != 1 && p->dim > 1) return CC1D_ERR_STATE_STRIDE;
     if (p->peers != nullptr) {
@@ -244,11 +256,9 @@ size_t cc1d_bwd_workspace_bytes(const cc1d_bwd_params *p) {
     return n < 16 ? 16 : n;   // never 0 for a valid problem, so callers can always allocate
 }
 
-int cc1d_bwd(const cc1d_bwd_params *p, cc1d_stream_t stream) {
-    bool cl = false;
-    const int rc = check_bwd(p, &cl);
-    if (rc != CC1D_OK) return rc;
-    if (p->workspace == nullptr || p->workspace_bytes < cc1d_bwd_workspace_bytes(p)) return CC1D_ERR_WORKSPACE;
+// Checked parameters -> launcher.  The launchers test the workspace against the partial rows of
+// the tiling they actually pick (CC1D_ERR_WORKSPACE when it is too small).
+static int run_bwd(const cc1d_bwd_params *p, bool cl, cc1d_stream_t stream) {
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     cc1d_bwd_params q = *p;
     if (q.batch <= 1) {
@@ -257,6 +267,14 @@ int cc1d_bwd(const cc1d_bwd_params *p, cc1d_stream_t stream) {
     }
     if (q.width == 2) q.initial_states_l_stride = q.dfinal_states_l_stride = q.dinitial_states_l_stride = 0;
     return cl ? launch_bwd_channel_last(q, s) : launch_bwd_channel_first(q, s);
+}
+
+int cc1d_bwd(const cc1d_bwd_params *p, cc1d_stream_t stream) {
+    bool cl = false;
+    const int rc = check_bwd(p, &cl);
+    if (rc != CC1D_OK) return rc;
+    if (p->workspace == nullptr || p->workspace_bytes < cc1d_bwd_workspace_bytes(p)) return CC1D_ERR_WORKSPACE;
+    return run_bwd(p, cl, stream);
 }
 
 }  // extern "C"
@@ -271,20 +289,29 @@ namespace {
 std::mutex g_scratch_mu;
 void *g_scratch_ptr[64] = {nullptr};
 
-// Device address of g_noalloc_scratch on the current device, or nullptr on failure.
-void *noalloc_scratch_address() {
+// Device address of g_noalloc_scratch on the current device.  The first call per device does the
+// lookup, which may load the library's device code: not something to do while `stream` is being
+// captured, so that case is refused instead.
+int noalloc_scratch_address(cudaStream_t stream, void **out) {
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CC1D_ERR_SCRATCH_ADDRESS;
     std::lock_guard<std::mutex> lock(g_scratch_mu);
     if (g_scratch_ptr[dev] == nullptr) {
-        void *ptr = nullptr;
-        if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) {
             (void)cudaGetLastError();
-            return nullptr;
+            return CC1D_ERR_SCRATCH_ADDRESS;
+        }
+        if (cap != cudaStreamCaptureStatusNone) return CC1D_ERR_CAPTURE;
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) {
+            (void)cudaGetLastError();
+            return CC1D_ERR_SCRATCH_ADDRESS;
         }
         g_scratch_ptr[dev] = ptr;
     }
-    return g_scratch_ptr[dev];
+    *out = g_scratch_ptr[dev];
+    return CC1D_OK;
 }
 }  // namespace
 
@@ -294,13 +321,16 @@ int cc1d_bwd_noalloc(const cc1d_bwd_params *p, cc1d_stream_t stream) {
     bool cl = false;
     const int rc = check_bwd(p, &cl);
     if (rc != CC1D_OK) return rc;
-    if (cc1d_bwd_workspace_bytes(p) > (size_t)CC1D_NOALLOC_SCRATCH_BYTES) return CC1D_ERR_SCRATCH_LIMIT;
-    void *scratch = noalloc_scratch_address();   // first call per device: one symbol lookup
-    if (scratch == nullptr) return CC1D_ERR_LAUNCH;
+    void *scratch = nullptr;   // first call per device: one symbol lookup
+    const int arc = noalloc_scratch_address(reinterpret_cast<cudaStream_t>(stream), &scratch);
+    if (arc != CC1D_OK) return arc;
     cc1d_bwd_params q = *p;
     q.workspace = scratch;
     q.workspace_bytes = CC1D_NOALLOC_SCRATCH_BYTES;
-    return cc1d_bwd(&q, stream);
+    // the launcher sizes the partial rows for the tiling these pointers select and launches
+    // nothing when they do not fit
+    const int lrc = run_bwd(&q, cl, stream);
+    return lrc == CC1D_ERR_WORKSPACE ? CC1D_ERR_SCRATCH_LIMIT : lrc;
 }
 
 int cc1d_update(const cc1d_update_params *p, cc1d_stream_t stream) {
@@ -340,6 +370,8 @@ int cc1d_prefill_varlen(const cc1d_prefill_varlen_params *p, cc1d_stream_t strea
     if (bad_dtype(p->itype) || bad_dtype(p->wtype)) return CC1D_ERR_DTYPE;
     if (p->width < 2 || p->width > 4) return CC1D_ERR_WIDTH;
     if (p->dim % 8 != 0) return CC1D_ERR_CL_DIM;
+    // cu_seqlens and seq_idx are int32, and the kernels index tokens with 32-bit integers
+    if (p->total_tokens >= (1ll << 31) - 4096) return CC1D_ERR_TOO_LARGE;
     const bool states = p->initial_states != nullptr || p->final_states != nullptr;
     if (states && p->state_len < p->width - 1) return CC1D_ERR_STATE_LEN;
     if (p->dim == 0) return CC1D_OK;

@@ -35,6 +35,7 @@ struct ReduceArgs {
     int *peer_status;
     int64_t peer_capacity;
     int world, rank;
+    uint32_t spin_limit;
 };
 
 // One warp per channel.  Lane l sums partial rows l, l+32, ... in ascending order, then a
@@ -130,13 +131,14 @@ __global__ void __launch_bounds__(128) reduce_partials_exchange_kernel(const Red
     for (int r = 0; r < a.world; ++r) {
         const uint2 *p = peer_lines8(a.peer_base[a.rank], parity, r, a.world, a.peer_capacity) + idx;
         uint2 line = ld_line8(p);
-        for (uint32_t it = 0; line.y != epoch && it < kPeerSpinLimitBwd; ++it) {
+        for (uint32_t it = 0; line.y != epoch && it < a.spin_limit; ++it) {
             __nanosleep(it < 64 ? 20 : 250);
             line = ld_line8(p);
         }
-        if (line.y != epoch) {        // the peer never delivered: report and stop
+        if (line.y != epoch) {        // the peer never delivered: report, poison this element, stop waiting
             *a.peer_status = 1;
-            return;
+            sum = __uint_as_float(0x7fc00000u);
+            break;
         }
         sum = r == 0 ? __uint_as_float(line.x) : sum + __uint_as_float(line.x);
     }
@@ -149,10 +151,11 @@ __global__ void __launch_bounds__(128) reduce_partials_exchange_kernel(const Red
 }
 
 static void set_peers(ReduceArgs &r, const cc1d_peer_group *g) {
-    r.world = 0; r.rank = 0; r.peer_status = nullptr; r.peer_capacity = 0;
+    r.world = 0; r.rank = 0; r.peer_status = nullptr; r.peer_capacity = 0; r.spin_limit = kPeerSpinLimitBwd;
     for (int i = 0; i < CC1D_MAX_PEERS; ++i) r.peer_base[i] = nullptr;
     if (g == nullptr) return;
     r.world = g->world; r.rank = g->rank; r.peer_status = g->status; r.peer_capacity = g->capacity;
+    if (g->spin_limit != 0) r.spin_limit = g->spin_limit;
     for (int i = 0; i < g->world && i < CC1D_MAX_PEERS; ++i) r.peer_base[i] = reinterpret_cast<char *>(g->peer_base[i]);
 }
 
@@ -579,7 +582,7 @@ int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream) {
     const uint64_t rows = (uint64_t)p.batch * (uint64_t)p.dim;
     if (p.seqlen >= (1ll << 31) - 4096 || p.dim >= (1ll << 31)) return CC1D_ERR_TOO_LARGE;
     const CfPlan pl = plan_channel_first(p);
-    if (pl.n_units >= (1ull << 32)) return CC1D_ERR_TOO_LARGE;
+    if (pl.n_units >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;   // unit + grid stride must not wrap 32 bits
     if (pl.n_units * (uint64_t)(p.width + 1) * sizeof(float) > p.workspace_bytes) return CC1D_ERR_WORKSPACE;
 
     BwdCfArgs a;
@@ -592,7 +595,7 @@ int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream) {
     a.dim = (uint32_t)p.dim; a.seqlen = (uint32_t)p.seqlen; a.wtype = p.wtype;
     a.vpr = (uint32_t)pl.vpr; a.gpr = (uint32_t)pl.gpr; a.gpu = (uint32_t)pl.gpu; a.upr = (uint32_t)pl.upr;
     a.n_units = (uint32_t)pl.n_units;
-    if (rows > 0 && p.seqlen > 0) {
+    if (rows > 0 && p.seqlen > 0 && p.phase != 2) {
         if (pl.vec) {
             const uint64_t ctas = (pl.n_units + 7) / 8;
             const bool full = p.seqlen % vec_elems(p.itype) == 0 && pl.vpr % kCfGroupVecs == 0;
@@ -620,7 +623,7 @@ int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream) {
     r.chan_stride = (int64_t)pl.upr * (p.width + 1);
     r.accumulate = p.accumulate;
     set_peers(r, p.peers);
-    if (p.dim == 0) return CC1D_OK;
+    if (p.dim == 0 || p.phase == 1) return CC1D_OK;
     return launch_reduce(r, p.width, stream);
 }
 
@@ -1204,6 +1207,8 @@ size_t bwd_workspace_bytes_channel_last(const cc1d_bwd_params &p) {
 
 int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
     const int C = kBwdClC;
+    // token positions are 32-bit integers in the kernels (chunk starts plus a halo must not wrap)
+    if (p.seqlen >= (1ll << 31) - 4096 || p.dim >= (1ll << 31)) return CC1D_ERR_TOO_LARGE;
     if (!is_aligned16(p.x) || !is_aligned16(p.dout) || !is_aligned16(p.dx)) return CC1D_ERR_ALIGN;
     if (p.initial_states && (!is_aligned16(p.initial_states) || p.initial_states_batch_stride % C ||
                              p.initial_states_l_stride % C)) return CC1D_ERR_ALIGN;
@@ -1226,7 +1231,7 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
     a.di_bs = p.dinitial_states_batch_stride; a.di_ls = p.dinitial_states_l_stride;
     a.dim = p.dim; a.seqlen = p.seqlen; a.wtype = p.wtype; a.tpt = pl.tpt;
     a.ncols = pl.ncols; a.ncolblk = pl.ncolblk; a.ngroups = pl.ngroups;
-    if (ctas > 0) {
+    if (ctas > 0 && p.phase != 2) {
         bool launched = false;
 #if CC1D_BWD_CL_TMA
         CUtensorMap xmap, dmap;
@@ -1262,7 +1267,7 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
     r.chan_stride = p.width + 1;
     r.accumulate = p.accumulate;
     set_peers(r, p.peers);
-    if (p.dim == 0) return CC1D_OK;
+    if (p.dim == 0 || p.phase == 1) return CC1D_OK;
     if (p.seqlen == 0) r.n_outer = 0;
     return launch_reduce(r, p.width, stream);
 }

@@ -168,7 +168,7 @@ int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
         const uint64_t gpu = groups_per_unit(rows, gpr);
         const uint64_t upr = (gpr + gpu - 1) / gpu;
         const uint64_t n_units = rows * upr;
-        if (n_units >= (1ull << 32)) return CC1D_ERR_TOO_LARGE;
+        if (n_units >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;   // unit + grid stride must not wrap 32 bits
         a.vpr = (uint32_t)vpr; a.gpr = (uint32_t)gpr; a.gpu = (uint32_t)gpu; a.upr = (uint32_t)upr;
         a.n_units = (uint32_t)n_units;
         const uint64_t ctas = (n_units + 7) / 8;
@@ -182,7 +182,7 @@ int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
     } else {
         const uint64_t tpr = ((uint64_t)p.seqlen + 255) / 256;
         const uint64_t n_tiles = rows * tpr;
-        if (n_tiles >= (1ull << 32)) return CC1D_ERR_TOO_LARGE;
+        if (n_tiles >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;   // tile + grid stride must not wrap 32 bits
         a.vpr = (uint32_t)tpr; a.gpr = a.gpu = a.upr = 0; a.n_units = (uint32_t)n_tiles;
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
             auto kernel = fwd_cf_scalar_kernel<T, W, kSilu>;
@@ -530,6 +530,8 @@ int pick_tokens_per_thread(int64_t batch, int64_t ncols, int64_t seqlen, int sms
 
 int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream) {
     if (p.batch == 0 || p.dim == 0 || p.seqlen == 0) return CC1D_OK;
+    // token positions are 32-bit integers in the kernels (chunk starts plus a halo must not wrap)
+    if (p.seqlen >= (1ll << 31) - 4096 || p.dim >= (1ll << 31)) return CC1D_ERR_TOO_LARGE;
     const int C = vec_elems(p.itype);
     if (!is_aligned16(p.x) || !is_aligned16(p.out)) return CC1D_ERR_ALIGN;
     if (p.initial_states && (!is_aligned16(p.initial_states) || p.initial_states_batch_stride % C ||

@@ -74,8 +74,17 @@ inline unsigned persistent_grid(K kernel, int threads, uint64_t ctas_wanted, boo
 #ifndef CC1D_PDL
 #define CC1D_PDL 1
 #endif
+// Status of the launches made since the last check_launch() on this host thread: launch_k keeps
+// the first cudaError_t that cudaLaunchKernelEx itself returned.  Nothing here calls
+// cudaGetLastError() on the success path, so an earlier, unrelated error that the host
+// application has not collected yet is neither reported as ours nor wiped.
+inline cudaError_t &pending_launch_error() {
+    static thread_local cudaError_t err = cudaSuccess;
+    return err;
+}
+
 template <typename... KArgs, typename... Args>
-inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -86,10 +95,20 @@ inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sme
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = CC1D_PDL ? 1 : 0;
-    (void)cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);   // errors surface in check_launch()
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+    if (rc != cudaSuccess && pending_launch_error() == cudaSuccess) pending_launch_error() = rc;
+    return rc;
 }
 
-inline int check_launch() { return cudaGetLastError() == cudaSuccess ? CC1D_OK : CC1D_ERR_LAUNCH; }
+// CC1D_ERR_LAUNCH when a launch_k since the previous call failed; the failed launch's own
+// (non-sticky) error is cleared so that it is reported once.
+inline int check_launch() {
+    cudaError_t &err = pending_launch_error();
+    if (err == cudaSuccess) return CC1D_OK;
+    err = cudaSuccess;
+    (void)cudaGetLastError();
+    return CC1D_ERR_LAUNCH;
+}
 
 }  // namespace cc1d
 

@@ -22,7 +22,8 @@
 // The epoch of a collective is either given by the caller or (epoch == 0) taken from the rank's
 // own `calls` words, which the kernel advances itself — a captured CUDA graph can then be replayed
 // any number of times and every replay is a new collective.
-// Every poll is bounded: when it runs out the thread sets *status and stops; dst is then invalid.
+// Every poll is bounded (spin_limit polls): when it runs out the thread sets *status, writes NaN to
+// the elements it could not complete and stops.
 #include "cc1d_common.cuh"
 #include "cc1d_kernels.h"
 
@@ -42,6 +43,7 @@ struct PeerArgs {
     int64_t count;            // floats, a multiple of 4
     int world, rank;
     uint32_t epoch;           // 0: numbered by the kernel
+    uint32_t spin_limit;
 };
 
 __device__ __forceinline__ uint4 *peer_lines(char *base, uint32_t parity, int from_rank, int world, int64_t count) {
@@ -84,12 +86,16 @@ __global__ void __launch_bounds__(kPeerThreads) peer_allreduce_kernel(const Peer
         for (int r = 0; r < a.world; ++r) {
             const uint4 *p = peer_lines(a.base[a.rank], parity, r, a.world, a.count) + i;
             uint4 line = ld_line(p);
-            for (uint32_t it = 0; (line.y != epoch || line.w != epoch) && it < kPeerSpinLimit; ++it) {
+            for (uint32_t it = 0; (line.y != epoch || line.w != epoch) && it < a.spin_limit; ++it) {
                 __nanosleep(it < 64 ? 20 : 250);
                 line = ld_line(p);
             }
-            if (line.y != epoch || line.w != epoch) {   // the peer never delivered: report and stop
+            if (line.y != epoch || line.w != epoch) {
+                // the peer never delivered: report, and poison this and every remaining element of
+                // this thread so that a caller who never reads the status cannot use the sums
                 *a.status = 1;
+                const float nan = __uint_as_float(0x7fc00000u);
+                for (int64_t k = i; k < nline; k += step) dst[k] = make_float2(nan, nan);
                 return;
             }
             if (r == 0) acc = make_float2(__uint_as_float(line.x), __uint_as_float(line.z));
@@ -109,6 +115,7 @@ int launch_peer_allreduce(const cc1d_peer_allreduce_params &p, cudaStream_t stre
     PeerArgs a;
     a.src = p.src; a.dst = p.dst; a.status = p.status;
     a.count = p.count; a.world = p.world; a.rank = p.rank; a.epoch = p.epoch;
+    a.spin_limit = p.spin_limit != 0 ? p.spin_limit : kPeerSpinLimit;
     for (int r = 0; r < kMaxPeers; ++r) a.base[r] = r < p.world ? reinterpret_cast<char *>(p.peer_base[r]) : nullptr;
     launch_k(peer_allreduce_kernel, dim3(kPeerCtas), dim3(kPeerThreads), 0, stream, a);
     return check_launch();

@@ -79,7 +79,9 @@ def batch_sharded_backward(
     ``PeerGradReducer`` is given; inside the backward's own finishing kernel when that reducer
     was created with ``fused=True``).  ``x`` / ``dout`` / states are the LOCAL shards; weight and bias
     are replicated.  Returns (dx, dweight, dbias, dinitial_states, packed_fp32) with
-    dweight/dbias cast to the weight dtype after the reduction.
+    dweight/dbias cast to the weight dtype after the reduction.  With a ``reducer`` the wait for
+    the other ranks is bounded: if it ran out the gradients are NaN and ``reducer.check()``
+    raises — call it before the optimizer step.
 
     ``bwd_impl`` exists for the CPU (gloo) tests of this host logic; the default is the
     CUDA extension.
@@ -244,11 +246,16 @@ class PeerGradReducer:
     (no multicast, no peer loads).
 
     ``reduce_(buf)`` sums ``buf`` in place (float32, numel <= count).  A peer that never shows up
-    makes the kernel give up after about half a second and set a status word instead of hanging;
-    ``check()`` (synchronises) raises if that ever happened.
+    makes the kernel give up after ``spin_limit`` polls of about 0.25 us each (0: the library's
+    default, about half a second — size it to the largest skew the job can have between ranks:
+    a first step that loads code lazily, a host stall, an evaluation on one rank).  Giving up
+    sets a status word and leaves NaN in every sum that could not be completed, so the result
+    cannot be used by accident; ``check()`` (synchronises) raises if it ever happened.  Call
+    ``check()`` before anything that cannot be undone, such as the optimizer step.
     """
 
-    def __init__(self, count: int, group: Optional[dist.ProcessGroup] = None, device=None, fused: bool = False):
+    def __init__(self, count: int, group: Optional[dist.ProcessGroup] = None, device=None, fused: bool = False,
+                 spin_limit: int = 0):
         import torch.distributed._symmetric_memory as symm_mem
 
         from causal_conv1d_b200._ext import ext
@@ -257,6 +264,7 @@ class PeerGradReducer:
         # fused: the exchange happens inside the backward's finishing kernel (see
         # batch_sharded_backward); the buffer then belongs to that kernel and reduce_ is not available
         self.fused = bool(fused)
+        self.spin_limit = int(spin_limit)
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -276,7 +284,8 @@ class PeerGradReducer:
         """Keyword arguments that make ``ext.causal_conv1d_bwd`` sum dweight / dbias over the ranks."""
         if not self.fused:
             raise RuntimeError("this reducer was not created with fused=True")
-        return dict(peer_ptrs=self._peer_ptrs, peer_rank=self.rank, peer_capacity=self.count, peer_status=self._status)
+        return dict(peer_ptrs=self._peer_ptrs, peer_rank=self.rank, peer_capacity=self.count, peer_status=self._status,
+                    peer_spin_limit=self.spin_limit)
 
     def reduce_(self, buf: torch.Tensor) -> torch.Tensor:
         if self.fused:
@@ -289,7 +298,7 @@ class PeerGradReducer:
         if not direct:
             work[:n].copy_(buf.reshape(-1))
         # epoch 0: the kernel numbers the collectives itself, so the call can be replayed in a CUDA graph
-        self._ext.peer_allreduce(work, self._peer_ptrs, self.rank, 0, self._status)
+        self._ext.peer_allreduce(work, self._peer_ptrs, self.rank, 0, self._status, self.spin_limit)
         if not direct:
             buf.copy_(work[:n].view_as(buf))
         return buf

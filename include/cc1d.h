@@ -44,7 +44,11 @@ typedef enum cc1d_status {
     CC1D_ERR_ALIGN = 12,        /* pointer not aligned for its element type          */
     CC1D_ERR_TOO_LARGE = 13,    /* problem exceeds an internal index range           */
     CC1D_ERR_LAUNCH = 14,       /* the CUDA launch itself failed (see cudaGetLastError) */
-    CC1D_ERR_SCRATCH_LIMIT = 15 /* problem needs more than the built-in scratch of cc1d_bwd_noalloc */
+    CC1D_ERR_SCRATCH_LIMIT = 15, /* problem needs more than the built-in scratch of cc1d_bwd_noalloc */
+    CC1D_ERR_SCRATCH_ADDRESS = 16, /* cc1d_bwd_noalloc could not look up its built-in scratch on this device */
+    CC1D_ERR_CAPTURE = 17,      /* first cc1d_bwd_noalloc call on a device made inside a stream capture */
+    CC1D_ERR_SEQ_IDX_STATES = 18, /* seq_idx given together with initial/final states (use cc1d_prefill_varlen) */
+    CC1D_ERR_PHASE = 19         /* cc1d_bwd_params.phase not in {0, 1, 2}                 */
 } cc1d_status;
 
 /* ---------------------------------------------------------------------------
@@ -57,7 +61,12 @@ typedef enum cc1d_status {
  *
  * Layout rule (csrc/causal_conv1d.cpp:176): channel-last iff
  * x_c_stride == 1 && x_l_stride > 1, otherwise channel-first (x_l_stride == 1).
- * seq_idx, initial_states and final_states are channel-last only.
+ * seq_idx, initial_states and final_states are channel-last only, and seq_idx
+ * excludes the state tensors (the reference's Python layer asserts the same,
+ * causal_conv1d/causal_conv1d_interface.py:27-33): under seq_idx the positions
+ * before the first token belong to no sequence, so a state could never
+ * contribute; the combination is rejected with CC1D_ERR_SEQ_IDX_STATES —
+ * cc1d_prefill_varlen is the call for packed sequences with states.
  * ------------------------------------------------------------------------- */
 typedef struct cc1d_fwd_params {
     int32_t itype;            /* cc1d_dtype of x, out, states                   */
@@ -87,14 +96,19 @@ int cc1d_fwd(const cc1d_fwd_params *p, cc1d_stream_t stream);
  * peer_base[r]: address, valid on THIS device, of rank r's exchange buffer —
  * cc1d_peer_allreduce_buffer_bytes(world, capacity) bytes of peer-mapped device memory per
  * rank, zero-filled once, used by nothing else (in particular not by cc1d_peer_allreduce:
- * the two lay their lines out differently).  capacity >= dim * (width + 1).  *status is set
- * to 1 when a bounded wait for a peer runs out (dweight / dbias are then invalid). */
+ * the two lay their lines out differently).  capacity >= dim * (width + 1).
+ * A wait for a peer is bounded: spin_limit polls (0: the default, about half a second; a poll
+ * sleeps ~0.25 us, so size it to the largest skew between ranks the job can have).  When it
+ * runs out *status is set to 1 and the elements of dweight / dbias that could not be completed
+ * are set to NaN, so a caller that never reads the status still cannot train on them. */
 #define CC1D_MAX_PEERS 16
 typedef struct cc1d_peer_group {
     int32_t world, rank;
     int64_t capacity;
     void *peer_base[CC1D_MAX_PEERS];
     int32_t *status;              /* device int32, zero-filled by the caller */
+    uint32_t spin_limit;          /* polls before a wait gives up; 0: default */
+    uint32_t reserved0;
 } cc1d_peer_group;
 
 /* ---------------------------------------------------------------------------
@@ -146,6 +160,14 @@ typedef struct cc1d_bwd_params {
      * reduction and the exchange), every rank ending with the same bits.  No counterpart in
      * the reference. */
     const cc1d_peer_group *peers;
+
+    /* 0: the whole backward.  1: only the main kernel (dx, dinitial_states, partial rows left
+     * in `workspace`).  2: only the finishing kernel (partial rows -> dweight / dbias, and the
+     * exchange over `peers`); same parameter block and workspace as the phase-1 call, on any
+     * stream ordered after it.  Splitting lets the exchange between ranks run beside the next
+     * kernels of the compute stream instead of in front of them. */
+    int32_t phase;
+    int32_t reserved1;
 } cc1d_bwd_params;
 
 /* Bytes of scratch cc1d_bwd needs for this problem (host-only arithmetic).
@@ -167,12 +189,14 @@ int cc1d_bwd(const cc1d_bwd_params *p, cc1d_stream_t stream);
  * exits.  p->workspace and p->workspace_bytes are ignored; x, dout, dx, dweight,
  * dbias and the state tensors are still the caller's.
  *
- *  - A problem whose cc1d_bwd_workspace_bytes() exceeds the buffer is rejected
- *    with CC1D_ERR_SCRATCH_LIMIT and nothing is launched.
+ *  - A problem whose partial rows (for the tiling that these pointers and
+ *    strides select; never more than cc1d_bwd_workspace_bytes()) exceed the
+ *    buffer is rejected with CC1D_ERR_SCRATCH_LIMIT and nothing is launched.
  *  - It calls no cudaMalloc / cudaFree / allocating library routine.  The first
  *    call on each device looks up the buffer's device address (one
  *    cudaGetSymbolAddress, with that device current); make that first call
- *    outside any stream capture.
+ *    outside any stream capture — inside one it is refused with
+ *    CC1D_ERR_CAPTURE (a failed lookup: CC1D_ERR_SCRATCH_ADDRESS).
  *  - All calls share the one buffer and it keeps the previous call's contents.
  *    Nothing in it has to start at zero (every slot that is read was written
  *    earlier in the same call), but two calls that overlap on the GPU (different
@@ -309,14 +333,17 @@ const char *cc1d_status_str(int status);
  * the epoch, into every rank's buffer, polls (bounded) its own buffer for all ranks'
  * vectors and adds them in rank order, so all ranks end with the same bits.
  * dst may equal src.  count must be a multiple of 4; src and dst 16-byte aligned.
- * If a poll runs out (a peer never arrived) *status is set to 1 and dst is not valid;
- * the call itself still returns CC1D_OK (it cannot know).  Calls of one communicator
- * must be ordered on each rank.
+ * Polls are bounded (spin_limit polls of ~0.25 us; 0: the default, about half a second —
+ * size it to the largest skew between ranks the job can have).  If one runs out (a peer
+ * never arrived) *status is set to 1 and every element of dst that could not be completed
+ * is set to NaN; the call itself still returns CC1D_OK (it cannot know).  Read the status
+ * before using the sums for anything that cannot be undone (an optimizer step).  Calls of
+ * one communicator must be ordered on each rank.
  * ------------------------------------------------------------------------- */
 typedef struct cc1d_peer_allreduce_params {
     int32_t world, rank;
     uint32_t epoch;
-    int32_t reserved0;
+    uint32_t spin_limit;          /* polls before a wait gives up; 0: default */
     int64_t count;
     const float *src;
     float *dst;

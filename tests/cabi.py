@@ -32,11 +32,12 @@ class BwdParams(ctypes.Structure):
                  ("accumulate", i32), ("reserved0", i32), ("seq_idx", vp), ("initial_states", vp)] +
                 _s3("initial_states") + [("dfinal_states", vp)] + _s3("dfinal_states") +
                 [("dinitial_states", vp)] + _s3("dinitial_states") + [("workspace", vp), ("workspace_bytes", sz),
-                                                                       ("peers", vp)])
+                                                                       ("peers", vp), ("phase", i32), ("reserved1", i32)])
 
 
 class PeerGroup(ctypes.Structure):
-    _fields_ = [("world", i32), ("rank", i32), ("capacity", i64), ("peer_base", vp * 16), ("status", vp)]
+    _fields_ = [("world", i32), ("rank", i32), ("capacity", i64), ("peer_base", vp * 16), ("status", vp),
+                ("spin_limit", ctypes.c_uint32), ("reserved0", ctypes.c_uint32)]
 
 
 class UpdateParams(ctypes.Structure):

@@ -22,7 +22,7 @@ def test_exports_every_declared_symbol(lib):
             "cc1d_status_str", "cc1d_abi_version"} <= set(names)
     for n in names:
         assert hasattr(lib, n), f"libcc1d.so does not export {n}"
-    assert lib.cc1d_abi_version() >= 3
+    assert lib.cc1d_abi_version() >= 4
 
 
 def test_struct_sizes_match_header():
@@ -53,6 +53,13 @@ def _fwd(**kw):
     (dict(x_c_stride=1, x_l_stride=68), 7, "multiples of 8"),
     (dict(seq_idx=FAKE), 8, "channel last"),
     (dict(x=FAKE + 1), 12, "aligned"),
+    # seq_idx excludes states (channel-last block: dim 64, tokens 128 apart by 64 elements)
+    (dict(x_c_stride=1, x_l_stride=64, out_c_stride=1, out_l_stride=64, seq_idx=FAKE, initial_states=FAKE,
+          initial_states_c_stride=1), 18, "seq_idx cannot be combined"),
+    (dict(x_c_stride=1, x_l_stride=64, out_c_stride=1, out_l_stride=64, seq_idx=FAKE, final_states=FAKE,
+          final_states_c_stride=1), 18, "seq_idx cannot be combined"),
+    # token positions are 32-bit in the channel-last kernels
+    (dict(batch=1, seqlen=(1 << 31) - 8, x_c_stride=1, x_l_stride=64, out_c_stride=1, out_l_stride=64), 13, "index range"),
 ])
 def test_fwd_rejects(lib, kw, code, text):
     p = _fwd(**kw)
@@ -92,6 +99,26 @@ def test_bwd_workspace_and_rejects(lib):
     q = cabi.BwdParams(itype=cabi.BF16, wtype=cabi.BF16, width=4, silu=1, batch=1, dim=5376, seqlen=32768,
                        x=FAKE, x_batch_stride=5376 * 32768, x_c_stride=1, x_l_stride=5376)
     assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(q)) == 64 * 5376 * 5 * 4
+
+
+def test_bwd_rejects_seq_idx_with_states_phase_and_long_sequences(lib):
+    def block(**kw):
+        p = cabi.BwdParams(itype=cabi.F32, wtype=cabi.F32, width=4, silu=1, batch=1, dim=64, seqlen=128,
+                           x=FAKE, x_c_stride=1, x_l_stride=64, weight=FAKE, weight_c_stride=4, weight_width_stride=1,
+                           dout=FAKE, dout_c_stride=1, dout_l_stride=64, dx=FAKE, dx_c_stride=1, dx_l_stride=64,
+                           dweight=FAKE, dweight_c_stride=4, dweight_width_stride=1,
+                           workspace=FAKE, workspace_bytes=1 << 40)
+        for k, v in kw.items():
+            setattr(p, k, v)
+        return p
+    for kw in (dict(initial_states=FAKE, initial_states_c_stride=1), dict(dfinal_states=FAKE),
+               dict(dinitial_states=FAKE, dinitial_states_c_stride=1)):
+        rc = lib.cc1d_bwd(ctypes.byref(block(seq_idx=FAKE, **kw)), None)
+        assert rc == 18 and b"seq_idx cannot be combined" in lib.cc1d_status_str(rc)
+    assert lib.cc1d_bwd(ctypes.byref(block(phase=3)), None) == 19
+    assert lib.cc1d_bwd(ctypes.byref(block(seqlen=(1 << 31) - 8)), None) == 13       # fp32: the non-TMA kernel
+    p = _prefill(total_tokens=(1 << 31) - 8)
+    assert lib.cc1d_prefill_varlen(ctypes.byref(p), None) == 13
 
 
 def test_varlen_rejects(lib):

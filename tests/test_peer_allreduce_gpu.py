@@ -84,23 +84,26 @@ def test_two_ranks_emulated_on_one_device():
     assert int(status.item()) == 0
 
 
-def test_wait_runs_out_instead_of_hanging():
-    """A peer that never delivers: the kernel gives up after its bounded wait (about half a
-    second) and raises the status word (nothing of that peer arrived, so nothing is written)."""
+@pytest.mark.parametrize("spin_limit", [0, 4000])
+def test_wait_runs_out_instead_of_hanging(spin_limit):
+    """A peer that never delivers: the kernel gives up after its bounded wait (the default of
+    about half a second, or the caller's limit), raises the status word and leaves NaN in every
+    element it could not complete, so that the sums cannot be used by accident."""
     ext = _ext()
     world, count = 2, 1024
     bufs = [_buffer(world, count), _buffer(world, count)]
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     v = torch.randn(count, device="cuda")
     keep = v.clone()
-    ext.peer_allreduce(v, [b.data_ptr() for b in bufs], 0, 1, status)
+    ext.peer_allreduce(v, [b.data_ptr() for b in bufs], 0, 1, status, spin_limit)
     torch.cuda.synchronize()
     assert int(status.item()) == 1
-    assert torch.equal(v, keep)
+    assert torch.isnan(v).all()
     # the context is still usable and the next collective works once the peer does deliver
     status.zero_()
+    v.copy_(keep)
     _deliver(bufs[0], world, count, 0, 1, torch.ones(count, device="cuda"), 2)
-    ext.peer_allreduce(v, [b.data_ptr() for b in bufs], 0, 2, status)
+    ext.peer_allreduce(v, [b.data_ptr() for b in bufs], 0, 2, status, spin_limit)
     assert int(status.item()) == 0 and torch.equal(v, keep + 1)
 
 
@@ -184,7 +187,32 @@ def test_fused_exchange_gives_up_when_the_peer_never_delivers():
     cap = w.numel() + b.numel()
     bufs = [_buffer(2, cap), _buffer(2, cap)]
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    dx, _, _ = _bwd(x, dout, w, b, peer_ptrs=[bf.data_ptr() for bf in bufs], peer_rank=0, peer_capacity=cap, peer_status=status)
+    dx, dw, db = _bwd(x, dout, w, b, peer_ptrs=[bf.data_ptr() for bf in bufs], peer_rank=0, peer_capacity=cap,
+                      peer_status=status, peer_spin_limit=4000)
     torch.cuda.synchronize()
     assert int(status.item()) == 1
+    assert torch.isnan(dw).all() and torch.isnan(db).all(), "sums that could not be completed must read as NaN"
     assert torch.equal(dx, _bwd(x, dout, w, b)[0]), "dx does not depend on the exchange"
+
+
+@pytest.mark.parametrize("channel_last", [False, True])
+def test_backward_split_into_phases_is_bit_identical(channel_last):
+    """phase 1 (main kernel) and phase 2 (finishing kernel) on two streams, sharing a caller
+    workspace, give the bits of the single call."""
+    torch.manual_seed(6)
+    ext = _ext()
+    x, dout, w, b = _bwd_inputs(channel_last, B=4, D=136, L=515)
+    want = _bwd(x, dout, w, b)
+    ws = torch.empty(ext.bwd_workspace_bytes(x.shape[0], x.shape[1], x.shape[2], w.shape[1], x.element_size(), channel_last),
+                     dtype=torch.uint8, device="cuda")
+    dx, dw, db = torch.empty_like(x), torch.empty_like(w), torch.empty_like(b)
+    side = torch.cuda.Stream()
+    ext.causal_conv1d_bwd(x, w, b, dout, None, None, None, dx, dw, db, None, True, False, phase=1, workspace=ws)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ext.causal_conv1d_bwd(x, w, b, dout, None, None, None, dx, dw, db, None, True, False, phase=2, workspace=ws)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, c) for a, c in zip((dx, dw, db), want))
+    with pytest.raises(RuntimeError):
+        ext.causal_conv1d_bwd(x, w, b, dout, None, None, None, dx, dw, db, None, True, False, phase=1)   # no workspace

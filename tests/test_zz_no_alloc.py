@@ -72,8 +72,17 @@ def test_noalloc_matches_workspace_entry_point(itype, channel_last):
         # new entry point: no workspace handed over at all
         q = _params(x, w, b, dout, *got, channel_last)
         q.workspace, q.workspace_bytes = None, 0
+        torch.cuda.synchronize()
+        free_before, torch_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
         assert lib.cc1d_bwd_noalloc(ctypes.byref(q), _stream()) == 0, f"call {call}"
         torch.cuda.synchronize()
+        if call == 1:
+            # the stated property: nothing was allocated on the device, by the driver or by torch
+            # (checked on the second call: the very first call on a device may load the library's
+            # device code, which the driver accounts for)
+            # (device allocations come in chunks of at least 2 MiB: anything less is not one)
+            assert free_before - torch.cuda.mem_get_info()[0] < (1 << 20)
+            assert torch.cuda.memory_allocated() == torch_before
         assert_close(got[0], ref[0], TOL[itype], f"dx (call {call})")
         assert_close_sum(got[1], ref[1], 2e-5, f"dweight (call {call})")
         assert_close_sum(got[2], ref[2], 2e-5, f"dbias (call {call})")
@@ -81,18 +90,72 @@ def test_noalloc_matches_workspace_entry_point(itype, channel_last):
         assert all(torch.equal(a, c) for a, c in zip(got, ref))
 
 
+def _fake_channel_first(batch, dim, seqlen, fake):
+    return cabi.BwdParams(itype=cabi.BF16, wtype=cabi.F32, width=4, silu=1, batch=batch, dim=dim, seqlen=seqlen,
+                          x=fake, x_batch_stride=dim * seqlen, x_c_stride=seqlen, x_l_stride=1,
+                          weight=0x1000, weight_c_stride=4, weight_width_stride=1,
+                          dout=fake, dout_batch_stride=dim * seqlen, dout_c_stride=seqlen, dout_l_stride=1,
+                          dx=fake, dx_batch_stride=dim * seqlen, dx_c_stride=seqlen, dx_l_stride=1,
+                          dweight=0x1000, dweight_c_stride=4, dweight_width_stride=1)
+
+
 def test_noalloc_rejects_problems_beyond_its_scratch():
     lib = cabi.load()
-    # (32, 8192, 8192) bf16 channel-first needs 42 MB of partial rows: more than the built-in 8 MiB.
-    # Validation happens before anything is launched, so the pointers are never dereferenced.
-    fake = 0x1000
-    p = cabi.BwdParams(itype=cabi.BF16, wtype=cabi.F32, width=4, silu=1, batch=32, dim=8192, seqlen=8192,
-                       x=fake, x_batch_stride=8192 * 8192, x_c_stride=8192, x_l_stride=1,
-                       weight=fake, weight_c_stride=4, weight_width_stride=1,
-                       dout=fake, dout_batch_stride=8192 * 8192, dout_c_stride=8192, dout_l_stride=1,
-                       dx=fake, dx_batch_stride=8192 * 8192, dx_c_stride=8192, dx_l_stride=1,
-                       dweight=fake, dweight_c_stride=4, dweight_width_stride=1)
+    # (32, 8192, 8192) bf16 channel-first, rows NOT 16-byte aligned (pointers at 0x1002): the
+    # element-wise tiling leaves one partial row per 256 elements = 32 * 8192 * 32 * 5 * 4 B = 168 MB,
+    # more than the built-in 8 MiB.  The size test comes before any launch, so the pointers are
+    # never dereferenced.
+    p = _fake_channel_first(32, 8192, 8192, 0x1002)
     assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(p)) > SCRATCH_BYTES
-    rc = lib.cc1d_bwd_noalloc(ctypes.byref(p), None)
+    rc = lib.cc1d_bwd_noalloc(ctypes.byref(p), _stream())
     assert rc == 15
     assert b"cc1d_bwd_noalloc" in lib.cc1d_status_str(rc)
+
+
+def test_noalloc_limit_follows_the_tiling_that_runs():
+    """cc1d_bwd_workspace_bytes() answers for the worse of the two channel-first tilings because it
+    may be asked before the tensors exist.  cc1d_bwd_noalloc knows the pointers: an aligned
+    problem whose vector tiling fits the built-in scratch is served even where the conservative
+    figure exceeds it."""
+    lib = cabi.load()
+    B, D, L, W = 4, 4096, 8192, 4          # conservative: 4*4096*32*5*4 B = 10.5 MB; vector tiling: far less
+    torch.manual_seed(13)
+    x = torch.randn(B, D, L, device="cuda", dtype=torch.bfloat16)
+    dout = torch.randn_like(x)
+    w, b = torch.randn(D, W, device="cuda"), torch.randn(D, device="cuda")
+    ref = [torch.empty_like(x), torch.empty_like(w), torch.empty_like(b)]
+    got = [torch.empty_like(x), torch.empty_like(w), torch.empty_like(b)]
+    p = _params(x, w, b, dout, *ref, False)
+    n = lib.cc1d_bwd_workspace_bytes(ctypes.byref(p))
+    assert n > SCRATCH_BYTES
+    ws = torch.empty(n, dtype=torch.uint8, device="cuda")
+    p.workspace, p.workspace_bytes = ws.data_ptr(), n
+    assert lib.cc1d_bwd(ctypes.byref(p), _stream()) == 0
+    q = _params(x, w, b, dout, *got, False)
+    assert lib.cc1d_bwd_noalloc(ctypes.byref(q), _stream()) == 0
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, c) for a, c in zip(got, ref))
+
+
+def test_noalloc_on_a_second_device():
+    """The scratch address is looked up per device; the entry point works on every GPU of the process."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    lib = cabi.load()
+    with torch.cuda.device(1):
+        torch.manual_seed(14)
+        x = torch.randn(2, 64, 512, device="cuda:1", dtype=torch.bfloat16)
+        dout = torch.randn_like(x)
+        w, b = torch.randn(64, 4, device="cuda:1"), torch.randn(64, device="cuda:1")
+        ref = [torch.empty_like(x), torch.empty_like(w), torch.empty_like(b)]
+        got = [torch.empty_like(x), torch.empty_like(w), torch.empty_like(b)]
+        p = _params(x, w, b, dout, *ref, False)
+        n = lib.cc1d_bwd_workspace_bytes(ctypes.byref(p))
+        ws = torch.empty(n, dtype=torch.uint8, device="cuda:1")
+        p.workspace, p.workspace_bytes = ws.data_ptr(), n
+        s = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        assert lib.cc1d_bwd(ctypes.byref(p), s) == 0
+        q = _params(x, w, b, dout, *got, False)
+        assert lib.cc1d_bwd_noalloc(ctypes.byref(q), s) == 0
+        torch.cuda.synchronize()
+        assert all(torch.equal(a, c) for a, c in zip(got, ref))

@@ -461,6 +461,215 @@ __global__ void __launch_bounds__(256, CC1D_BWD_CF_MINBLK) bwd_cf_vec_kernel(con
     }
 }
 
+// ---- 16-bit I/O, rows made of whole groups, 32-byte aligned: 32 bytes per lane ----------------
+// A lane owns SLOTS of 16 consecutive elements (two 16-byte vectors A, B moved by one 256-bit
+// load / store); a warp instruction covers 1 KB of the row.  The fp32 pairs hold (A[i], B[i]),
+// so of the four halos a pair of vectors has, two stay inside the lane: B's left x halo is
+// A's tail and A's right g halo is B's head.  Only A's left halo (previous lane's B tail, 2
+// shuffles) and B's right halo (next lane's A head, width-1 shuffles) cross lanes.  Slots are
+// walked back to front; lane 0 keeps g of its first elements for lane 31 of the slot before.
+__device__ __forceinline__ void ld_stream32(uint4 &a, uint4 &b, const void *p) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p));
+}
+__device__ __forceinline__ void st_stream32(void *p, const uint4 &a, const uint4 &b) {
+    asm volatile("st.global.cs.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 :: "l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
+}
+
+#ifndef CC1D_BWD_WIDE
+#define CC1D_BWD_WIDE 1            // 0: never take the 32-bytes-per-lane kernel
+#endif
+#ifndef CC1D_BWD_WIDE_THREADS
+#define CC1D_BWD_WIDE_THREADS 128    // with 5 CTAs per SM: 96 registers, 20 warps per SM
+#endif
+#ifndef CC1D_BWD_WIDE_MINBLK
+#define CC1D_BWD_WIDE_MINBLK 5
+#endif
+#ifndef CC1D_BWD_WIDE_PERSISTENT
+#define CC1D_BWD_WIDE_PERSISTENT 0   // 1: grid = resident CTAs, grid-stride loop over the units; 0: one unit per warp
+#endif
+#ifndef CC1D_BWD_WIDE_STEP
+#define CC1D_BWD_WIDE_STEP 2         // slots loaded, then computed, per step (1 or kCfVecs / 2)
+#endif
+#ifndef CC1D_BWD_WIDE_PREFETCH
+#define CC1D_BWD_WIDE_PREFETCH 0   // 1: the next group's vectors are requested before the current group is computed
+#endif
+constexpr int kWideSlots = kCfVecs / 2;       // same group size (and partial rows) as the 16-byte kernel
+constexpr uint32_t kWideSlotElems = 32 * 16;
+
+template <int kSlots> struct WideGroup {
+    uint4 xa[kSlots], xb[kSlots], da[kSlots], db[kSlots];
+    uint32_t cz, cw;          // lane 31: the 4 elements of x before the group (zeros at the row start)
+};
+
+template <typename T, int kSlots>
+__device__ __forceinline__ void wide_load(WideGroup<kSlots> &r, const T *__restrict__ xr, const T *__restrict__ dr,
+                                          uint32_t g, int lane) {
+    const uint32_t gs = g * (kSlots * kWideSlotElems);
+    #pragma unroll
+    for (int j = 0; j < kSlots; ++j) {
+        const uint32_t e = gs + j * kWideSlotElems + lane * 16;
+        ld_stream32(r.xa[j], r.xb[j], xr + e);
+        ld_stream32(r.da[j], r.db[j], dr + e);
+    }
+    r.cz = 0; r.cw = 0;
+    if (lane == 31 && g > 0) {
+        const uint2 t = *reinterpret_cast<const uint2 *>(xr + gs - 4);
+        r.cz = t.x; r.cw = t.y;
+    }
+}
+
+template <typename T, int W, bool kSilu, int kSlots>
+__device__ __forceinline__ void wide_group(const WideGroup<kSlots> &r, const float (&wv)[W], const float (&wy)[W], float by,
+                                           float (&gfirst)[W - 1], float2 (&dw2)[W], float2 &db2, T *__restrict__ dxr,
+                                           uint32_t g, int lane) {
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    const int src_prev = (lane + 31) & 31, src_next = (lane + 1) & 31;
+    const uint32_t gs = g * (kSlots * kWideSlotElems);
+    #pragma unroll
+    for (int j = kSlots - 1; j >= 0; --j) {
+        // left x halo of A: the previous lane's B tail; lane 0 gets what lane 31 holds of the slot before
+        const uint32_t oz = j > 0 ? r.xb[j > 0 ? j - 1 : 0].z : r.cz, ow = j > 0 ? r.xb[j > 0 ? j - 1 : 0].w : r.cw;
+        uint32_t pz = 0;
+        if (W >= 4) pz = __shfl_sync(kFullMask, lane == 31 ? oz : r.xb[j].z, src_prev);
+        const uint32_t pw = __shfl_sync(kFullMask, lane == 31 ? ow : r.xb[j].w, src_prev);
+        float2 xx[W - 1 + 8], gx[8 + W - 1];
+        {
+            const float2 pa = unpack_pair<T>(pz), pb = unpack_pair<T>(pw);
+            const float p[4] = {pa.x, pa.y, pb.x, pb.y};   // elements 4..7 of the vector before A
+            float af[8], bf[8], df[8], ef[8];
+            unpack<T>(r.xa[j], af); unpack<T>(r.xb[j], bf); unpack<T>(r.da[j], df); unpack<T>(r.db[j], ef);
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) xx[k] = make_float2(p[4 - (W - 1) + k], af[8 - (W - 1) + k]);
+            #pragma unroll
+            for (int i = 0; i < 8; ++i) { xx[W - 1 + i] = make_float2(af[i], bf[i]); gx[i] = make_float2(df[i], ef[i]); }
+        }
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (kSilu) {
+                float2 y = splat2(by);
+                #pragma unroll
+                for (int k = 0; k < W; ++k) y = fma2(splat2(wy[k]), xx[i + k], y);
+                gx[i] = act_grad_pair<kTanh>(y, gx[i]);
+            }
+            db2 = add2(db2, gx[i]);
+            #pragma unroll
+            for (int k = 0; k < W; ++k) dw2[k] = fma2(xx[i + k], gx[i], dw2[k]);
+        }
+        // right g halo: A's is B's head; B's is the next lane's A head, lane 31 takes lane 0's from
+        // the slot done just before (gfirst), which then moves on to this slot's
+        #pragma unroll
+        for (int k = 0; k < W - 1; ++k) {
+            const float nb = __shfl_sync(kFullMask, lane == 0 ? gfirst[k] : gx[k].x, src_next);
+            gfirst[k] = gx[k].x;
+            gx[8 + k] = make_float2(gx[k].y, nb);
+        }
+        float o0[8], o1[8];
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float2 acc = make_float2(0.f, 0.f);
+            #pragma unroll
+            for (int k = 0; k < W; ++k) acc = fma2(splat2(wv[k]), gx[i + (W - 1 - k)], acc);
+            o0[i] = acc.x; o1[i] = acc.y;
+        }
+        st_stream32(dxr + gs + j * kWideSlotElems + lane * 16, pack<T>(o0), pack<T>(o1));
+    }
+}
+
+template <typename T, int W, bool kSilu, int kSlots, bool kPrefetch>
+__global__ void __launch_bounds__(CC1D_BWD_WIDE_THREADS, CC1D_BWD_WIDE_MINBLK) bwd_cf_wide_kernel(const BwdCfArgs a) {
+    pdl_wait();
+    static_assert(sizeof(T) == 2, "16-bit I/O only");
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    constexpr uint32_t kGroupElems = kSlots * kWideSlotElems;
+    const int lane = threadIdx.x & 31;
+    const uint32_t warps_per_cta = blockDim.x >> 5;
+    const uint32_t nwarps = gridDim.x * warps_per_cta;
+
+    for (uint32_t unit = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); unit < a.n_units; unit += nwarps) {
+        const uint32_t row = unit / a.upr;
+        const uint32_t seg = unit - row * a.upr;
+        const uint32_t b = row / a.dim;
+        const uint32_t c = row - b * a.dim;
+        const T *__restrict__ xr = reinterpret_cast<const T *>(a.x) + b * a.x_bs + c * a.x_cs;
+        const T *__restrict__ dr = reinterpret_cast<const T *>(a.dout) + b * a.d_bs + c * a.d_cs;
+        T *__restrict__ dxr = reinterpret_cast<T *>(a.dx) + b * a.o_bs + c * a.o_cs;
+        const uint32_t g0 = seg * a.gpu;
+        const uint32_t g1 = g0 + a.gpu < a.gpr ? g0 + a.gpu : a.gpr;
+
+        // first loads requested before the taps are: kPrefetch walks the unit slot by slot with the
+        // next slot's vectors already in flight, otherwise a whole group is loaded, then computed
+        constexpr int kStep = kPrefetch ? 1 : (CC1D_BWD_WIDE_STEP < kSlots ? CC1D_BWD_WIDE_STEP : kSlots);   // slots per load/compute step
+        const uint32_t s0 = g0 * (kSlots / kStep), s1 = g1 * (kSlots / kStep);
+        WideGroup<kStep> cur;
+        wide_load<T, kStep>(cur, xr, dr, s1 - 1, lane);
+
+        float wv[W], wy[W];
+        constexpr float pre = ActGrad<kTanh>::kPre, post = 1.f / ActGrad<kTanh>::kGScale;
+        #pragma unroll
+        for (int k = 0; k < W; ++k) {
+            const float w = load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype);
+            wv[k] = post * w;
+            wy[k] = pre * w;
+        }
+        const float by = a.bias != nullptr ? pre * load_w(a.bias, c, a.wtype) : 0.f;
+
+        float2 dw2[W], db2 = make_float2(0.f, 0.f);
+        #pragma unroll
+        for (int k = 0; k < W; ++k) dw2[k] = make_float2(0.f, 0.f);
+        // g of the first width-1 elements after the unit (zero past the row end), same in all lanes
+        float gfirst[W - 1];
+        #pragma unroll
+        for (int k = 0; k < W - 1; ++k) gfirst[k] = 0.f;
+        if (g1 < a.gpr) {   // warp-uniform
+            const uint32_t en = g1 * kGroupElems;
+            uint4 xlast = make_uint4(0, 0, 0, 0), xedge = make_uint4(0, 0, 0, 0);
+            if (kSilu) { xlast = ld_cached(xr + en - 8); xedge = ld_cached(xr + en); }
+            const uint4 dedge = ld_cached(dr + en);
+            seed_right_halo<T, W, kSilu, kTanh>(xlast, xedge, dedge, wy, by, gfirst);
+        }
+
+        if constexpr (kPrefetch) {
+            WideGroup<kStep> nxt;
+            uint32_t s = s1 - 1;
+            while (true) {
+                if (s > s0) wide_load<T, kStep>(nxt, xr, dr, s - 1, lane);
+                wide_group<T, W, kSilu, kStep>(cur, wv, wy, by, gfirst, dw2, db2, dxr, s, lane);
+                if (s == s0) break;
+                --s;
+                if (s > s0) wide_load<T, kStep>(cur, xr, dr, s - 1, lane);
+                wide_group<T, W, kSilu, kStep>(nxt, wv, wy, by, gfirst, dw2, db2, dxr, s, lane);
+                if (s == s0) break;
+                --s;
+            }
+        } else {
+            for (uint32_t s = s1 - 1;; --s) {
+                wide_group<T, W, kSilu, kStep>(cur, wv, wy, by, gfirst, dw2, db2, dxr, s, lane);
+                if (s == s0) break;
+                wide_load<T, kStep>(cur, xr, dr, s - 1, lane);
+            }
+        }
+
+        // fold the pair components, then the warp tree (fixed order): one partial row per unit
+        float dw[W], db = (db2.x + db2.y) * post;      // the sums were taken over kGScale * g
+        #pragma unroll
+        for (int k = 0; k < W; ++k) dw[k] = (dw2[k].x + dw2[k].y) * post;
+        #pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            #pragma unroll
+            for (int k = 0; k < W; ++k) dw[k] += __shfl_xor_sync(kFullMask, dw[k], off);
+            db += __shfl_xor_sync(kFullMask, db, off);
+        }
+        if (lane == 0) {
+            float *p = a.ws + (uint64_t)unit * (W + 1);
+            #pragma unroll
+            for (int k = 0; k < W; ++k) p[k] = dw[k];
+            p[W] = db;
+        }
+    }
+}
+
 // Any alignment: one (row, 256-element tile) per CTA, a thread per element; block tree in
 // shared memory.  Partial row per tile.
 template <typename T, int W, bool kSilu>
@@ -599,6 +808,30 @@ int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream) {
         if (pl.vec) {
             const uint64_t ctas = (pl.n_units + 7) / 8;
             const bool full = p.seqlen % vec_elems(p.itype) == 0 && pl.vpr % kCfGroupVecs == 0;
+            // 16-bit rows of whole groups whose starts are 32-byte aligned: 32 bytes per lane
+            const bool wide = CC1D_BWD_WIDE && kCfVecs % 2 == 0 && full && p.itype != CC1D_F32 &&
+                              ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.dout) |
+                                reinterpret_cast<uintptr_t>(p.dx)) & 31u) == 0 &&
+                              (a.x_bs | a.x_cs | a.d_bs | a.d_cs | a.o_bs | a.o_cs) % 16 == 0;
+            if (wide) {
+                if (p.itype == CC1D_BF16) {
+                    using T = __nv_bfloat16;
+                    CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
+                        auto kernel = bwd_cf_wide_kernel<T, W, kSilu, kWideSlots, CC1D_BWD_WIDE_PREFETCH != 0>;
+                        const uint64_t wctas = (pl.n_units + CC1D_BWD_WIDE_THREADS / 32 - 1) / (CC1D_BWD_WIDE_THREADS / 32);
+                        launch_k(kernel, dim3(persistent_grid(kernel, CC1D_BWD_WIDE_THREADS, wctas, CC1D_BWD_WIDE_PERSISTENT != 0)),
+                                 dim3(CC1D_BWD_WIDE_THREADS), 0, stream, a);
+                    }););
+                } else {
+                    using T = __half;
+                    CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
+                        auto kernel = bwd_cf_wide_kernel<T, W, kSilu, kWideSlots, CC1D_BWD_WIDE_PREFETCH != 0>;
+                        const uint64_t wctas = (pl.n_units + CC1D_BWD_WIDE_THREADS / 32 - 1) / (CC1D_BWD_WIDE_THREADS / 32);
+                        launch_k(kernel, dim3(persistent_grid(kernel, CC1D_BWD_WIDE_THREADS, wctas, CC1D_BWD_WIDE_PERSISTENT != 0)),
+                                 dim3(CC1D_BWD_WIDE_THREADS), 0, stream, a);
+                    }););
+                }
+            } else
             CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
                 CC1D_DISPATCH_BOOL(full, kFull, {
                     auto kernel = bwd_cf_vec_kernel<T, W, kSilu, kFull, kCfVecs>;

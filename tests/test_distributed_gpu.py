@@ -156,6 +156,24 @@ def _peer_worker(rank, world, port, ret):
                     acc += p
                 ok &= torch.equal(got, acc)
             red.check()
+        # the batch-sharded backward on all ranks: exchange inside the finishing kernel against NCCL
+        from causal_conv1d_b200.distributed import batch_shard, batch_sharded_backward
+        torch.manual_seed(0)
+        B, D, L, W = 2 * world, 136, 1024, 4
+        x = torch.randn(B, D, L, dtype=torch.bfloat16).to(dev)
+        dout = torch.randn(B, D, L, dtype=torch.bfloat16).to(dev)
+        w, b = torch.randn(D, W).to(dev), torch.randn(D).to(dev)
+        xs, ds = batch_shard(x, rank, world), batch_shard(dout, rank, world)
+        dx_n, dw_n, db_n, _, _ = batch_sharded_backward(xs, w, b, ds, activation="silu")
+        fused = PeerGradReducer(D * W + D, fused=True)
+        for _ in range(3):                           # both parities of the exchange buffer
+            dx_f, dw_f, db_f, _, packed = batch_sharded_backward(xs, w, b, ds, activation="silu", reducer=fused)
+            ok &= torch.equal(dx_f, dx_n)
+            ok &= torch.allclose(dw_f, dw_n, rtol=1e-5, atol=1e-4) and torch.allclose(db_f, db_n, rtol=1e-5, atol=1e-4)
+            every = [torch.empty_like(packed) for _ in range(world)]
+            dist.all_gather(every, packed)
+            ok &= all(torch.equal(every[0], g) for g in every)
+        fused.check()
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
@@ -163,7 +181,8 @@ def _peer_worker(rank, world, port, ret):
 
 def test_peer_allreduce_on_all_visible_gpus():
     """As many ranks as there are GPUs (2 to 8): same result as NCCL within fp32 rounding, the
-    same bits on every rank, and exactly the sum taken in rank order."""
+    same bits on every rank, and exactly the sum taken in rank order; then the batch-sharded
+    backward with the exchange fused into its finishing kernel."""
     world = min(torch.cuda.device_count(), 8)
     if world < 2:
         pytest.skip("needs 2 GPUs")

@@ -205,6 +205,42 @@ def test_causal_conv1d_wide_dim(seqlen, width, itype, channel_last):
     _run_fwd_bwd(4096 + 32, seqlen, width, has_bias, silu, itype, channel_last, init, final, use_cpu_oracle=False)
 
 
+@pytest.mark.parametrize("itype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("width", [2, 3, 4])
+@pytest.mark.parametrize("silu", [False, True])
+@pytest.mark.parametrize("batch,dim,seqlen", [(1, 8, 1024), (2, 24, 2048), (1, 3, 8192), (3, 5, 3072)])
+def test_channel_first_rows_of_whole_groups(batch, dim, seqlen, silu, width, itype):
+    """16-bit channel-first rows made of whole 1024-element groups on 32-byte aligned rows take the
+    backward kernel that moves 32 bytes per lane; few rows, so that rows are cut into several warp
+    units (the seeded right halo).  Checked against the CPU oracle, and bit-for-bit against the same
+    problem placed 16 bytes off a 32-byte boundary (which takes the 16-byte kernel)."""
+    torch.manual_seed(7)
+    x = torch.randn(batch, dim, seqlen, device=DEV, dtype=itype)
+    dout = torch.randn_like(x)
+    w = torch.randn(dim, width, device=DEV)
+    b = torch.randn(dim, device=DEV)
+    act = "silu" if silu else None
+
+    def run(xv, dv):
+        xr, wr, br = xv.detach().requires_grad_(), w.detach().requires_grad_(), b.detach().requires_grad_()
+        out = _api().causal_conv1d_fn(xr, wr, br, activation=act)
+        out.backward(dv)
+        return out, xr.grad, wr.grad, br.grad
+
+    out, dx, dw, db = run(x, dout)
+    r = oracle.bwd(x, w, b, dout, activation=act)
+    assert_close(out, oracle.fwd(x, w, b, activation=act).to(itype), TOL[itype], "out")
+    assert_close(dx, r["dx"].to(itype), TOL[itype], "dx")
+    assert_close_sum(dw, r["dweight"], SUM_TOL[itype], "dweight")
+    assert_close_sum(db, r["dbias"], SUM_TOL[itype], "dbias")
+    # the same rows at an offset of 8 elements inside rows of seqlen + 16 elements
+    shifted = lambda t: torch.cat([t.new_zeros(batch, dim, 8), t, t.new_zeros(batch, dim, 8)], dim=-1)[..., 8:8 + seqlen]
+    out2, dx2, dw2, db2 = run(shifted(x), shifted(dout))
+    assert torch.equal(out, out2) and torch.equal(dx, dx2)
+    assert_close_sum(dw2, dw, 2e-5, "dweight, other kernel")
+    assert_close_sum(db2, db, 2e-5, "dbias, other kernel")
+
+
 @pytest.mark.parametrize("silu,has_bias,init,final", list(itertools.product([False, True], repeat=4)))
 @pytest.mark.parametrize("width", [2, 3, 4])
 def test_causal_conv1d_all_flag_combos(width, silu, has_bias, init, final):

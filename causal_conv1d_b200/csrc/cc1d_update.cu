@@ -239,6 +239,127 @@ __global__ void __launch_bounds__(128, 4) update_cfstate_kernel(const UpdArgs a)
     for (int i = 0; i < S; ++i) sp[i] = make_uint4(nw[4 * i], nw[4 * i + 1], nw[4 * i + 2], nw[4 * i + 3]);
 }
 
+// ---- channel-first state, several tokens and / or the circular buffer (16-bit types) -------------
+// Same ownership as update_cfstate_kernel: a thread holds the C = 8 channels x S state elements of
+// its block as raw bits in registers.  x and out are channel-major as well for L > 1 (the L tokens of
+// a channel adjacent: (batch, dim, L) contiguous), so the thread's tokens are L 16-byte vectors.
+//   linear (S == width-1 or width): per channel seq = [state | tokens]; output i is the dot product of
+//     the taps with seq[S-(W-1)+i ..]; the new state is seq[L .. L+S).
+//   circular (S == 8, one 16-byte vector per channel): the vector is rotated so that the write position
+//     cache_seqlens % 8 comes first (selects + funnel shifts: no dynamic register indexing), the window
+//     is then its last width-1 elements and the tokens go to its first L; rotated back and stored.
+// A circular step rewrites the whole 16-byte row of every channel: the rows are 16 bytes, DRAM moves
+// 32-byte sectors, so nothing narrower than the row could be written anyway.
+template <typename T> __device__ __forceinline__ uint32_t bits_from_f(float v);
+template <> __device__ __forceinline__ uint32_t bits_from_f<__nv_bfloat16>(float v) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    return (uint32_t)*reinterpret_cast<const unsigned short *>(&h);
+}
+template <> __device__ __forceinline__ uint32_t bits_from_f<__half>(float v) {
+    const __half h = __float2half_rn(v);
+    return (uint32_t)*reinterpret_cast<const unsigned short *>(&h);
+}
+
+// 8 16-bit elements in 4 registers, rotated left by n elements (element j <- element (j + n) % 8)
+__device__ __forceinline__ void rotate8(uint32_t (&r)[4], int n) {
+    uint32_t t0 = r[0], t1 = r[1], t2 = r[2], t3 = r[3], u;
+    if (n & 2) { u = t0; t0 = t1; t1 = t2; t2 = t3; t3 = u; }
+    if (n & 4) { u = t0; t0 = t2; t2 = u; u = t1; t1 = t3; t3 = u; }
+    if (n & 1) {
+        const uint32_t v0 = __funnelshift_r(t0, t1, 16), v1 = __funnelshift_r(t1, t2, 16),
+                       v2 = __funnelshift_r(t2, t3, 16), v3 = __funnelshift_r(t3, t0, 16);
+        t0 = v0; t1 = v1; t2 = v2; t3 = v3;
+    }
+    r[0] = t0; r[1] = t1; r[2] = t2; r[3] = t3;
+}
+
+template <typename T, int W, bool kSilu, int S, bool kCirc, int L>
+__global__ void __launch_bounds__(128, 4) update_cfstate_multi_kernel(const UpdArgs a) {
+    pdl_wait();
+    static_assert(sizeof(T) == 2, "16-bit types");
+    static_assert(!kCirc || S == 8, "circular mode: 8 slots");
+    constexpr int C = 8;
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    const uint64_t gid = (uint64_t)blockIdx.x * 128 + threadIdx.x;
+    const int32_t b = (int32_t)(gid / a.ncols);
+    const uint32_t col = (uint32_t)(gid - (uint64_t)b * a.ncols);
+    if (b >= a.batch) return;
+
+    const int32_t coord = a.indices != nullptr ? __ldg(a.indices + b) : b;
+    const int32_t cs = kCirc ? __ldg(a.cache_seqlens + b) : 0;
+    const uint4 *xp = reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.x) + (int64_t)b * a.x_bs + (int64_t)col * C * L);
+    uint4 *op = reinterpret_cast<uint4 *>(reinterpret_cast<T *>(a.out) + (int64_t)b * a.o_bs + (int64_t)col * C * L);
+    uint4 xv[L];
+    #pragma unroll
+    for (int i = 0; i < L; ++i) xv[i] = ld_stream(xp + i);
+    if (coord < 0) {   // padded entry: zero output, state untouched
+        #pragma unroll
+        for (int i = 0; i < L; ++i) st_stream(op + i, make_uint4(0, 0, 0, 0));
+        return;
+    }
+    uint4 *sp = reinterpret_cast<uint4 *>(reinterpret_cast<T *>(a.state) + coord * a.s_bs + (int64_t)col * C * S);
+    uint4 sv[S];
+    #pragma unroll
+    for (int i = 0; i < S; ++i) sv[i] = ld_cached(sp + i);
+    float wv[W][C], bv[C];
+    load_taps<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, kTanh ? 0.5f : 1.f);
+
+    uint32_t old[S * 4], nw[S * 4], xr[L * 4], ob[L * 4];
+    #pragma unroll
+    for (int i = 0; i < S; ++i) { old[4 * i] = sv[i].x; old[4 * i + 1] = sv[i].y; old[4 * i + 2] = sv[i].z; old[4 * i + 3] = sv[i].w; }
+    #pragma unroll
+    for (int i = 0; i < L; ++i) { xr[4 * i] = xv[i].x; xr[4 * i + 1] = xv[i].y; xr[4 * i + 2] = xv[i].z; xr[4 * i + 3] = xv[i].w; }
+    #pragma unroll
+    for (int i = 0; i < S * 4; ++i) nw[i] = 0;
+    #pragma unroll
+    for (int i = 0; i < L * 4; ++i) ob[i] = 0;
+    int wr = 0;
+    if (kCirc) {
+        wr = cs % S;
+        if (wr < 0) wr += S;
+    }
+    #pragma unroll
+    for (int c = 0; c < C; ++c) {
+        uint32_t seq[W - 1 + L];          // the window, then the tokens
+        if (kCirc) {
+            uint32_t row[4] = {old[4 * c], old[4 * c + 1], old[4 * c + 2], old[4 * c + 3]};
+            rotate8(row, wr);              // element 0 is now the write position
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) seq[k] = Bits<T>::get(row, S - (W - 1) + k);
+            #pragma unroll
+            for (int i = 0; i < L; ++i) seq[W - 1 + i] = Bits<T>::get(xr, c * L + i);
+            uint32_t upd[4] = {0, 0, 0, 0};
+            #pragma unroll
+            for (int j = 0; j < S; ++j) Bits<T>::put(upd, j, j < L ? seq[W - 1 + j] : Bits<T>::get(row, j));
+            rotate8(upd, (S - wr) & (S - 1));
+            #pragma unroll
+            for (int j = 0; j < 4; ++j) nw[4 * c + j] = upd[j];
+        } else {
+            uint32_t all[S + L];
+            #pragma unroll
+            for (int j = 0; j < S; ++j) all[j] = Bits<T>::get(old, c * S + j);
+            #pragma unroll
+            for (int i = 0; i < L; ++i) all[S + i] = Bits<T>::get(xr, c * L + i);
+            #pragma unroll
+            for (int j = 0; j < W - 1 + L; ++j) seq[j] = all[S - (W - 1) + j];
+            #pragma unroll
+            for (int t = 0; t < S; ++t) Bits<T>::put(nw, c * S + t, all[t + L]);
+        }
+        #pragma unroll
+        for (int i = 0; i < L; ++i) {
+            float acc = bv[c];
+            #pragma unroll
+            for (int k = 0; k < W; ++k) acc = fmaf(wv[k][c], Bits<T>::to_f(seq[i + k]), acc);
+            const float o = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
+            Bits<T>::put(ob, c * L + i, bits_from_f<T>(o));
+        }
+    }
+    #pragma unroll
+    for (int i = 0; i < L; ++i) st_stream(op + i, make_uint4(ob[4 * i], ob[4 * i + 1], ob[4 * i + 2], ob[4 * i + 3]));
+    #pragma unroll
+    for (int i = 0; i < S; ++i) sp[i] = make_uint4(nw[4 * i], nw[4 * i + 1], nw[4 * i + 2], nw[4 * i + 3]);
+}
+
 template <typename T, int W, bool kSilu, bool kCirc>
 __global__ void __launch_bounds__(128) update_generic_kernel(const UpdArgs a) {
     pdl_wait();
@@ -324,6 +445,43 @@ int launch_update(const cc1d_update_params &p, cudaStream_t stream) {
                              p.conv_state_l_stride == 1 && p.conv_state_c_stride == S && (S == p.width - 1 || S == p.width) &&
                              S >= 2 && is_aligned16(p.x) && is_aligned16(p.out) && is_aligned16(p.conv_state) &&
                              x_bs % C == 0 && o_bs % C == 0 && (p.conv_state_batch_stride * elem_size(p.itype)) % 16 == 0;
+    // contiguous (entries, dim, S) state with 16-bit elements, up to 4 tokens (x and out (batch, dim, L)
+    // contiguous as well when L > 1): linear with S == width-1 or width, or the circular pool of 8 slots
+    const int64_t Lx = p.seqlen;
+    const bool x_cm = Lx == 1 ? (p.dim == 1 || (p.x_c_stride == 1 && p.out_c_stride == 1))
+                              : (p.x_l_stride == 1 && p.out_l_stride == 1 && (p.dim == 1 || (p.x_c_stride == Lx && p.out_c_stride == Lx)));
+    const bool cf_multi_ok = p.itype != CC1D_F32 && Lx >= 1 && Lx <= 4 && p.dim % 8 == 0 && x_cm &&
+                             p.conv_state_l_stride == 1 && p.conv_state_c_stride == S &&
+                             ((!circ && Lx > 1 && (S == p.width - 1 || S == p.width) && S >= 2) || (circ && S == 8)) &&
+                             is_aligned16(p.x) && is_aligned16(p.out) && is_aligned16(p.conv_state) &&
+                             x_bs % 8 == 0 && o_bs % 8 == 0 && p.conv_state_batch_stride % 8 == 0;
+    if (cf_multi_ok) {
+        a.ncols = (uint32_t)(p.dim / 8);
+        a.ncolblk = 0;
+        const uint64_t ctas = ((uint64_t)a.ncols * (uint64_t)p.batch + 127) / 128;
+        if (ctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
+#define CC1D_LAUNCH_MULTI(TT, SS, CIRC, LL) \
+        launch_k(update_cfstate_multi_kernel<TT, W, kSilu, SS, CIRC, LL>, dim3((unsigned)ctas), dim3(128), 0, stream, a)
+#define CC1D_MULTI_BY_L(TT, SS, CIRC) \
+        do { if (Lx == 1) { if (CIRC) CC1D_LAUNCH_MULTI(TT, SS, CIRC, (CIRC ? 1 : 2)); } \
+             else if (Lx == 2) CC1D_LAUNCH_MULTI(TT, SS, CIRC, 2); \
+             else if (Lx == 3) CC1D_LAUNCH_MULTI(TT, SS, CIRC, 3); \
+             else CC1D_LAUNCH_MULTI(TT, SS, CIRC, 4); } while (0)
+        CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
+            if (p.itype == CC1D_BF16) {
+                if (circ) CC1D_MULTI_BY_L(__nv_bfloat16, 8, true);
+                else if (S == W) CC1D_MULTI_BY_L(__nv_bfloat16, W, false);
+                else if (W >= 3) CC1D_MULTI_BY_L(__nv_bfloat16, (W >= 3 ? W - 1 : W), false);
+            } else {
+                if (circ) CC1D_MULTI_BY_L(__half, 8, true);
+                else if (S == W) CC1D_MULTI_BY_L(__half, W, false);
+                else if (W >= 3) CC1D_MULTI_BY_L(__half, (W >= 3 ? W - 1 : W), false);
+            }
+        }););
+#undef CC1D_MULTI_BY_L
+#undef CC1D_LAUNCH_MULTI
+        return check_launch();
+    }
     if (cf_state_ok) {
         a.ncols = (uint32_t)(p.dim / C);
         a.ncolblk = 0;

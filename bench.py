@@ -6,8 +6,8 @@
 Workload (N = 1): the Mamba-1 2.8B-shape prefill, forward + backward, bf16:
 x (8, 5120, 2048) channel-first, weight (5120, 4) / bias bf16, SiLU.  One step = one forward
 plus one backward over one batch.  At N > 1 every rank runs the same per-GPU batch (weak
-scaling) and each step ends with the single exchange of the packed fp32 dweight/dbias (inside
-the backward's finishing kernel over NVLink peer memory; NCCL when that cannot be set up).
+scaling) and each step ends with the single exchange of the packed fp32 dweight/dbias (one
+kernel per rank over NVLink peer memory; NCCL when that cannot be set up).
 The timed steps are CUDA-graph replays.  Extra keys: `kernels` (forward and backward timed
 back to back), `secondary` (the packed varlen prefill, the prefill with conv states and the
 decode update at N = 1; the channel-sharded decode update and the strong-scaling step at N > 1).
@@ -36,9 +36,9 @@ UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes of one launch of the backward kernel, from an ncu capture of this workload:
-# dram__bytes_read.sum + dram__bytes_write.sum (write-back of the last ~42 MB of dx is still
+# dram__bytes_read.sum + dram__bytes_write.sum (write-back of the last ~26 MB of dx is still
 # pending in L2 when the counter stops)
-BWD_KERNEL_DRAM_TRAFFIC_BYTES = 335684096 + 133846016
+BWD_KERNEL_DRAM_TRAFFIC_BYTES = 335688704 + 142050816
 
 
 def algorithmic_bytes(batch):
@@ -212,7 +212,7 @@ ALLREDUCE_TEXT = {
 }
 
 
-def workload_config(n_gpus, allreduce="fused", graph=True):
+def workload_config(n_gpus, allreduce="peer", graph=True):
     return {
         "workload": "C2 Mamba-1 2.8B-shape prefill fwd+bwd: x (8,5120,2048) bf16 channel-first per GPU, "
                     "weight (5120,4)+bias bf16, SiLU, dout N(0,1), seed 1",
@@ -296,7 +296,7 @@ def run_b200(args):
                 from causal_conv1d_b200.distributed import PeerGradReducer
                 n = grads[0][0].numel()
                 # a wait of up to ~4 s: ranks reach their first replay at different times
-                if mode == "peer":
+                if mode in ("peer", "auto"):
                     reducer = PeerGradReducer(n, spin_limit=1 << 24)
                 else:
                     fused_reducer = PeerGradReducer(n, fused=True, spin_limit=1 << 24)
@@ -310,7 +310,7 @@ def run_b200(args):
                 reducer = fused_reducer = aligner = None
                 peer_args, mode = {}, "nccl"
             elif mode == "auto":
-                mode = "fused"
+                mode = "peer"
     split = mode in ("fused", "peer")            # finishing kernel / exchange on a side branch
     use_graph = mode != "nccl" and not args.no_graph
     side = torch.cuda.Stream() if split else None
@@ -574,19 +574,19 @@ def run_b200(args):
             "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
             "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": workload_config(world, mode if world > 1 else "fused", use_graph),
+            "config": workload_config(world, mode if world > 1 else "peer", use_graph),
             "clocks": clocks.summary(),
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": k_e2e, "api": "causal_conv1d_fn + autograd backward, pinned host tensors; copy-in / kernels / copy-out of "
                            "consecutive steps overlap on three streams"},
             "gpu_launches": launches_per_step * K,
-            "roofline": {"bound": "hbm", "kernel": "bwd_cf_vec_kernel (+ reduce_partials_kernel, same launch pair)",
+            "roofline": {"bound": "hbm", "kernel": "bwd_cf_wide_kernel (+ reduce_partials_kernel, same launch pair)",
                          "achieved": round(bwd_gbs, 1), "peak": peak, "unit": UNIT, "frac": round(bwd_gbs / peak, 4),
                          "traffic": BWD_KERNEL_DRAM_TRAFFIC_BYTES, "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": bwd_b, "avg_launch_ms": round(bwd_ms, 5),
                          "launches_timed": n_split, "frac_of_nominal_8TBs": round(bwd_gbs / NOMINAL_HBM_GBS, 4)},
             "kernels": {"fwd_cf_vec_kernel": {"gbs": round(fwd_gbs, 1), "ms": round(fwd_ms, 5), "frac": round(fwd_gbs / peak, 4)},
-                        "bwd_cf_vec_kernel + reduce_partials_kernel": {"gbs": round(bwd_gbs, 1), "ms": round(bwd_ms, 5),
+                        "bwd_cf_wide_kernel + reduce_partials_kernel": {"gbs": round(bwd_gbs, 1), "ms": round(bwd_ms, 5),
                                                                        "frac": round(bwd_gbs / peak, 4)},
                         "step": {"gbs": round(value / world, 1), "ms": round(ms_per_step, 5), "frac": round(value / world / peak, 4)},
                         "launches_timed": n_split, "clocks": clocks_split.summary()},
@@ -913,9 +913,9 @@ def main():
     ap.add_argument("--buffer-sets", type=int, default=3, help="rotating input/output sets (profiling: 1)")
     ap.add_argument("--skip-e2e", action="store_true", help="kernel loop only (for ncu captures)")
     ap.add_argument("--allreduce", default="auto", choices=["auto", "nccl", "peer", "fused"],
-                    help="N > 1: auto (default) = fused when peer memory can be set up on every rank, else nccl; fused: the "
-                         "exchange inside the backward's finishing kernel; peer: the one-shot peer-memory kernel; nccl: "
-                         "NCCL all-reduce launched from the host")
+                    help="N > 1: auto (default) = peer when peer memory can be set up on every rank, else nccl; peer: the "
+                         "one-shot peer-memory all-reduce kernel after the backward; fused: the exchange inside the "
+                         "backward's finishing kernel; nccl: NCCL all-reduce launched from the host")
     ap.add_argument("--no-graph", action="store_true", help="launch every timed step from the host instead of replaying CUDA graphs")
     ap.add_argument("--no-secondary", action="store_true", help="skip the extra workloads reported under `secondary`")
     ap.add_argument("--measure-allreduce", action="store_true",

@@ -6,6 +6,8 @@
 // first) or fixed-order shared-memory sum over the CTA's token chunks (channel-last) -> one
 // partial row per warp unit / CTA in the caller's workspace -> reduce_partials_kernel sums
 // the rows in index order.  No float atomics anywhere, so repeated runs are bitwise equal.
+// Channel-first rows of 16-bit elements made of whole groups on 32-byte aligned rows take
+// bwd_cf_wide_kernel (32 bytes per lane, two of the four halos of a vector pair inside the lane).
 //
 // Replaces csrc/causal_conv1d_bwd.cu:53-259 (channel-first), :329-589 (channel-last) and
 // the deterministic-mode workspaces + ATen sums of csrc/causal_conv1d.cpp:388-462.

@@ -4,7 +4,9 @@
 // consecutive 16-byte vectors of one row.  A lane owns vector (j * 32 + lane); the
 // (width-1)-element halo comes from the neighbouring lane by warp shuffle, only lane 0 of a
 // unit's first vector re-reads one vector from global.  No shared memory, no barrier, every
-// x byte is requested from DRAM once.
+// x byte is requested from DRAM once.  16-bit rows made of whole groups on 32-byte aligned
+// rows take fwd_cf_wide_kernel: 32 bytes per lane (256-bit loads and stores), arithmetic on
+// fp32 pairs, half of the halos inside the lane.
 //
 // Channel-last (x[b, :, t] contiguous): a thread owns one 16-byte vector of channels and
 // slides down `tpt` consecutive tokens keeping the last width-1 vectors in registers; a
@@ -114,6 +116,108 @@ __global__ void __launch_bounds__(256) fwd_cf_vec_kernel(const FwdCfArgs a) {
     }
 }
 
+// ---- 16-bit I/O, rows made of whole groups, 32-byte aligned: 32 bytes per lane ----------------
+// A lane owns slots of 16 consecutive elements (two 16-byte vectors A, B moved by one 256-bit
+// load / store; a warp instruction covers 1 KB of the row).  The arithmetic runs on fp32 pairs
+// (A[i], B[i]) (FFMA2): B's left halo is A's tail, already in the lane, so only A's halo (the
+// previous lane's B tail, 2 shuffles per 16 elements) crosses lanes.
+#ifndef CC1D_FWD_WIDE
+#define CC1D_FWD_WIDE 1
+#endif
+#ifndef CC1D_FWD_WIDE_THREADS
+#define CC1D_FWD_WIDE_THREADS 256
+#endif
+#ifndef CC1D_FWD_WIDE_MINBLK
+#define CC1D_FWD_WIDE_MINBLK 4       // 64 registers, 32 warps per SM
+#endif
+__device__ __forceinline__ void fwd_ld32(uint4 &a, uint4 &b, const void *p) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p));
+}
+__device__ __forceinline__ void fwd_st32(void *p, const uint4 &a, const uint4 &b) {
+    asm volatile("st.global.cs.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 :: "l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
+}
+
+template <typename T, int W, bool kSilu, int kSlots>
+__global__ void __launch_bounds__(CC1D_FWD_WIDE_THREADS, CC1D_FWD_WIDE_MINBLK) fwd_cf_wide_kernel(const FwdCfArgs a) {
+    pdl_wait();
+    static_assert(sizeof(T) == 2, "16-bit I/O only");
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    constexpr uint32_t kSlotElems = 32 * 16, kGroupElems = kSlots * kSlotElems;
+    const int lane = threadIdx.x & 31;
+    const int src_prev = (lane + 31) & 31;
+    const uint32_t warps_per_cta = blockDim.x >> 5;
+    const uint32_t nwarps = gridDim.x * warps_per_cta;
+
+    for (uint32_t unit = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); unit < a.n_units; unit += nwarps) {
+        const uint32_t row = unit / a.upr;
+        const uint32_t seg = unit - row * a.upr;
+        const uint32_t b = row / a.dim;
+        const uint32_t c = row - b * a.dim;
+        const T *__restrict__ xr = reinterpret_cast<const T *>(a.x) + b * a.x_bs + c * a.x_cs;
+        T *__restrict__ outr = reinterpret_cast<T *>(a.out) + b * a.o_bs + c * a.o_cs;
+        const uint32_t g0 = seg * a.gpu;
+        const uint32_t g1 = g0 + a.gpu < a.gpr ? g0 + a.gpu : a.gpr;
+
+        uint4 xa[kSlots], xb[kSlots];
+        #pragma unroll
+        for (int j = 0; j < kSlots; ++j) fwd_ld32(xa[j], xb[j], xr + g0 * kGroupElems + j * kSlotElems + lane * 16);
+        // lane 31: the 4 elements of x before the group (zeros at the row start)
+        uint32_t cz = 0, cw = 0;
+        if (lane == 31 && g0 > 0) {
+            const uint2 t = *reinterpret_cast<const uint2 *>(xr + g0 * kGroupElems - 4);
+            cz = t.x; cw = t.y;
+        }
+        const float pre = kTanh ? 0.5f : 1.f;     // the tanh form of SiLU works on y/2
+        float2 wv[W];
+        #pragma unroll
+        for (int k = 0; k < W; ++k) wv[k] = splat2(pre * load_w(a.weight, c * a.w_cs + k * a.w_ws, a.wtype));
+        const float2 bv = splat2(a.bias != nullptr ? pre * load_w(a.bias, c, a.wtype) : 0.f);
+
+        for (uint32_t g = g0; g < g1; ++g) {
+            #pragma unroll
+            for (int j = 0; j < kSlots; ++j) {
+                // left halo of A: the previous lane's B tail; lane 0 gets what lane 31 holds of the slot before
+                const uint32_t oz = j > 0 ? xb[j > 0 ? j - 1 : 0].z : cz, ow = j > 0 ? xb[j > 0 ? j - 1 : 0].w : cw;
+                uint32_t pz = 0;
+                if (W >= 4) pz = __shfl_sync(kFullMask, lane == 31 ? oz : xb[j].z, src_prev);
+                const uint32_t pw = __shfl_sync(kFullMask, lane == 31 ? ow : xb[j].w, src_prev);
+                float2 xx[W - 1 + 8];
+                {
+                    const float2 pa = unpack_pair<T>(pz), pb = unpack_pair<T>(pw);
+                    const float p[4] = {pa.x, pa.y, pb.x, pb.y};   // elements 4..7 of the vector before A
+                    float af[8], bf[8];
+                    unpack<T>(xa[j], af); unpack<T>(xb[j], bf);
+                    #pragma unroll
+                    for (int k = 0; k < W - 1; ++k) xx[k] = make_float2(p[4 - (W - 1) + k], af[8 - (W - 1) + k]);
+                    #pragma unroll
+                    for (int i = 0; i < 8; ++i) xx[W - 1 + i] = make_float2(af[i], bf[i]);
+                }
+                float o0[8], o1[8];
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float2 y = bv;
+                    #pragma unroll
+                    for (int k = 0; k < W; ++k) y = fma2(wv[k], xx[i + k], y);
+                    if (kSilu) {
+                        if (kTanh) y = fma2(y, make_float2(tanh_approx(y.x), tanh_approx(y.y)), y);   // silu(2h) = h + h tanh(h)
+                        else y = make_float2(silu_f(y.x), silu_f(y.y));
+                    }
+                    o0[i] = y.x; o1[i] = y.y;
+                }
+                fwd_st32(outr + g * kGroupElems + j * kSlotElems + lane * 16, pack<T>(o0), pack<T>(o1));
+            }
+            if (g + 1 < g1) {
+                // lane 31 keeps the tail of the group for lane 0 of the next one, then the next group's vectors
+                cz = xb[kSlots - 1].z; cw = xb[kSlots - 1].w;
+                #pragma unroll
+                for (int j = 0; j < kSlots; ++j) fwd_ld32(xa[j], xb[j], xr + (g + 1) * kGroupElems + j * kSlotElems + lane * 16);
+            }
+        }
+    }
+}
+
 // Any alignment / row stride: one output element per thread, lanes along seqlen.
 template <typename T, int W, bool kSilu>
 __global__ void __launch_bounds__(256) fwd_cf_scalar_kernel(const FwdCfArgs a) {
@@ -173,6 +277,23 @@ int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
         a.n_units = (uint32_t)n_units;
         const uint64_t ctas = (n_units + 7) / 8;
         const bool full = p.seqlen % V == 0 && vpr % (32 * kVecs) == 0;
+        const bool wide = CC1D_FWD_WIDE && kCfVecs % 2 == 0 && full && p.itype != CC1D_F32 &&
+                          ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.out)) & 31u) == 0 &&
+                          (a.x_bs | a.x_cs | a.o_bs | a.o_cs) % 16 == 0;
+        if (wide) {
+            const uint64_t wctas = (n_units + CC1D_FWD_WIDE_THREADS / 32 - 1) / (CC1D_FWD_WIDE_THREADS / 32);
+            if (p.itype == CC1D_BF16) {
+                using T = __nv_bfloat16;
+                CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
+                    launch_k(fwd_cf_wide_kernel<T, W, kSilu, kCfVecs / 2>, dim3((unsigned)wctas), dim3(CC1D_FWD_WIDE_THREADS), 0, stream, a);
+                }););
+            } else {
+                using T = __half;
+                CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
+                    launch_k(fwd_cf_wide_kernel<T, W, kSilu, kCfVecs / 2>, dim3((unsigned)wctas), dim3(CC1D_FWD_WIDE_THREADS), 0, stream, a);
+                }););
+            }
+        } else
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
             CC1D_DISPATCH_BOOL(full, kFull, {
                 auto kernel = fwd_cf_vec_kernel<T, W, kSilu, kFull, kVecs>;

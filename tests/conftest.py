@@ -87,7 +87,7 @@ class Golden:
     def __init__(self):
         d = os.path.join(ROOT, "tests", "golden")
         self.arrays, self.meta = {}, {}
-        for stem in ("golden", "golden_prefill"):      # one file per generating script
+        for stem in ("golden", "golden_prefill", "golden_gather"):      # one file per generating script
             self.arrays.update(np.load(os.path.join(d, stem + ".npz")))
             with open(os.path.join(d, stem + ".json")) as f:
                 self.meta.update(json.load(f)["cases"])

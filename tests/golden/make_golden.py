@@ -2,7 +2,7 @@
 
 Run once, in a container that has the reference checkout (it is not needed at test time):
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <reference checkout>
 
 The reference package is imported from the given path with its compiled module
 ``causal_conv1d_cuda`` stubbed (``causal_conv1d/cpp_functions.py:5`` imports it, the
@@ -46,7 +46,7 @@ def main(ref_path):
             if v is not None:
                 arrays[f"{case}/{k}"] = v
 
-    # ---- fwd + bwd cases (incl. BASELINE config 1) --------------------------------
+    # ---- fwd + bwd cases (incl. the small fp32 plumbing configuration: batch 2, dim 64, seqlen 512) --------------------------------
     def fwd_bwd_case(name, seed, batch, dim, seqlen, width, itype, wtype, has_bias, silu,
                      init, final, uniform_w=False):
         torch.manual_seed(seed)
@@ -177,4 +177,6 @@ def main(ref_path):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    main(sys.argv[1])

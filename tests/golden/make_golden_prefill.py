@@ -1,7 +1,7 @@
 """Golden fixtures for the packed variable-length prefill with per-sequence conv states,
 generated from the REFERENCE's own PyTorch functions.
 
-    python tests/golden/make_golden_prefill.py /root/reference
+    python tests/golden/make_golden_prefill.py <reference checkout>
 
 The reference has no single call for this case; its semantics are pinned the way the
 reference's seq_idx test pins its kernel (``tests/test_causal_conv1d.py:448-454``): the pack
@@ -87,4 +87,6 @@ def main(ref_path):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    main(sys.argv[1])

@@ -214,3 +214,68 @@ def test_c5_fp32_and_fp16_reduced_batch():
         assert_close_sum(w.grad, dw_ref, 2e-5 if itype == torch.float32 else 3e-3, f"dweight {itype}")
         del x, dout, out, dw_ref
         torch.cuda.empty_cache()
+
+
+# The stress sweep at FULL size (batch 32) for the dtype / width / activation / layout combinations
+# beyond the two bf16 width-4 cases above: fp32 in both layouts (2^31 elements of 4 bytes: byte offsets
+# beyond 2^33), widths 2 and 3 and no activation for each 16-bit dtype.  Channel-last cases run with
+# return_final_states and a non-zero dfinal_states.
+@pytest.mark.parametrize("itype,width,channel_last,silu", [
+    (torch.float32, 4, False, True),
+    (torch.float32, 3, True, False),
+    (torch.float16, 2, False, False),
+    (torch.float16, 3, True, True),
+    (torch.bfloat16, 3, False, True),
+    (torch.bfloat16, 2, True, False),
+])
+def test_c5_stress_sweep_full_size(itype, width, channel_last, silu):
+    torch.manual_seed(4)
+    B, D, L = 32, 8192, 8192
+    act = "silu" if silu else None
+    if channel_last:
+        x = torch.randn(B, L, D, device=DEV, dtype=itype).transpose(1, 2)
+        dout = torch.randn(B, L, D, device=DEV, dtype=itype).transpose(1, 2)
+        dfin = torch.randn(B, width - 1, D, device=DEV, dtype=itype).transpose(1, 2)
+    else:
+        x = torch.randn(B, D, L, device=DEV, dtype=itype)
+        dout = torch.randn(B, D, L, device=DEV, dtype=itype)
+        dfin = None
+    x.requires_grad_()
+    w = _uniform((D, width), torch.float32, 11).requires_grad_()
+    b = _uniform((D,), torch.float32, 12).requires_grad_()
+
+    def run():
+        x.grad = w.grad = b.grad = None
+        if channel_last:
+            out, fs = _fn()(x, w, b, return_final_states=True, activation=act)
+            torch.autograd.backward([out, fs], [dout, dfin])
+            return out, fs
+        out = _fn()(x, w, b, activation=act)
+        out.backward(dout)
+        return out, None
+
+    out, fs = run()
+    if channel_last:
+        assert torch.equal(fs, x.detach()[:, :, -(width - 1):]), "final_states must be the last width-1 inputs, bit-exact"
+    dx, dw, db = x.grad, w.grad.clone(), b.grad.clone()
+    dw_ref = torch.zeros(D, width, device=DEV, dtype=torch.float64)
+    db_ref = torch.zeros(D, device=DEV, dtype=torch.float64)
+    for i in range(B):
+        r = conv_grads64(x.detach()[i:i + 1], w.detach(), b.detach(), dout[i:i + 1], None, None,
+                         None if dfin is None else dfin[i:i + 1], act)
+        if i % 8 == 0 or i == B - 1:   # elementwise checks on some slices (the last one holds the largest offsets)
+            assert_close(out[i:i + 1], r["out"].to(itype), TOL[itype], f"out[{i}]")
+            assert_close(dx[i:i + 1], r["dx"].to(itype), TOL[itype], f"dx[{i}]")
+        dw_ref += r["dweight"]
+        db_ref += r["dbias"]
+        del r
+    sum_tol = 2e-5 if itype == torch.float32 else 1e-3
+    assert_close_sum(dw, dw_ref, sum_tol, "dweight (262144 terms per entry)")
+    assert_close_sum(db, db_ref, sum_tol, "dbias")
+    del dw_ref, db_ref, out
+    for _ in range(9):      # 10 backward runs in all: dweight / dbias / dx bitwise reproducible
+        run()
+        assert torch.equal(w.grad, dw) and torch.equal(b.grad, db), "dweight/dbias must be bitwise reproducible"
+    assert torch.equal(x.grad, dx)
+    del x, dout, dx
+    torch.cuda.empty_cache()

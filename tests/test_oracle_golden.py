@@ -59,6 +59,22 @@ def test_update(golden, case):
     check(out.to(it), g("out", it), it, wt, "out")
 
 
+@pytest.mark.parametrize("case", golden_names("update_gather"))
+def test_update_gather(golden, case):
+    """conv_state_indices with padded entries: gather -> causal_conv1d_update_ref -> scatter, stored by
+    tests/golden/make_golden_gather.py."""
+    m = golden.meta[case]
+    it, wt = DT[m["itype"]], DT[m["wtype"]]
+    g = lambda k, dt=None: golden.get(case, k, dt)
+    out, st = oracle.update(g("x", it), g("conv_state", it), g("weight", wt), g("bias", wt),
+                            activation="silu" if m["silu"] else None, cache_seqlens=g("cache_seqlens"),
+                            conv_state_indices=g("conv_state_indices"))
+    assert torch.equal(st.to(it), g("conv_state_out", it)), "pool must be bit-exact"
+    idx = g("conv_state_indices")
+    assert (out[idx < 0] == 0).all()
+    check(out.to(it), g("out", it), it, wt, "out")
+
+
 @pytest.mark.parametrize("case", golden_names("varlen_states"))
 def test_varlen_states(golden, case):
     m = golden.meta[case]

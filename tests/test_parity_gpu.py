@@ -115,6 +115,26 @@ def test_golden_update(golden, case, state_layout):
     check(out, g("out", it), it, wt, "out")
 
 
+@pytest.mark.parametrize("state_layout", ["channel_last", "channel_first"])
+@pytest.mark.parametrize("case", golden_names("update_gather"))
+def test_golden_update_gather(golden, case, state_layout):
+    """conv_state_indices (with padded entries) against the fixtures made from the reference's
+    causal_conv1d_update_ref by gather / scatter."""
+    m = golden.meta[case]
+    it, wt = DT[m["itype"]], DT[m["wtype"]]
+    g = lambda k, dt=None: None if golden.get(case, k, dt) is None else golden.get(case, k, dt).to(DEV)
+    x, pool = g("x", it), g("conv_state", it)
+    if state_layout == "channel_last":
+        pool = pool.transpose(1, 2).contiguous().transpose(1, 2)
+        x = x.transpose(1, 2).contiguous().transpose(1, 2)
+    out = _api().causal_conv1d_update(x, pool, g("weight", wt), g("bias", wt), activation="silu" if m["silu"] else None,
+                                      cache_seqlens=g("cache_seqlens"), conv_state_indices=g("conv_state_indices"))
+    assert torch.equal(pool.cpu(), golden.get(case, "conv_state_out", it)), "pool must be bit-exact"
+    idx = g("conv_state_indices")
+    assert (out[idx < 0] == 0).all()
+    check(out, golden.get(case, "out", it), it, wt, "out")
+
+
 @pytest.mark.parametrize("case", golden_names("varlen_states"))
 def test_golden_varlen_states(golden, case):
     m = golden.meta[case]

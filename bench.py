@@ -585,7 +585,7 @@ def run_b200(args):
                          "traffic": BWD_KERNEL_DRAM_TRAFFIC_BYTES, "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": bwd_b, "avg_launch_ms": round(bwd_ms, 5),
                          "launches_timed": n_split, "frac_of_nominal_8TBs": round(bwd_gbs / NOMINAL_HBM_GBS, 4)},
-            "kernels": {"fwd_cf_vec_kernel": {"gbs": round(fwd_gbs, 1), "ms": round(fwd_ms, 5), "frac": round(fwd_gbs / peak, 4)},
+            "kernels": {"fwd_cf_wide_kernel": {"gbs": round(fwd_gbs, 1), "ms": round(fwd_ms, 5), "frac": round(fwd_gbs / peak, 4)},
                         "bwd_cf_wide_kernel + reduce_partials_kernel": {"gbs": round(bwd_gbs, 1), "ms": round(bwd_ms, 5),
                                                                        "frac": round(bwd_gbs / peak, 4)},
                         "step": {"gbs": round(value / world, 1), "ms": round(ms_per_step, 5), "frac": round(value / world / peak, 4)},

@@ -220,7 +220,8 @@ def workload_config(n_gpus, allreduce="peer", graph=True):
         "width": WIDTH, "activation": "silu",
         "parallelism": f"batch-sharded dp{n_gpus}, {ALLREDUCE_TEXT[allreduce]}" if n_gpus > 1 else "single GPU",
         "l2": "inputs larger than L2: 3 rotating buffer sets of 671 MB (x, dout, out, dx) per GPU",
-        "launch": ("the K timed steps are CUDA-graph replays (graphs of up to 60 steps captured after the warm-up)"
+        "launch": ("the K timed steps are CUDA-graph replays (graphs of up to 60 steps captured after the warm-up); in a "
+                   "captured step the backward's finishing kernel runs on a side branch beside the next forward"
                    if graph else "every step launched from the host"),
         "kernel_split": "forward launches back to back, then backward launches back to back, after the timed region "
                         "(CUDA events around each loop)",
@@ -311,8 +312,10 @@ def run_b200(args):
                 peer_args, mode = {}, "nccl"
             elif mode == "auto":
                 mode = "peer"
-    split = mode in ("fused", "peer")            # finishing kernel / exchange on a side branch
     use_graph = mode != "nccl" and not args.no_graph
+    # finishing kernel (+ exchange) on a side branch of the captured step, beside the next forward:
+    # nothing in the next step depends on dweight / dbias
+    split = mode in ("fused", "peer") or (mode == "single" and use_graph)
     side = torch.cuda.Stream() if split else None
     pending = [None, None]                       # NCCL work handles
     side_done = [None, None]                     # side-branch events per gradient buffer
@@ -436,11 +439,15 @@ def run_b200(args):
                                                          None, True), n_split)
         bwd_ms = loop_ms(lambda i: ext.causal_conv1d_bwd(sets[i % nsets][0], weight, bias, sets[i % nsets][1], None, None, None,
                                                          sets[i % nsets][3], dw_l, db_l, None, True, False), n_split)
+        # the dominant kernel alone (phase 1: dx and the partial rows; the finishing kernel not launched)
+        bwd_main_ms = loop_ms(lambda i: ext.causal_conv1d_bwd(sets[i % nsets][0], weight, bias, sets[i % nsets][1], None, None,
+                                                              None, sets[i % nsets][3], dw_l, db_l, None, True, False,
+                                                              phase=1, workspace=scratch[0]), n_split)
     barrier()
 
     if args.skip_e2e:
         if rank == 0:
-            print(json.dumps({"partial": True, "ms_per_step": ms_per_step, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+            print(json.dumps({"partial": True, "ms_per_step": ms_per_step, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "bwd_main_ms": bwd_main_ms,
                               "value": value, "mode": mode, "graph": use_graph}), flush=True)
         if world > 1:
             dist.destroy_process_group()
@@ -456,24 +463,34 @@ def run_b200(args):
     # Three streams, the way a host-fed pipeline is normally written: step i's host->device copies,
     # step i-1's kernels and step i-2's device->host copies overlap (PCIe is full duplex).  Every
     # step still pays for all of its own copies inside the timed region.
-    s_in, s_run, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    # With --e2e-copy-streams n every large tensor travels as n batch slices on n streams per direction
+    # (several copy engines per direction keep more of the PCIe link busy than one).
+    ncs = max(1, min(B, args.e2e_copy_streams))
+    cuts = [(k * B // ncs, (k + 1) * B // ncs) for k in range(ncs)]
+    s_run = torch.cuda.Stream()
+    s_ins, s_outs = [torch.cuda.Stream() for _ in range(ncs)], [torch.cuda.Stream() for _ in range(ncs)]
+    s_in, s_out = s_ins[0], s_outs[0]
     slots = [{"x": torch.empty(B, DIM, SEQLEN, device=dev, dtype=torch.bfloat16),
               "dout": torch.empty(B, DIM, SEQLEN, device=dev, dtype=torch.bfloat16),
-              "in_done": torch.cuda.Event(), "run_done": torch.cuda.Event(), "out_done": torch.cuda.Event()}
+              "in_done": [torch.cuda.Event() for _ in range(ncs)], "run_done": torch.cuda.Event(),
+              "out_done": [torch.cuda.Event() for _ in range(ncs)]}
              for _ in range(2)]
     wps = [weight.clone().requires_grad_() for _ in range(2)]
     bps = [bias.clone().requires_grad_() for _ in range(2)]
 
     def e2e_step(i):
         sl, wq, bq = slots[i % 2], wps[i % 2], bps[i % 2]
-        with torch.cuda.stream(s_in):
-            s_in.wait_event(sl["run_done"])          # the slot's previous kernels have read x / dout
-            sl["x"].copy_(hx, non_blocking=True)
-            sl["dout"].copy_(hdout, non_blocking=True)
-            sl["in_done"].record()
+        for j, (lo, hi) in enumerate(cuts):
+            st = s_ins[j]
+            with torch.cuda.stream(st):
+                st.wait_event(sl["run_done"])        # the slot's previous kernels have read x / dout
+                sl["x"][lo:hi].copy_(hx[lo:hi], non_blocking=True)
+                sl["dout"][lo:hi].copy_(hdout[lo:hi], non_blocking=True)
+                sl["in_done"][j].record(st)
         with torch.cuda.stream(s_run):
-            s_run.wait_event(sl["in_done"])
-            s_run.wait_event(sl["out_done"])         # the slot's previous results have left the device
+            for j in range(ncs):
+                s_run.wait_event(sl["in_done"][j])
+                s_run.wait_event(sl["out_done"][j])  # the slot's previous results have left the device
             xd = sl["x"].detach().requires_grad_()
             wq.grad = bq.grad = None
             out = causal_conv1d_fn(xd, wq, bq, activation="silu")
@@ -482,22 +499,28 @@ def run_b200(args):
                 dist.all_reduce(wq.grad)
                 dist.all_reduce(bq.grad)
             sl["run_done"].record()
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(sl["run_done"])
-            for t in (out, xd.grad, wq.grad, bq.grad):
-                t.record_stream(s_out)
-            hout.copy_(out.detach(), non_blocking=True)
-            hdx.copy_(xd.grad, non_blocking=True)
-            hdw.copy_(wq.grad, non_blocking=True)
-            hdb.copy_(bq.grad, non_blocking=True)
-            sl["out_done"].record()
+        od, dxg = out.detach(), xd.grad
+        for j, (lo, hi) in enumerate(cuts):
+            st = s_outs[j]
+            with torch.cuda.stream(st):
+                st.wait_event(sl["run_done"])
+                for t in (od, dxg, wq.grad, bq.grad):
+                    t.record_stream(st)
+                hout[lo:hi].copy_(od[lo:hi], non_blocking=True)
+                hdx[lo:hi].copy_(dxg[lo:hi], non_blocking=True)
+                if j == 0:
+                    hdw.copy_(wq.grad, non_blocking=True)
+                    hdb.copy_(bq.grad, non_blocking=True)
+                sl["out_done"][j].record(st)
+
+    all_streams = [s_run] + s_ins + s_outs
 
     def e2e_join():
         cur = torch.cuda.current_stream()
-        for st in (s_in, s_run, s_out):
+        for st in all_streams:
             cur.wait_stream(st)
 
-    for st in (s_in, s_run, s_out):
+    for st in all_streams:
         st.wait_stream(torch.cuda.current_stream())
     for i in range(2):
         e2e_step(i)
@@ -505,7 +528,7 @@ def run_b200(args):
     barrier()
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s2.record()
-    for st in (s_in, s_run, s_out):
+    for st in all_streams:
         st.wait_event(s2)
     for i in range(k_e2e):
         e2e_step(i)
@@ -569,6 +592,8 @@ def run_b200(args):
         peak, peak_src = measured_peak()
         bwd_gbs = bwd_b / (bwd_ms * 1e-3) / 1e9
         fwd_gbs = fwd_b / (fwd_ms * 1e-3) / 1e9
+        main_b = bwd_b - (WIDTH + 1) * DIM * 4          # the fp32 gradients are written by the finishing kernel
+        main_gbs = main_b / (bwd_main_ms * 1e-3) / 1e9
         launches_per_step = 3 + (1 if mode == "peer" else 0)
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm,
@@ -578,14 +603,17 @@ def run_b200(args):
             "clocks": clocks.summary(),
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": k_e2e, "api": "causal_conv1d_fn + autograd backward, pinned host tensors; copy-in / kernels / copy-out of "
-                           "consecutive steps overlap on three streams"},
+                           f"consecutive steps overlap ({ncs} copy stream(s) per direction)"},
             "gpu_launches": launches_per_step * K,
-            "roofline": {"bound": "hbm", "kernel": "bwd_cf_wide_kernel (+ reduce_partials_kernel, same launch pair)",
-                         "achieved": round(bwd_gbs, 1), "peak": peak, "unit": UNIT, "frac": round(bwd_gbs / peak, 4),
+            "roofline": {"bound": "hbm", "kernel": "bwd_cf_wide_kernel (launched alone: cc1d_bwd phase 1)",
+                         "achieved": round(main_gbs, 1), "peak": peak, "unit": UNIT, "frac": round(main_gbs / peak, 4),
                          "traffic": BWD_KERNEL_DRAM_TRAFFIC_BYTES, "peak_source": peak_src,
-                         "algorithmic_bytes_per_launch": bwd_b, "avg_launch_ms": round(bwd_ms, 5),
-                         "launches_timed": n_split, "frac_of_nominal_8TBs": round(bwd_gbs / NOMINAL_HBM_GBS, 4)},
+                         "algorithmic_bytes_per_launch": main_b, "avg_launch_ms": round(bwd_main_ms, 5),
+                         "launches_timed": n_split, "frac_of_nominal_8TBs": round(main_gbs / NOMINAL_HBM_GBS, 4),
+                         "with_finishing_kernel": {"achieved": round(bwd_gbs, 1), "frac": round(bwd_gbs / peak, 4),
+                                                   "avg_launch_pair_ms": round(bwd_ms, 5)}},
             "kernels": {"fwd_cf_wide_kernel": {"gbs": round(fwd_gbs, 1), "ms": round(fwd_ms, 5), "frac": round(fwd_gbs / peak, 4)},
+                        "bwd_cf_wide_kernel": {"gbs": round(main_gbs, 1), "ms": round(bwd_main_ms, 5), "frac": round(main_gbs / peak, 4)},
                         "bwd_cf_wide_kernel + reduce_partials_kernel": {"gbs": round(bwd_gbs, 1), "ms": round(bwd_ms, 5),
                                                                        "frac": round(bwd_gbs / peak, 4)},
                         "step": {"gbs": round(value / world, 1), "ms": round(ms_per_step, 5), "frac": round(value / world / peak, 4)},
@@ -916,6 +944,8 @@ def main():
                     help="N > 1: auto (default) = peer when peer memory can be set up on every rank, else nccl; peer: the "
                          "one-shot peer-memory all-reduce kernel after the backward; fused: the exchange inside the "
                          "backward's finishing kernel; nccl: NCCL all-reduce launched from the host")
+    ap.add_argument("--e2e-copy-streams", type=int, default=2,
+                    help="streams (batch slices in flight) per direction in the end-to-end measurement")
     ap.add_argument("--no-graph", action="store_true", help="launch every timed step from the host instead of replaying CUDA graphs")
     ap.add_argument("--no-secondary", action="store_true", help="skip the extra workloads reported under `secondary`")
     ap.add_argument("--measure-allreduce", action="store_true",

@@ -17,7 +17,10 @@
 
 namespace cc1d {
 
-constexpr int kTilingSMs = 148;  // tiling (and so workspace size) is fixed for B200, not queried
+// SM count the channel-last tiling is sized for.  A constant, not a device query: the library is built
+// for sm_100a (B200, 148 SMs) only, and cc1d_bwd_workspace_bytes() is host-only arithmetic that must
+// give the answer the launcher will use even when no device is current.
+constexpr int kTilingSMs = 148;
 
 // ======================================================================================
 // final reduction of the partial rows

@@ -23,14 +23,15 @@ __device__ __forceinline__ int64_t load_cu(const void *cu, int64_t i, int is64) 
 }
 
 // kVec: thread copies one 16-byte vector of channels (x and states both channel-contiguous);
-// otherwise one element with arbitrary strides.  grid = (ncolblk * state_len, batch).
+// otherwise one element with arbitrary strides.  Flat grid over (batch entry, state slot, column block).
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(128) varlen_states_kernel(const VarlenArgs a) {
     pdl_wait();
     constexpr int C = kVec ? Elem<T>::kVec : 1;
     const uint32_t cb = blockIdx.x % a.ncolblk;
-    const int64_t k = blockIdx.x / a.ncolblk;          // state slot
-    const int64_t b = blockIdx.y;
+    const uint32_t rest = blockIdx.x / a.ncolblk;
+    const int64_t k = rest % (uint32_t)a.state_len;    // state slot
+    const int64_t b = rest / (uint32_t)a.state_len;
     const uint32_t col = cb * 128 + threadIdx.x;
     if (col >= a.ncols) return;
     const int64_t end = load_cu(a.cu, b + 1, a.cu_is64);
@@ -51,7 +52,6 @@ __global__ void __launch_bounds__(128) varlen_states_kernel(const VarlenArgs a) 
 
 int launch_varlen_states(const cc1d_varlen_states_params &p, cudaStream_t stream) {
     if (p.batch == 0 || p.dim == 0 || p.state_len == 0) return CC1D_OK;
-    if (p.batch > 65535) return CC1D_ERR_TOO_LARGE;
     const int C = vec_elems(p.itype);
     VarlenArgs a;
     a.x = p.x; a.cu = p.cu_seqlens; a.states = p.states;
@@ -63,9 +63,10 @@ int launch_varlen_states(const cc1d_varlen_states_params &p, cudaStream_t stream
                      p.states_l_stride % C == 0;
     a.ncols = (uint32_t)(vec ? p.dim / C : p.dim);
     a.ncolblk = (a.ncols + 127) / 128;
-    const uint64_t gx = (uint64_t)a.ncolblk * (uint64_t)p.state_len;
+    if (p.state_len >= (1ll << 31) || p.batch >= (1ll << 31)) return CC1D_ERR_TOO_LARGE;
+    const uint64_t gx = (uint64_t)a.ncolblk * (uint64_t)p.state_len * (uint64_t)p.batch;
     if (gx >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
-    const dim3 grid((unsigned)gx, (unsigned)p.batch);
+    const dim3 grid((unsigned)gx);
     CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_BOOL(vec, kVec, {
         launch_k(varlen_states_kernel<T, kVec>, dim3(grid), dim3(128), 0, stream, a);
     }););

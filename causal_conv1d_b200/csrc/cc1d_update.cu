@@ -245,9 +245,10 @@ __global__ void __launch_bounds__(128, 4) update_cfstate_kernel(const UpdArgs a)
 // a channel adjacent: (batch, dim, L) contiguous), so the thread's tokens are L 16-byte vectors.
 //   linear (S == width-1 or width): per channel seq = [state | tokens]; output i is the dot product of
 //     the taps with seq[S-(W-1)+i ..]; the new state is seq[L .. L+S).
-//   circular (S == 8, one 16-byte vector per channel): the vector is rotated so that the write position
-//     cache_seqlens % 8 comes first (selects + funnel shifts: no dynamic register indexing), the window
-//     is then its last width-1 elements and the tokens go to its first L; rotated back and stored.
+//   circular (S == 8, one 16-byte vector per channel): one branch on the write position
+//     cache_seqlens % 8 (the same for the whole thread, nearly always for the whole warp), so that the
+//     window slots and the slots the tokens go to are compile-time positions in every case: no dynamic
+//     register indexing, no rotation.
 // A circular step rewrites the whole 16-byte row of every channel: the rows are 16 bytes, DRAM moves
 // 32-byte sectors, so nothing narrower than the row could be written anyway.
 template <typename T> __device__ __forceinline__ uint32_t bits_from_f(float v);
@@ -260,17 +261,48 @@ template <> __device__ __forceinline__ uint32_t bits_from_f<__half>(float v) {
     return (uint32_t)*reinterpret_cast<const unsigned short *>(&h);
 }
 
-// 8 16-bit elements in 4 registers, rotated left by n elements (element j <- element (j + n) % 8)
-__device__ __forceinline__ void rotate8(uint32_t (&r)[4], int n) {
-    uint32_t t0 = r[0], t1 = r[1], t2 = r[2], t3 = r[3], u;
-    if (n & 2) { u = t0; t0 = t1; t1 = t2; t2 = t3; t3 = u; }
-    if (n & 4) { u = t0; t0 = t2; t2 = u; u = t1; t1 = t3; t3 = u; }
-    if (n & 1) {
-        const uint32_t v0 = __funnelshift_r(t0, t1, 16), v1 = __funnelshift_r(t1, t2, 16),
-                       v2 = __funnelshift_r(t2, t3, 16), v3 = __funnelshift_r(t3, t0, 16);
-        t0 = v0; t1 = v1; t2 = v2; t3 = v3;
+// The 8 channels of a thread: `old` holds their S state elements each (flat c * S + s), `xr` their L
+// tokens (flat c * L + i); fills the new state `nw` and the outputs `ob` (both zero on entry).
+// kWr: the circular buffer's write position (linear mode: unused).
+template <typename T, int W, bool kSilu, int S, bool kCirc, int L, int kWr>
+__device__ __forceinline__ void cfstate_channels(const uint32_t (&old)[S * 4], const uint32_t (&xr)[L * 4],
+                                                 const float (&wv)[W][8], const float (&bv)[8], uint32_t (&nw)[S * 4],
+                                                 uint32_t (&ob)[L * 4]) {
+    constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    #pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        uint32_t seq[W - 1 + L];          // the window, then the tokens
+        #pragma unroll
+        for (int i = 0; i < L; ++i) seq[W - 1 + i] = Bits<T>::get(xr, c * L + i);
+        if (kCirc) {
+            // window: the width-1 slots before the write position; tokens go to slots kWr, kWr + 1, ... (mod S)
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) seq[k] = Bits<T>::get(old, c * S + (kWr - (W - 1) + k + S) % S);
+            #pragma unroll
+            for (int j = 0; j < S; ++j) {
+                const int i = (j - kWr + S) % S;      // token index that lands in slot j, if any
+                Bits<T>::put(nw, c * S + j, i < L ? seq[W - 1 + (i < L ? i : 0)] : Bits<T>::get(old, c * S + j));
+            }
+        } else {
+            uint32_t all[S + L];
+            #pragma unroll
+            for (int j = 0; j < S; ++j) all[j] = Bits<T>::get(old, c * S + j);
+            #pragma unroll
+            for (int i = 0; i < L; ++i) all[S + i] = seq[W - 1 + i];
+            #pragma unroll
+            for (int k = 0; k < W - 1; ++k) seq[k] = all[S - (W - 1) + k];
+            #pragma unroll
+            for (int t = 0; t < S; ++t) Bits<T>::put(nw, c * S + t, all[t + L]);
+        }
+        #pragma unroll
+        for (int i = 0; i < L; ++i) {
+            float acc = bv[c];
+            #pragma unroll
+            for (int k = 0; k < W; ++k) acc = fmaf(wv[k][c], Bits<T>::to_f(seq[i + k]), acc);
+            const float o = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
+            Bits<T>::put(ob, c * L + i, bits_from_f<T>(o));
+        }
     }
-    r[0] = t0; r[1] = t1; r[2] = t2; r[3] = t3;
 }
 
 template <typename T, int W, bool kSilu, int S, bool kCirc, int L>
@@ -313,46 +345,23 @@ __global__ void __launch_bounds__(128, 4) update_cfstate_multi_kernel(const UpdA
     for (int i = 0; i < S * 4; ++i) nw[i] = 0;
     #pragma unroll
     for (int i = 0; i < L * 4; ++i) ob[i] = 0;
-    int wr = 0;
-    if (kCirc) {
-        wr = cs % S;
+    if constexpr (kCirc) {
+        // The write position is the same for all channels of the thread (and, a few warps apart, of the
+        // warp): one branch on it, and every position inside a case is a compile-time constant.
+        int wr = cs % S;
         if (wr < 0) wr += S;
-    }
-    #pragma unroll
-    for (int c = 0; c < C; ++c) {
-        uint32_t seq[W - 1 + L];          // the window, then the tokens
-        if (kCirc) {
-            uint32_t row[4] = {old[4 * c], old[4 * c + 1], old[4 * c + 2], old[4 * c + 3]};
-            rotate8(row, wr);              // element 0 is now the write position
-            #pragma unroll
-            for (int k = 0; k < W - 1; ++k) seq[k] = Bits<T>::get(row, S - (W - 1) + k);
-            #pragma unroll
-            for (int i = 0; i < L; ++i) seq[W - 1 + i] = Bits<T>::get(xr, c * L + i);
-            uint32_t upd[4] = {0, 0, 0, 0};
-            #pragma unroll
-            for (int j = 0; j < S; ++j) Bits<T>::put(upd, j, j < L ? seq[W - 1 + j] : Bits<T>::get(row, j));
-            rotate8(upd, (S - wr) & (S - 1));
-            #pragma unroll
-            for (int j = 0; j < 4; ++j) nw[4 * c + j] = upd[j];
-        } else {
-            uint32_t all[S + L];
-            #pragma unroll
-            for (int j = 0; j < S; ++j) all[j] = Bits<T>::get(old, c * S + j);
-            #pragma unroll
-            for (int i = 0; i < L; ++i) all[S + i] = Bits<T>::get(xr, c * L + i);
-            #pragma unroll
-            for (int j = 0; j < W - 1 + L; ++j) seq[j] = all[S - (W - 1) + j];
-            #pragma unroll
-            for (int t = 0; t < S; ++t) Bits<T>::put(nw, c * S + t, all[t + L]);
+        switch (wr) {
+            case 0: cfstate_channels<T, W, kSilu, S, true, L, 0>(old, xr, wv, bv, nw, ob); break;
+            case 1: cfstate_channels<T, W, kSilu, S, true, L, 1>(old, xr, wv, bv, nw, ob); break;
+            case 2: cfstate_channels<T, W, kSilu, S, true, L, 2>(old, xr, wv, bv, nw, ob); break;
+            case 3: cfstate_channels<T, W, kSilu, S, true, L, 3>(old, xr, wv, bv, nw, ob); break;
+            case 4: cfstate_channels<T, W, kSilu, S, true, L, 4>(old, xr, wv, bv, nw, ob); break;
+            case 5: cfstate_channels<T, W, kSilu, S, true, L, 5>(old, xr, wv, bv, nw, ob); break;
+            case 6: cfstate_channels<T, W, kSilu, S, true, L, 6>(old, xr, wv, bv, nw, ob); break;
+            default: cfstate_channels<T, W, kSilu, S, true, L, 7>(old, xr, wv, bv, nw, ob); break;
         }
-        #pragma unroll
-        for (int i = 0; i < L; ++i) {
-            float acc = bv[c];
-            #pragma unroll
-            for (int k = 0; k < W; ++k) acc = fmaf(wv[k][c], Bits<T>::to_f(seq[i + k]), acc);
-            const float o = !kSilu ? acc : (kTanh ? silu_half_arg(acc) : silu_f(acc));
-            Bits<T>::put(ob, c * L + i, bits_from_f<T>(o));
-        }
+    } else {
+        cfstate_channels<T, W, kSilu, S, false, L, 0>(old, xr, wv, bv, nw, ob);
     }
     #pragma unroll
     for (int i = 0; i < L; ++i) st_stream(op + i, make_uint4(ob[4 * i], ob[4 * i + 1], ob[4 * i + 2], ob[4 * i + 3]));

@@ -336,46 +336,51 @@ struct FwdClArgs {
 #ifndef CC1D_FWD_CL_TMA
 #define CC1D_FWD_CL_TMA 1
 #endif
+#ifndef CC1D_FWD_TMA_MINBLK
+#define CC1D_FWD_TMA_MINBLK 4        // 128 registers: 4 CTAs (16 warps) per SM
+#endif
 constexpr int kClRows = 8;    // token chunks per CTA (threadIdx.y)
 constexpr int kClUnroll = 4;  // tokens per block: loads of one block are in flight while the previous computes
 
 // One token of the sliding window: out = act(bias + sum_k w[k] * window[k]), then shift.
+// Arithmetic on fp32 pairs of adjacent channels (FFMA2: two multiply-adds per issue slot; the
+// pairs are what unpacking a 16-bit x 2 word yields, so no register moves are needed to form them).
 template <typename T, int W, int C, bool kSilu, bool kSeqIdx, bool kTanh>
-__device__ __forceinline__ void fwd_cl_token_impl(const Raw<T, C> &raw, int sid, float (&win)[W - 1][C], int (&sw)[W - 1],
-                                                  const float (&wv)[W][C], const float (&bv)[C], char *optr, bool store) {
-    float cur[C], o[C];
-    unpack_raw<T>(raw, cur);
+__device__ __forceinline__ void fwd_cl_token_impl(const Raw<T, C> &raw, int sid, float2 (&win)[W - 1][C / 2], int (&sw)[W - 1],
+                                                  const float2 (&wv)[W][C / 2], const float2 (&bv)[C / 2], char *optr, bool store) {
+    constexpr int P = C / 2;
+    float2 cur[P], o[P];
+    unpack_pairs<T>(raw, cur);
     #pragma unroll
-    for (int c = 0; c < C; ++c) {
-        float acc = bv[c];
+    for (int c = 0; c < P; ++c) {
+        float2 acc = bv[c];
         #pragma unroll
         for (int k = 0; k < W - 1; ++k) {
-            if (!kSeqIdx || sw[k] == sid) acc = fmaf(wv[k][c], win[k][c], acc);
+            if (!kSeqIdx || sw[k] == sid) acc = fma2(wv[k][c], win[k][c], acc);
         }
-        acc = fmaf(wv[W - 1][c], cur[c], acc);
-        if (kSilu) acc = kTanh ? silu_half_arg(acc) : silu_f(acc);
+        acc = fma2(wv[W - 1][c], cur[c], acc);
+        if (kSilu) {
+            if (kTanh) acc = fma2(acc, make_float2(tanh_approx(acc.x), tanh_approx(acc.y)), acc);   // silu(2h) = h + h tanh(h)
+            else acc = make_float2(silu_f(acc.x), silu_f(acc.y));
+        }
         // a padded token (seq_idx < 0) outputs exactly zero: no bias, no activation
-        o[c] = (kSeqIdx && sid < 0) ? 0.f : acc;
+        o[c] = (kSeqIdx && sid < 0) ? make_float2(0.f, 0.f) : acc;
     }
-    if (store) st_stream_raw(optr, PackRaw<T, C>::run(o));
+    if (store) st_stream_raw(optr, PackPairs<T, C>::run(o));
     #pragma unroll
     for (int k = 0; k < W - 2; ++k) {
         #pragma unroll
-        for (int c = 0; c < C; ++c) win[k][c] = win[k + 1][c];
+        for (int c = 0; c < P; ++c) win[k][c] = win[k + 1][c];
         if (kSeqIdx) sw[k] = sw[k + 1];
     }
     #pragma unroll
-    for (int c = 0; c < C; ++c) win[W - 2][c] = cur[c];
+    for (int c = 0; c < P; ++c) win[W - 2][c] = cur[c];
     // unmasked code only ever runs when every id in the window already equals sid (or there are no ids)
     if (kSeqIdx) sw[W - 2] = sid;
 }
-
-// seq_idx depends on (batch, token) only, so it is uniform across a warp.  Sequence
-// boundaries are rare: when the window and the current token all carry one non-negative id,
-// no tap is masked and the unmasked code runs (a warp-uniform branch).
 template <typename T, int W, int C, bool kSilu, bool kSeqIdx, bool kTanh>
-__device__ __forceinline__ void fwd_cl_token(const Raw<T, C> &raw, int sid, float (&win)[W - 1][C], int (&sw)[W - 1],
-                                             const float (&wv)[W][C], const float (&bv)[C], char *optr, bool store = true) {
+__device__ __forceinline__ void fwd_cl_token(const Raw<T, C> &raw, int sid, float2 (&win)[W - 1][C / 2], int (&sw)[W - 1],
+                                             const float2 (&wv)[W][C / 2], const float2 (&bv)[C / 2], char *optr, bool store = true) {
     if (kSeqIdx) {
         bool same = sid >= 0;
         #pragma unroll
@@ -426,7 +431,7 @@ __global__ void __launch_bounds__(32 * kClRows, 2) fwd_cl_kernel(const FwdClArgs
         }
     }
     // window = the width-1 tokens before t0 (x, or initial_states, or zero)
-    float win[W - 1][C];
+    float2 win[W - 1][C / 2];
     int sw[W - 1];
     #pragma unroll
     for (int k = 0; k < W - 1; ++k) {
@@ -440,10 +445,10 @@ __global__ void __launch_bounds__(32 * kClRows, 2) fwd_cl_kernel(const FwdClArgs
         } else if (a.init != nullptr) {
             ld_cached_raw(r, reinterpret_cast<const T *>(a.init) + b * a.i_bs + (p + (W - 1)) * a.i_ls + (int64_t)col * C);
         }
-        unpack_raw<T>(r, win[k]);
+        unpack_pairs<T>(r, win[k]);
     }
-    float wv[W][C], bv[C];
-    load_taps<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, kTanh ? 0.5f : 1.f);
+    float2 wv[W][C / 2], bv[C / 2];
+    load_taps_pairs<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, kTanh ? 0.5f : 1.f);
 
     // full blocks: the next block's loads are issued before the current block is computed
     for (int blk = 0; blk < nfull; ++blk) {
@@ -477,7 +482,7 @@ __global__ void __launch_bounds__(32 * kClRows, 2) fwd_cl_kernel(const FwdClArgs
     if (a.fin != nullptr && t1 == L) {
         T *fp = reinterpret_cast<T *>(a.fin) + b * a.f_bs + (int64_t)col * C;
         #pragma unroll
-        for (int k = 0; k < W - 1; ++k) st_plain_raw(fp + k * a.f_ls, PackRaw<T, C>::run(win[k]));
+        for (int k = 0; k < W - 1; ++k) st_plain_raw(fp + k * a.f_ls, PackPairs<T, C>::run(win[k]));
     }
 }
 
@@ -499,7 +504,7 @@ constexpr int kTmaStages = CC1D_TMA_STAGES;
 constexpr size_t kFwdTmaSmem = (size_t)kTmaWarps * kTmaStages * kTmaStageBytes + (size_t)kTmaWarps * kTmaStages * 8;
 
 template <typename T, int W, bool kSilu, bool kSeqIdx>
-__global__ void __launch_bounds__(32 * kTmaWarps) fwd_cl_tma_kernel(const FwdClArgs a, const __grid_constant__ CUtensorMap xmap) {
+__global__ void __launch_bounds__(32 * kTmaWarps, CC1D_FWD_TMA_MINBLK) fwd_cl_tma_kernel(const FwdClArgs a, const __grid_constant__ CUtensorMap xmap) {
     pdl_wait();
     constexpr int C = Elem<T>::kVec;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
@@ -542,7 +547,7 @@ __global__ void __launch_bounds__(32 * kTmaWarps) fwd_cl_tma_kernel(const FwdClA
     const int32_t *__restrict__ sp = kSeqIdx ? a.seq_idx + (int64_t)b * L + t0 : nullptr;
 
     // window = the width-1 tokens before t0 (x, or initial_states, or zero)
-    float win[W - 1][C];
+    float2 win[W - 1][C / 2];
     int sw[W - 1];
     #pragma unroll
     for (int k = 0; k < W - 1; ++k) {
@@ -556,17 +561,17 @@ __global__ void __launch_bounds__(32 * kTmaWarps) fwd_cl_tma_kernel(const FwdClA
         } else if (a.init != nullptr && lane_ok) {
             ld_cached_raw(r, reinterpret_cast<const T *>(a.init) + b * a.i_bs + (p + (W - 1)) * a.i_ls + (int64_t)col * C);
         }
-        unpack_raw<T>(r, win[k]);
+        unpack_pairs<T>(r, win[k]);
     }
-    float wv[W][C], bv[C];
+    float2 wv[W][C / 2], bv[C / 2];
     if (lane_ok) {
-        load_taps<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, kTanh ? 0.5f : 1.f);
+        load_taps_pairs<W, C>(wv, bv, a.weight, a.w_cs, a.w_ws, a.bias, a.wtype, (int64_t)col * C, kTanh ? 0.5f : 1.f);
     } else {
         #pragma unroll
-        for (int c = 0; c < C; ++c) {
-            bv[c] = 0.f;
+        for (int c = 0; c < C / 2; ++c) {
+            bv[c] = make_float2(0.f, 0.f);
             #pragma unroll
-            for (int k = 0; k < W; ++k) wv[k][c] = 0.f;
+            for (int k = 0; k < W; ++k) wv[k][c] = make_float2(0.f, 0.f);
         }
     }
 
@@ -635,7 +640,7 @@ __global__ void __launch_bounds__(32 * kTmaWarps) fwd_cl_tma_kernel(const FwdClA
     if (a.fin != nullptr && t1 == L && lane_ok) {
         T *fp = reinterpret_cast<T *>(a.fin) + b * a.f_bs + (int64_t)col * C;
         #pragma unroll
-        for (int k = 0; k < W - 1; ++k) st_plain_raw(fp + k * a.f_ls, PackRaw<T, C>::run(win[k]));
+        for (int k = 0; k < W - 1; ++k) st_plain_raw(fp + k * a.f_ls, PackPairs<T, C>::run(win[k]));
     }
 }
 

@@ -138,10 +138,19 @@ void causal_conv1d_bwd(const at::Tensor &x, const at::Tensor &weight, const OptT
     TORCH_CHECK(dweight.scalar_type() == at::kFloat, "dweight must be float32");
     TORCH_CHECK(x.stride(2) == 1 || x.stride(1) == 1, "x must be contiguous along seqlen or along dim");
     const bool cl = channel_last(x);
-    // bring dout into x's layout class if autograd handed over a different one
+    // dout normally arrives in x's layout class.  When autograd hands over the other one: a channel-first
+    // dout beside a channel-last x is read in place by the 16-bit kernels (no copy) as long as its rows are
+    // 16-byte aligned; every other mixed case is brought into x's layout class by one copy, as in the
+    // reference (csrc/causal_conv1d.cpp:297-298).
     at::Tensor dout_l = dout;
     if (!cl && dout.stride(2) != 1) dout_l = dout.contiguous();
-    if (cl && dout.stride(1) != 1) dout_l = dout.transpose(-1, -2).contiguous().transpose(-1, -2);
+    const auto to_channel_last = [](const at::Tensor &t) { return t.transpose(-1, -2).contiguous().transpose(-1, -2); };
+    bool dout_in_place = false;
+    if (cl && dout.stride(1) != 1 && d.dim > 1) {
+        dout_in_place = d.seqlen > 1 && dout.stride(2) == 1 && x.scalar_type() != at::kFloat && dout.stride(1) % 8 == 0 &&
+                        (d.batch <= 1 || dout.stride(0) % 8 == 0) && reinterpret_cast<uintptr_t>(dout.data_ptr()) % 16 == 0;
+        if (!dout_in_place) dout_l = to_channel_last(dout);
+    }
     if (!cl) TORCH_CHECK(dx.stride(2) == 1 || d.seqlen <= 1, "dx must be contiguous along seqlen");
     if (cl) TORCH_CHECK(dx.stride(1) == 1 || d.dim <= 1, "dx must be contiguous along dim");
 
@@ -220,7 +229,14 @@ void causal_conv1d_bwd(const at::Tensor &x, const at::Tensor &weight, const OptT
         peers.spin_limit = (uint32_t)peer_spin_limit;
         p.peers = &peers;
     }
-    raise_on(cc1d_bwd(&p, at::cuda::getCurrentCUDAStream().stream()), "causal_conv1d_bwd");
+    int rc = cc1d_bwd(&p, at::cuda::getCurrentCUDAStream().stream());
+    if (dout_in_place && (rc == CC1D_ERR_STRIDE || rc == CC1D_ERR_ALIGN)) {
+        // the library could not serve this dout where it lies (e.g. no tensor map for its strides): one copy
+        dout_l = to_channel_last(dout);
+        p.dout = dout_l.data_ptr(); p.dout_batch_stride = dout_l.stride(0); p.dout_c_stride = dout_l.stride(1); p.dout_l_stride = dout_l.stride(2);
+        rc = cc1d_bwd(&p, at::cuda::getCurrentCUDAStream().stream());
+    }
+    raise_on(rc, "causal_conv1d_bwd");
 }
 
 void causal_conv1d_update(const at::Tensor &x, const at::Tensor &conv_state, const at::Tensor &weight,

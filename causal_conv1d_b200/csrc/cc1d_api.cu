@@ -57,32 +57,40 @@ void allow_dynamic_smem(const void *kernel, size_t bytes) {
     else (void)cudaGetLastError();   // the launch that follows reports the failure
 }
 
-bool make_channel_last_tensor_map(CUtensorMap *map, int dtype, const void *base, int64_t dim, int64_t seqlen,
-                                  int64_t batch, int64_t l_stride, int64_t batch_stride, int row_bytes) {
-    using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static EncodeFn encode = nullptr;
+using TensorMapEncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                       const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled, resolved once through the runtime (no link-time dependency on libcuda)
+static TensorMapEncodeFn tensor_map_encoder() {
+    static TensorMapEncodeFn encode = nullptr;
     static bool looked_up = false;
-    {
-        static std::mutex mu;
-        std::lock_guard<std::mutex> lock(mu);
-        if (!looked_up) {
-            looked_up = true;
-            void *fn = nullptr;
-            cudaDriverEntryPointQueryResult qres;
-            if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
-                qres == cudaDriverEntryPointSuccess) {
-                encode = reinterpret_cast<EncodeFn>(fn);
-            } else {
-                (void)cudaGetLastError();
-            }
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!looked_up) {
+        looked_up = true;
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess) {
+            encode = reinterpret_cast<TensorMapEncodeFn>(fn);
+        } else {
+            (void)cudaGetLastError();
         }
     }
+    return encode;
+}
+
+static CUtensorMapDataType tensor_map_dtype(int dtype) {
+    return dtype == CC1D_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+           : dtype == CC1D_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+}
+
+bool make_channel_last_tensor_map(CUtensorMap *map, int dtype, const void *base, int64_t dim, int64_t seqlen,
+                                  int64_t batch, int64_t l_stride, int64_t batch_stride, int row_bytes) {
+    const TensorMapEncodeFn encode = tensor_map_encoder();
     if (encode == nullptr) return false;
     const int es = elem_size(dtype);
-    const CUtensorMapDataType dt = dtype == CC1D_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                   : dtype == CC1D_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     if (batch < 1) batch = 1;
     if (batch == 1 || batch_stride <= 0) batch_stride = l_stride * seqlen;   // unused extent: any legal stride
     const cuuint64_t dims[3] = {(cuuint64_t)dim, (cuuint64_t)seqlen, (cuuint64_t)batch};
@@ -91,8 +99,29 @@ bool make_channel_last_tensor_map(CUtensorMap *map, int dtype, const void *base,
     const cuuint32_t estr[3] = {1, 1, 1};
     if (strides[0] % 16 || strides[1] % 16 || strides[0] >= (1ull << 40) || strides[1] >= (1ull << 40)) return false;
     if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
-    const CUresult rc = encode(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+    const CUresult rc = encode(map, tensor_map_dtype(dtype), 3, const_cast<void *>(base), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
+}
+
+bool make_channel_first_tensor_map(CUtensorMap *map, int dtype, const void *base, int64_t seqlen, int64_t dim,
+                                   int64_t batch, int64_t c_stride, int64_t batch_stride, int box_tokens, int box_channels) {
+    const TensorMapEncodeFn encode = tensor_map_encoder();
+    if (encode == nullptr) return false;
+    const int es = elem_size(dtype);
+    if (batch < 1) batch = 1;
+    if (batch == 1 || batch_stride <= 0) batch_stride = c_stride * dim;      // unused extent: any legal stride
+    if (c_stride <= 0 || batch_stride <= 0) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)seqlen, (cuuint64_t)dim, (cuuint64_t)batch};
+    const cuuint64_t strides[2] = {(cuuint64_t)c_stride * es, (cuuint64_t)batch_stride * es};   // bytes, dims 1..2
+    const cuuint32_t box[3] = {(cuuint32_t)box_tokens, (cuuint32_t)box_channels, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    if ((box_tokens * es) % 16 || box_channels > 256) return false;
+    if (strides[0] % 16 || strides[1] % 16 || strides[0] >= (1ull << 40) || strides[1] >= (1ull << 40)) return false;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
+    const CUresult rc = encode(map, tensor_map_dtype(dtype), 3, const_cast<void *>(base), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return rc == CUDA_SUCCESS;
 }
@@ -226,8 +255,16 @@ static int check_bwd(const cc1d_bwd_params *p, bool *cl) {
     if ((p->bias == nullptr) != (p->dbias == nullptr)) return CC1D_ERR_NULL;
     if (!elem_aligned(p->dout, p->itype) || !elem_aligned(p->dx, p->itype) ||
         !elem_aligned(p->dweight, CC1D_F32) || !elem_aligned(p->dbias, CC1D_F32)) return CC1D_ERR_ALIGN;
-    rc = check_same_layout(*cl, p->dout_batch_stride, p->dout_c_stride, p->dout_l_stride, p->seqlen, p->dim, p->batch);
-    if (rc != CC1D_OK) return rc;
+    // dout normally has x's layout class; beside a channel-last x it may also be channel-first (seqlen
+    // stride 1, 16-bit types, 16-byte aligned rows): the backward then reads it in place
+    const bool dout_cf = *cl && p->seqlen > 1 && p->dim > 1 && p->dout_l_stride == 1 && p->dout_c_stride != 1;
+    if (dout_cf) {
+        if (p->itype == CC1D_F32 || p->dout_c_stride % 8 != 0 || (p->batch > 1 && p->dout_batch_stride % 8 != 0))
+            return CC1D_ERR_STRIDE;
+    } else {
+        rc = check_same_layout(*cl, p->dout_batch_stride, p->dout_c_stride, p->dout_l_stride, p->seqlen, p->dim, p->batch);
+        if (rc != CC1D_OK) return rc;
+    }
     rc = check_same_layout(*cl, p->dx_batch_stride, p->dx_c_stride, p->dx_l_stride, p->seqlen, p->dim, p->batch);
     if (rc != CC1D_OK) return rc;
     if (!*cl && (p->seq_idx || p->initial_states || p->dfinal_states || p->dinitial_states)) return CC1D_ERR_LAYOUT;

@@ -1215,7 +1215,10 @@ template <> __device__ __forceinline__ uint2 lds_raw<uint2>(uint32_t addr) {
     return v;
 }
 
-template <typename T, int W, bool kSilu, bool kSeqIdx>
+// kDoutCf: dout is stored channel-first ((batch, dim, seqlen) with seqlen stride 1) although x and dx are
+// channel-last: its box arrives as [32 * C channels][kTmaRows tokens] (16 bytes per channel), a thread
+// reads the C rows of its channels once per stage and picks token r out of them with byte permutes.
+template <typename T, int W, bool kSilu, bool kSeqIdx, bool kDoutCf>
 __global__ void __launch_bounds__(32 * kBwdClRows, CC1D_BWD_CL_MINBLK)
 bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap dmap) {
     pdl_wait();
@@ -1264,7 +1267,8 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
                 if (s < nst) {
                     mbar_expect_tx(bars + 8 * s, kStageBytes);
                     tma_load_3d(ring + s * kStageBytes, &xmap, c0, t0 + s * kTmaRows, (int)b, bars + 8 * s);
-                    tma_load_3d(ring + s * kStageBytes + kBoxBytes, &dmap, c0, t0 + s * kTmaRows, (int)b, bars + 8 * s);
+                    if (kDoutCf) tma_load_3d(ring + s * kStageBytes + kBoxBytes, &dmap, t0 + s * kTmaRows, c0, (int)b, bars + 8 * s);
+                    else tma_load_3d(ring + s * kStageBytes + kBoxBytes, &dmap, c0, t0 + s * kTmaRows, (int)b, bars + 8 * s);
                 }
             }
         }
@@ -1329,6 +1333,28 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
             }
             const uint32_t xsrc = ring + s * kStageBytes + tx * (C * (int)sizeof(T));
             const uint32_t dsrc = xsrc + kBoxBytes;
+            // channel-first dout: the thread's C channel rows of this stage, kTmaRows tokens each
+            uint4 dch[C];
+            if (kDoutCf) {
+                #pragma unroll
+                for (int j = 0; j < C; ++j) dch[j] = lds128(ring + s * kStageBytes + kBoxBytes + (tx * C + j) * 16);
+            }
+            auto dout_row = [&](int r) -> R {
+                if constexpr (kDoutCf) {
+                    static_assert(!kDoutCf || (sizeof(T) == 2 && C == 4), "channel-first dout: 16-bit types, 4 channels per thread");
+                    const uint32_t w0 = (r >> 1) == 0 ? dch[0].x : (r >> 1) == 1 ? dch[0].y : (r >> 1) == 2 ? dch[0].z : dch[0].w;
+                    const uint32_t w1 = (r >> 1) == 0 ? dch[1].x : (r >> 1) == 1 ? dch[1].y : (r >> 1) == 2 ? dch[1].z : dch[1].w;
+                    const uint32_t w2 = (r >> 1) == 0 ? dch[2].x : (r >> 1) == 1 ? dch[2].y : (r >> 1) == 2 ? dch[2].z : dch[2].w;
+                    const uint32_t w3 = (r >> 1) == 0 ? dch[3].x : (r >> 1) == 1 ? dch[3].y : (r >> 1) == 2 ? dch[3].z : dch[3].w;
+                    const uint32_t sel = (r & 1) ? 0x7632u : 0x5410u;
+                    R v;
+                    v.x = __byte_perm(w0, w1, sel);
+                    v.y = __byte_perm(w2, w3, sel);
+                    return v;
+                } else {
+                    return lds_raw<R>(dsrc + r * kRowBytes);
+                }
+            };
             const bool steady = base >= W - 1 && base + kTmaRows <= n_in &&
                                 (a.dfin == nullptr || t0 + base + kTmaRows <= L - (W - 1));
             // one test per stage instead of one per position: when the window and all positions of
@@ -1349,14 +1375,14 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
             if (plain) {
                 #pragma unroll
                 for (int r = 0; r < kTmaRows; ++r) {
-                    const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = lds_raw<R>(dsrc + r * kRowBytes);
+                    const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = dout_row(r);
                     bwd_cl_position_impl<T, W, C, kSilu, false, kTanh>(
                         xr, dr, 0, true, lane_ok, false, xwin, gwin, swin, wv, wy, bv, dw, nullptr, 0, optr + r * os, nullptr);
                 }
             } else if (steady) {
                 #pragma unroll
                 for (int r = 0; r < kTmaRows; ++r) {
-                    const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = lds_raw<R>(dsrc + r * kRowBytes);
+                    const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = dout_row(r);
                     bwd_cl_position_impl<T, W, C, kSilu, kSeqIdx, kTanh>(
                         xr, dr, sid[r], true, lane_ok, false, xwin, gwin, swin, wv, wy, bv, dw, nullptr, 0, optr + r * os, nullptr);
                 }
@@ -1365,7 +1391,7 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
                 for (int r = 0; r < kTmaRows; ++r) {
                     const int i = base + r;               // position t0 + i
                     if (i < n_ext) {
-                        const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = lds_raw<R>(dsrc + r * kRowBytes);
+                        const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = dout_row(r);
                         const int q = t0 + i - (W - 1);   // dx position produced now
                         const bool st_dx = i >= W - 1 && lane_ok;
                         const bool st_di = q < 0 && want_dinit;
@@ -1383,7 +1409,8 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
                 fence_proxy_async_smem();
                 mbar_expect_tx(bars + 8 * s, kStageBytes);
                 tma_load_3d(ring + s * kStageBytes, &xmap, c0, t0 + (st + kBwdTmaStages) * kTmaRows, (int)b, bars + 8 * s);
-                tma_load_3d(ring + s * kStageBytes + kBoxBytes, &dmap, c0, t0 + (st + kBwdTmaStages) * kTmaRows, (int)b, bars + 8 * s);
+                if (kDoutCf) tma_load_3d(ring + s * kStageBytes + kBoxBytes, &dmap, t0 + (st + kBwdTmaStages) * kTmaRows, c0, (int)b, bars + 8 * s);
+                else tma_load_3d(ring + s * kStageBytes + kBoxBytes, &dmap, c0, t0 + (st + kBwdTmaStages) * kTmaRows, (int)b, bars + 8 * s);
             }
         }
     }
@@ -1453,6 +1480,9 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
     if (p.dinitial_states && (!is_aligned16(p.dinitial_states) || p.dinitial_states_batch_stride % C ||
                               p.dinitial_states_l_stride % C)) return CC1D_ERR_ALIGN;
     const ClPlan pl = plan_channel_last(p);
+    // dout stored channel-first beside a channel-last x (what autograd hands over when the consumer of
+    // `out` made it contiguous): read in place through a second kind of tensor map, no re-layout copy
+    const bool dout_cf = p.seqlen > 1 && p.dim > 1 && p.dout_l_stride == 1 && p.dout_c_stride != 1;
     const uint64_t ctas = (uint64_t)pl.ncolblk * pl.ngroups * (uint64_t)p.batch;
     if (ctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
     if (bwd_workspace_bytes_channel_last(p) > p.workspace_bytes) return CC1D_ERR_WORKSPACE;
@@ -1477,16 +1507,32 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
         // 16-bit I/O only: fp32 stages would leave room for a single CTA per SM
         if (p.itype != CC1D_F32 && p.seqlen < (1ll << 31) - 16 && p.batch < (1ll << 31) &&
             make_channel_last_tensor_map(&xmap, p.itype, p.x, p.dim, p.seqlen, p.batch, p.x_l_stride, p.x_batch_stride, row_bytes) &&
-            make_channel_last_tensor_map(&dmap, p.itype, p.dout, p.dim, p.seqlen, p.batch, p.dout_l_stride, p.dout_batch_stride, row_bytes)) {
-            CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
-                CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
-                    auto kernel = bwd_cl_tma_kernel<T, W, kSilu, kSeqIdx>;
-                    allow_dynamic_smem(reinterpret_cast<const void *>(kernel), BwdTma<T>::kSmem);
-                    launch_k(kernel, dim3((unsigned)ctas), dim3(32 * kBwdClRows), BwdTma<T>::kSmem, stream, a, xmap, dmap);
-                }););););
+            (dout_cf ? make_channel_first_tensor_map(&dmap, p.itype, p.dout, p.seqlen, p.dim, p.batch, p.dout_c_stride,
+                                                     p.dout_batch_stride, kTmaRows, 32 * kBwdClC)
+                     : make_channel_last_tensor_map(&dmap, p.itype, p.dout, p.dim, p.seqlen, p.batch, p.dout_l_stride,
+                                                    p.dout_batch_stride, row_bytes))) {
+            if (p.itype == CC1D_BF16) {
+                using T = __nv_bfloat16;
+                CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx,
+                    CC1D_DISPATCH_BOOL(dout_cf, kDoutCf, {
+                        auto kernel = bwd_cl_tma_kernel<T, W, kSilu, kSeqIdx, kDoutCf>;
+                        allow_dynamic_smem(reinterpret_cast<const void *>(kernel), BwdTma<T>::kSmem);
+                        launch_k(kernel, dim3((unsigned)ctas), dim3(32 * kBwdClRows), BwdTma<T>::kSmem, stream, a, xmap, dmap);
+                    }););););
+            } else {
+                using T = __half;
+                CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx,
+                    CC1D_DISPATCH_BOOL(dout_cf, kDoutCf, {
+                        auto kernel = bwd_cl_tma_kernel<T, W, kSilu, kSeqIdx, kDoutCf>;
+                        allow_dynamic_smem(reinterpret_cast<const void *>(kernel), BwdTma<T>::kSmem);
+                        launch_k(kernel, dim3((unsigned)ctas), dim3(32 * kBwdClRows), BwdTma<T>::kSmem, stream, a, xmap, dmap);
+                    }););););
+            }
             launched = true;
         }
 #endif
+        // a channel-first dout is only served by the TMA kernel (16-bit types, a tensor map the driver accepts)
+        if (!launched && dout_cf) return CC1D_ERR_STRIDE;
         if (!launched) {
             CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
                 CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {

@@ -83,4 +83,10 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 bool make_channel_last_tensor_map(CUtensorMap *map, int dtype, const void *base, int64_t dim, int64_t seqlen,
                                   int64_t batch, int64_t l_stride, int64_t batch_stride, int row_bytes = kTmaRowBytes);
 
+// Host: tensor map over a channel-first tensor (seqlen, dim, batch) with element strides
+// (1, c_stride, batch_stride) and a box of [box_tokens tokens, box_channels channels, 1]: the box
+// lands in shared memory channel by channel, box_tokens elements each.
+bool make_channel_first_tensor_map(CUtensorMap *map, int dtype, const void *base, int64_t seqlen, int64_t dim,
+                                   int64_t batch, int64_t c_stride, int64_t batch_stride, int box_tokens, int box_channels);
+
 }  // namespace cc1d

@@ -134,7 +134,11 @@ typedef struct cc1d_bwd_params {
     const void *weight;
     int64_t weight_c_stride, weight_width_stride;
     const void *bias;         /* may be NULL                                    */
-    const void *dout;         /* same layout class as x                         */
+    const void *dout;         /* same layout class as x; beside a channel-last x it
+                                 may also be channel-first (l stride 1, 16-bit types,
+                                 c / batch strides % 8 == 0, 16-byte aligned): read in
+                                 place, no re-layout copy (the reference copies,
+                                 csrc/causal_conv1d.cpp:297-298)                 */
     int64_t dout_batch_stride, dout_c_stride, dout_l_stride;
     void *dx;                 /* same layout class as x                         */
     int64_t dx_batch_stride, dx_c_stride, dx_l_stride;

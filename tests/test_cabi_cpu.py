@@ -116,6 +116,9 @@ def test_bwd_rejects_seq_idx_with_states_phase_and_long_sequences(lib):
         rc = lib.cc1d_bwd(ctypes.byref(block(seq_idx=FAKE, **kw)), None)
         assert rc == 18 and b"seq_idx cannot be combined" in lib.cc1d_status_str(rc)
     assert lib.cc1d_bwd(ctypes.byref(block(phase=3)), None) == 19
+    # a channel-first dout beside a channel-last x: 16-bit types with 16-byte aligned rows only
+    assert lib.cc1d_bwd(ctypes.byref(block(dout_c_stride=128, dout_l_stride=1)), None) == 5          # fp32
+    assert lib.cc1d_bwd(ctypes.byref(block(itype=cabi.BF16, dout_c_stride=130, dout_l_stride=1)), None) == 5
     assert lib.cc1d_bwd(ctypes.byref(block(seqlen=(1 << 31) - 8)), None) == 13       # fp32: the non-TMA kernel
     p = _prefill(total_tokens=(1 << 31) - 8)
     assert lib.cc1d_prefill_varlen(ctypes.byref(p), None) == 13

@@ -534,3 +534,48 @@ def test_strided_slices_in_and_out(channel_last):
     assert dx.data_ptr() == sl(dproj).data_ptr() and torch.equal(dx, dx2) and torch.equal(dw, dw2) and torch.equal(db, db2)
     ref = oracle.fwd(x, w, b, activation="silu")
     assert_close(out, ref.to(it), TOL[it], "out")
+
+
+@pytest.mark.parametrize("itype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("mode", ["plain", "seq_idx", "states"])
+@pytest.mark.parametrize("batch,dim,seqlen", [(2, 264, 1000), (1, 128, 64), (3, 40, 333), (2, 512, 4096)])
+def test_channel_first_dout_beside_channel_last_x(batch, dim, seqlen, mode, itype):
+    """Autograd may hand the backward a channel-first dout although x (and so out) is channel-last.
+    The 16-bit kernels read such a dout where it lies (rows 16-byte aligned: seqlen % 8 == 0), every
+    other case goes through one re-layout copy; either way the results are those of a channel-last
+    dout with the same values, bit for bit."""
+    torch.manual_seed(11)
+    width = 4
+    x = torch.randn(batch, seqlen, dim, device=DEV, dtype=itype).transpose(1, 2)
+    w = torch.randn(dim, width, device=DEV)
+    b = torch.randn(dim, device=DEV)
+    dout_cf = torch.randn(batch, dim, seqlen, device=DEV, dtype=itype)                  # channel-first values
+    dout_cl = dout_cf.transpose(1, 2).contiguous().transpose(1, 2)                       # same values, channel-last
+    assert dout_cf.stride(2) == 1 and dout_cl.stride(1) == 1
+    sidx = ini = dfin = None
+    if mode == "seq_idx":
+        cut = seqlen // 3
+        sidx = torch.cat([torch.zeros(cut), torch.ones(seqlen - cut)]).int().repeat(batch, 1).to(DEV)
+    if mode == "states":
+        ini = torch.randn(batch, width - 1, dim, device=DEV, dtype=itype).transpose(1, 2)
+        dfin = torch.randn(batch, width - 1, dim, device=DEV, dtype=itype).transpose(1, 2)
+
+    def run(dout):
+        from causal_conv1d_b200.cpp_functions import causal_conv1d_bwd_function
+        return causal_conv1d_bwd_function(x, w, b, dout, sidx, ini, dfin, None, ini is not None, True)
+
+    want = run(dout_cl)
+    got = run(dout_cf)
+    for a_, b_, name in zip(got, want, ("dx", "dweight", "dbias", "dinitial_states")):
+        if b_ is None:
+            assert a_ is None
+        else:
+            assert torch.equal(a_, b_), name
+    assert got[0].stride(1) == 1, "dx keeps x's layout"
+    # and through autograd: a consumer that made `out` contiguous hands back a channel-first gradient
+    xr = x.detach().requires_grad_()
+    out = _api().causal_conv1d_fn(xr, w, b, seq_idx=sidx, activation="silu")
+    out.contiguous().backward(dout_cf)
+    xr2 = x.detach().requires_grad_()
+    _api().causal_conv1d_fn(xr2, w, b, seq_idx=sidx, activation="silu").backward(dout_cl)
+    assert torch.equal(xr.grad, xr2.grad)

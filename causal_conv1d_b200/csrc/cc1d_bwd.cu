@@ -6,7 +6,7 @@
 // first) or fixed-order shared-memory sum over the CTA's token chunks (channel-last) -> one
 // partial row per warp unit / CTA in the caller's workspace -> reduce_partials_kernel sums
 // the rows in index order.  No float atomics anywhere, so repeated runs are bitwise equal.
-// Channel-first rows of 16-bit elements made of whole groups on 32-byte aligned rows take
+// Channel-first rows of 16-bit elements, a multiple of 16 long, on 32-byte aligned rows take
 // bwd_cf_wide_kernel (32 bytes per lane, two of the four halos of a vector pair inside the lane).
 //
 // Replaces csrc/causal_conv1d_bwd.cu:53-259 (channel-first), :329-589 (channel-last) and
@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(256, CC1D_BWD_CF_MINBLK) bwd_cf_vec_kernel(con
     }
 }
 
-// ---- 16-bit I/O, rows made of whole groups, 32-byte aligned: 32 bytes per lane ----------------
+// ---- 16-bit I/O, rows of a multiple of 16 elements, 32-byte aligned: 32 bytes per lane --------
 // A lane owns SLOTS of 16 consecutive elements (two 16-byte vectors A, B moved by one 256-bit
 // load / store); a warp instruction covers 1 KB of the row.  The fp32 pairs hold (A[i], B[i]),
 // so of the four halos a pair of vectors has, two stay inside the lane: B's left x halo is
@@ -508,15 +508,21 @@ template <int kSlots> struct WideGroup {
     uint32_t cz, cw;          // lane 31: the 4 elements of x before the group (zeros at the row start)
 };
 
-template <typename T, int kSlots>
+// kWhole: every slot of the row is complete; otherwise seqlen is only a multiple of 16, a lane's 16
+// elements are either all inside the row or all past its end (then they read as zeros: g = 0 there).
+template <typename T, int kSlots, bool kWhole>
 __device__ __forceinline__ void wide_load(WideGroup<kSlots> &r, const T *__restrict__ xr, const T *__restrict__ dr,
-                                          uint32_t g, int lane) {
+                                          uint32_t g, int lane, uint32_t L) {
     const uint32_t gs = g * (kSlots * kWideSlotElems);
     #pragma unroll
     for (int j = 0; j < kSlots; ++j) {
         const uint32_t e = gs + j * kWideSlotElems + lane * 16;
-        ld_stream32(r.xa[j], r.xb[j], xr + e);
-        ld_stream32(r.da[j], r.db[j], dr + e);
+        if (kWhole || e < L) {
+            ld_stream32(r.xa[j], r.xb[j], xr + e);
+            ld_stream32(r.da[j], r.db[j], dr + e);
+        } else {
+            r.xa[j] = r.xb[j] = r.da[j] = r.db[j] = make_uint4(0, 0, 0, 0);
+        }
     }
     r.cz = 0; r.cw = 0;
     if (lane == 31 && g > 0) {
@@ -525,10 +531,10 @@ __device__ __forceinline__ void wide_load(WideGroup<kSlots> &r, const T *__restr
     }
 }
 
-template <typename T, int W, bool kSilu, int kSlots>
+template <typename T, int W, bool kSilu, int kSlots, bool kWhole>
 __device__ __forceinline__ void wide_group(const WideGroup<kSlots> &r, const float (&wv)[W], const float (&wy)[W], float by,
                                            float (&gfirst)[W - 1], float2 (&dw2)[W], float2 &db2, T *__restrict__ dxr,
-                                           uint32_t g, int lane) {
+                                           uint32_t g, int lane, uint32_t L) {
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
     const int src_prev = (lane + 31) & 31, src_next = (lane + 1) & 31;
     const uint32_t gs = g * (kSlots * kWideSlotElems);
@@ -578,11 +584,12 @@ __device__ __forceinline__ void wide_group(const WideGroup<kSlots> &r, const flo
             for (int k = 0; k < W; ++k) acc = fma2(splat2(wv[k]), gx[i + (W - 1 - k)], acc);
             o0[i] = acc.x; o1[i] = acc.y;
         }
-        st_stream32(dxr + gs + j * kWideSlotElems + lane * 16, pack<T>(o0), pack<T>(o1));
+        const uint32_t e = gs + j * kWideSlotElems + lane * 16;
+        if (kWhole || e < L) st_stream32(dxr + e, pack<T>(o0), pack<T>(o1));
     }
 }
 
-template <typename T, int W, bool kSilu, int kSlots, bool kPrefetch>
+template <typename T, int W, bool kSilu, int kSlots, bool kPrefetch, bool kWhole>
 __global__ void __launch_bounds__(CC1D_BWD_WIDE_THREADS, CC1D_BWD_WIDE_MINBLK) bwd_cf_wide_kernel(const BwdCfArgs a) {
     pdl_wait();
     static_assert(sizeof(T) == 2, "16-bit I/O only");
@@ -608,7 +615,7 @@ __global__ void __launch_bounds__(CC1D_BWD_WIDE_THREADS, CC1D_BWD_WIDE_MINBLK) b
         constexpr int kStep = kPrefetch ? 1 : (CC1D_BWD_WIDE_STEP < kSlots ? CC1D_BWD_WIDE_STEP : kSlots);   // slots per load/compute step
         const uint32_t s0 = g0 * (kSlots / kStep), s1 = g1 * (kSlots / kStep);
         WideGroup<kStep> cur;
-        wide_load<T, kStep>(cur, xr, dr, s1 - 1, lane);
+        wide_load<T, kStep, kWhole>(cur, xr, dr, s1 - 1, lane, a.seqlen);
 
         float wv[W], wy[W];
         constexpr float pre = ActGrad<kTanh>::kPre, post = 1.f / ActGrad<kTanh>::kGScale;
@@ -639,20 +646,20 @@ __global__ void __launch_bounds__(CC1D_BWD_WIDE_THREADS, CC1D_BWD_WIDE_MINBLK) b
             WideGroup<kStep> nxt;
             uint32_t s = s1 - 1;
             while (true) {
-                if (s > s0) wide_load<T, kStep>(nxt, xr, dr, s - 1, lane);
-                wide_group<T, W, kSilu, kStep>(cur, wv, wy, by, gfirst, dw2, db2, dxr, s, lane);
+                if (s > s0) wide_load<T, kStep, kWhole>(nxt, xr, dr, s - 1, lane, a.seqlen);
+                wide_group<T, W, kSilu, kStep, kWhole>(cur, wv, wy, by, gfirst, dw2, db2, dxr, s, lane, a.seqlen);
                 if (s == s0) break;
                 --s;
-                if (s > s0) wide_load<T, kStep>(cur, xr, dr, s - 1, lane);
-                wide_group<T, W, kSilu, kStep>(nxt, wv, wy, by, gfirst, dw2, db2, dxr, s, lane);
+                if (s > s0) wide_load<T, kStep, kWhole>(cur, xr, dr, s - 1, lane, a.seqlen);
+                wide_group<T, W, kSilu, kStep, kWhole>(nxt, wv, wy, by, gfirst, dw2, db2, dxr, s, lane, a.seqlen);
                 if (s == s0) break;
                 --s;
             }
         } else {
             for (uint32_t s = s1 - 1;; --s) {
-                wide_group<T, W, kSilu, kStep>(cur, wv, wy, by, gfirst, dw2, db2, dxr, s, lane);
+                wide_group<T, W, kSilu, kStep, kWhole>(cur, wv, wy, by, gfirst, dw2, db2, dxr, s, lane, a.seqlen);
                 if (s == s0) break;
-                wide_load<T, kStep>(cur, xr, dr, s - 1, lane);
+                wide_load<T, kStep, kWhole>(cur, xr, dr, s - 1, lane, a.seqlen);
             }
         }
 
@@ -813,28 +820,28 @@ int launch_bwd_channel_first(const cc1d_bwd_params &p, cudaStream_t stream) {
         if (pl.vec) {
             const uint64_t ctas = (pl.n_units + 7) / 8;
             const bool full = p.seqlen % vec_elems(p.itype) == 0 && pl.vpr % kCfGroupVecs == 0;
-            // 16-bit rows of whole groups whose starts are 32-byte aligned: 32 bytes per lane
-            const bool wide = CC1D_BWD_WIDE && kCfVecs % 2 == 0 && full && p.itype != CC1D_F32 &&
+            // 16-bit rows whose length is a multiple of 16 elements and whose starts are 32-byte aligned: 32
+            // bytes per lane (a lane's 16 elements are then never cut by the row end)
+            const bool wide = CC1D_BWD_WIDE && kCfVecs % 2 == 0 && p.itype != CC1D_F32 && p.seqlen % 16 == 0 &&
                               ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.dout) |
                                 reinterpret_cast<uintptr_t>(p.dx)) & 31u) == 0 &&
                               (a.x_bs | a.x_cs | a.d_bs | a.d_cs | a.o_bs | a.o_cs) % 16 == 0;
             if (wide) {
+                const uint64_t wctas = (pl.n_units + CC1D_BWD_WIDE_THREADS / 32 - 1) / (CC1D_BWD_WIDE_THREADS / 32);
                 if (p.itype == CC1D_BF16) {
                     using T = __nv_bfloat16;
-                    CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
-                        auto kernel = bwd_cf_wide_kernel<T, W, kSilu, kWideSlots, CC1D_BWD_WIDE_PREFETCH != 0>;
-                        const uint64_t wctas = (pl.n_units + CC1D_BWD_WIDE_THREADS / 32 - 1) / (CC1D_BWD_WIDE_THREADS / 32);
+                    CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, CC1D_DISPATCH_BOOL(full, kWhole, {
+                        auto kernel = bwd_cf_wide_kernel<T, W, kSilu, kWideSlots, CC1D_BWD_WIDE_PREFETCH != 0, kWhole>;
                         launch_k(kernel, dim3(persistent_grid(kernel, CC1D_BWD_WIDE_THREADS, wctas, CC1D_BWD_WIDE_PERSISTENT != 0)),
                                  dim3(CC1D_BWD_WIDE_THREADS), 0, stream, a);
-                    }););
+                    });););
                 } else {
                     using T = __half;
-                    CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
-                        auto kernel = bwd_cf_wide_kernel<T, W, kSilu, kWideSlots, CC1D_BWD_WIDE_PREFETCH != 0>;
-                        const uint64_t wctas = (pl.n_units + CC1D_BWD_WIDE_THREADS / 32 - 1) / (CC1D_BWD_WIDE_THREADS / 32);
+                    CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, CC1D_DISPATCH_BOOL(full, kWhole, {
+                        auto kernel = bwd_cf_wide_kernel<T, W, kSilu, kWideSlots, CC1D_BWD_WIDE_PREFETCH != 0, kWhole>;
                         launch_k(kernel, dim3(persistent_grid(kernel, CC1D_BWD_WIDE_THREADS, wctas, CC1D_BWD_WIDE_PERSISTENT != 0)),
                                  dim3(CC1D_BWD_WIDE_THREADS), 0, stream, a);
-                    }););
+                    });););
                 }
             } else
             CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,

@@ -4,9 +4,9 @@
 // consecutive 16-byte vectors of one row.  A lane owns vector (j * 32 + lane); the
 // (width-1)-element halo comes from the neighbouring lane by warp shuffle, only lane 0 of a
 // unit's first vector re-reads one vector from global.  No shared memory, no barrier, every
-// x byte is requested from DRAM once.  16-bit rows made of whole groups on 32-byte aligned
-// rows take fwd_cf_wide_kernel: 32 bytes per lane (256-bit loads and stores), arithmetic on
-// fp32 pairs, half of the halos inside the lane.
+// x byte is requested from DRAM once.  16-bit rows of a multiple of 16 elements on 32-byte
+// aligned rows take fwd_cf_wide_kernel: 32 bytes per lane (256-bit loads and stores),
+// arithmetic on fp32 pairs, half of the halos inside the lane.
 //
 // Channel-last (x[b, :, t] contiguous): a thread owns one 16-byte vector of channels and
 // slides down `tpt` consecutive tokens keeping the last width-1 vectors in registers; a
@@ -139,7 +139,9 @@ __device__ __forceinline__ void fwd_st32(void *p, const uint4 &a, const uint4 &b
                  :: "l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
 }
 
-template <typename T, int W, bool kSilu, int kSlots>
+// kWhole: every slot of the row is complete; otherwise seqlen is only a multiple of 16 and a lane's 16
+// elements are either all inside the row or all past its end (nothing loaded, nothing stored).
+template <typename T, int W, bool kSilu, int kSlots, bool kWhole>
 __global__ void __launch_bounds__(CC1D_FWD_WIDE_THREADS, CC1D_FWD_WIDE_MINBLK) fwd_cf_wide_kernel(const FwdCfArgs a) {
     pdl_wait();
     static_assert(sizeof(T) == 2, "16-bit I/O only");
@@ -160,9 +162,14 @@ __global__ void __launch_bounds__(CC1D_FWD_WIDE_THREADS, CC1D_FWD_WIDE_MINBLK) f
         const uint32_t g0 = seg * a.gpu;
         const uint32_t g1 = g0 + a.gpu < a.gpr ? g0 + a.gpu : a.gpr;
 
+        const uint32_t L = a.seqlen;
         uint4 xa[kSlots], xb[kSlots];
         #pragma unroll
-        for (int j = 0; j < kSlots; ++j) fwd_ld32(xa[j], xb[j], xr + g0 * kGroupElems + j * kSlotElems + lane * 16);
+        for (int j = 0; j < kSlots; ++j) {
+            const uint32_t e = g0 * kGroupElems + j * kSlotElems + lane * 16;
+            xa[j] = xb[j] = make_uint4(0, 0, 0, 0);
+            if (kWhole || e < L) fwd_ld32(xa[j], xb[j], xr + e);
+        }
         // lane 31: the 4 elements of x before the group (zeros at the row start)
         uint32_t cz = 0, cw = 0;
         if (lane == 31 && g0 > 0) {
@@ -206,13 +213,18 @@ __global__ void __launch_bounds__(CC1D_FWD_WIDE_THREADS, CC1D_FWD_WIDE_MINBLK) f
                     }
                     o0[i] = y.x; o1[i] = y.y;
                 }
-                fwd_st32(outr + g * kGroupElems + j * kSlotElems + lane * 16, pack<T>(o0), pack<T>(o1));
+                const uint32_t e = g * kGroupElems + j * kSlotElems + lane * 16;
+                if (kWhole || e < L) fwd_st32(outr + e, pack<T>(o0), pack<T>(o1));
             }
             if (g + 1 < g1) {
                 // lane 31 keeps the tail of the group for lane 0 of the next one, then the next group's vectors
                 cz = xb[kSlots - 1].z; cw = xb[kSlots - 1].w;
                 #pragma unroll
-                for (int j = 0; j < kSlots; ++j) fwd_ld32(xa[j], xb[j], xr + (g + 1) * kGroupElems + j * kSlotElems + lane * 16);
+                for (int j = 0; j < kSlots; ++j) {
+                    const uint32_t e = (g + 1) * kGroupElems + j * kSlotElems + lane * 16;
+                    xa[j] = xb[j] = make_uint4(0, 0, 0, 0);
+                    if (kWhole || e < L) fwd_ld32(xa[j], xb[j], xr + e);
+                }
             }
         }
     }
@@ -277,21 +289,21 @@ int launch_fwd_channel_first(const cc1d_fwd_params &p, cudaStream_t stream) {
         a.n_units = (uint32_t)n_units;
         const uint64_t ctas = (n_units + 7) / 8;
         const bool full = p.seqlen % V == 0 && vpr % (32 * kVecs) == 0;
-        const bool wide = CC1D_FWD_WIDE && kCfVecs % 2 == 0 && full && p.itype != CC1D_F32 &&
+        const bool wide = CC1D_FWD_WIDE && kCfVecs % 2 == 0 && p.itype != CC1D_F32 && p.seqlen % 16 == 0 &&
                           ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.out)) & 31u) == 0 &&
                           (a.x_bs | a.x_cs | a.o_bs | a.o_cs) % 16 == 0;
         if (wide) {
             const uint64_t wctas = (n_units + CC1D_FWD_WIDE_THREADS / 32 - 1) / (CC1D_FWD_WIDE_THREADS / 32);
             if (p.itype == CC1D_BF16) {
                 using T = __nv_bfloat16;
-                CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
-                    launch_k(fwd_cf_wide_kernel<T, W, kSilu, kCfVecs / 2>, dim3((unsigned)wctas), dim3(CC1D_FWD_WIDE_THREADS), 0, stream, a);
-                }););
+                CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, CC1D_DISPATCH_BOOL(full, kWhole, {
+                    launch_k(fwd_cf_wide_kernel<T, W, kSilu, kCfVecs / 2, kWhole>, dim3((unsigned)wctas), dim3(CC1D_FWD_WIDE_THREADS), 0, stream, a);
+                });););
             } else {
                 using T = __half;
-                CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, {
-                    launch_k(fwd_cf_wide_kernel<T, W, kSilu, kCfVecs / 2>, dim3((unsigned)wctas), dim3(CC1D_FWD_WIDE_THREADS), 0, stream, a);
-                }););
+                CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, CC1D_DISPATCH_BOOL(full, kWhole, {
+                    launch_k(fwd_cf_wide_kernel<T, W, kSilu, kCfVecs / 2, kWhole>, dim3((unsigned)wctas), dim3(CC1D_FWD_WIDE_THREADS), 0, stream, a);
+                });););
             }
         } else
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,

@@ -228,12 +228,14 @@ def test_causal_conv1d_wide_dim(seqlen, width, itype, channel_last):
 @pytest.mark.parametrize("itype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("width", [2, 3, 4])
 @pytest.mark.parametrize("silu", [False, True])
-@pytest.mark.parametrize("batch,dim,seqlen", [(1, 8, 1024), (2, 24, 2048), (1, 3, 8192), (3, 5, 3072)])
+@pytest.mark.parametrize("batch,dim,seqlen", [(1, 8, 1024), (2, 24, 2048), (1, 3, 8192), (3, 5, 3072),
+                                              (2, 24, 2000), (1, 8, 528), (3, 5, 16), (2, 7, 1040), (1, 3, 8176)])
 def test_channel_first_rows_of_whole_groups(batch, dim, seqlen, silu, width, itype):
-    """16-bit channel-first rows made of whole 1024-element groups on 32-byte aligned rows take the
-    backward kernel that moves 32 bytes per lane; few rows, so that rows are cut into several warp
+    """16-bit channel-first rows whose length is a multiple of 16 elements on 32-byte aligned rows take
+    the kernels that move 32 bytes per lane (whole 1024-element groups: the variant without bounds
+    tests; otherwise lanes past the row end idle); few rows, so that rows are cut into several warp
     units (the seeded right halo).  Checked against the CPU oracle, and bit-for-bit against the same
-    problem placed 16 bytes off a 32-byte boundary (which takes the 16-byte kernel)."""
+    problem placed 16 bytes off a 32-byte boundary (which takes the 16-byte kernels)."""
     torch.manual_seed(7)
     x = torch.randn(batch, dim, seqlen, device=DEV, dtype=itype)
     dout = torch.randn_like(x)

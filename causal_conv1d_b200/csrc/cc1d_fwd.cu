@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(256) fwd_cf_vec_kernel(const FwdCfArgs a) {
     }
 }
 
-// ---- 16-bit I/O, rows made of whole groups, 32-byte aligned: 32 bytes per lane ----------------
+// ---- 16-bit I/O, rows of a multiple of 16 elements, 32-byte aligned: 32 bytes per lane --------
 // A lane owns slots of 16 consecutive elements (two 16-byte vectors A, B moved by one 256-bit
 // load / store; a warp instruction covers 1 KB of the row).  The arithmetic runs on fp32 pairs
 // (A[i], B[i]) (FFMA2): B's left halo is A's tail, already in the lane, so only A's halo (the

@@ -1374,11 +1374,6 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
                 for (int k = 0; k < W - 1; ++k) same = same && swin[k] == first;
                 plain = __all_sync(kFullMask, same) && plain;
             }
-            int sid[kTmaRows];       // per-row ids: only the masked paths look at them
-            if (!plain) {
-                #pragma unroll
-                for (int r = 0; r < kTmaRows; ++r) sid[r] = kSeqIdx ? __shfl_sync(kFullMask, my_id, r) : 0;
-            }
             if (plain) {
                 #pragma unroll
                 for (int r = 0; r < kTmaRows; ++r) {
@@ -1387,16 +1382,20 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
                         xr, dr, 0, true, lane_ok, false, xwin, gwin, swin, wv, wy, bv, dw, nullptr, 0, optr + r * os, nullptr);
                 }
             } else if (steady) {
-                #pragma unroll
+                // a stage that holds a sequence boundary: rare, so kept compact (not unrolled) -- the
+                // kernel's code size is what the steady-state loop above pays for in instruction fetches
+                #pragma unroll 1
                 for (int r = 0; r < kTmaRows; ++r) {
+                    const int sid = kSeqIdx ? __shfl_sync(kFullMask, my_id, r) : 0;
                     const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = dout_row(r);
                     bwd_cl_position_impl<T, W, C, kSilu, kSeqIdx, kTanh>(
-                        xr, dr, sid[r], true, lane_ok, false, xwin, gwin, swin, wv, wy, bv, dw, nullptr, 0, optr + r * os, nullptr);
+                        xr, dr, sid, true, lane_ok, false, xwin, gwin, swin, wv, wy, bv, dw, nullptr, 0, optr + r * os, nullptr);
                 }
             } else {
                 #pragma unroll
                 for (int r = 0; r < kTmaRows; ++r) {
                     const int i = base + r;               // position t0 + i
+                    const int sid = kSeqIdx ? __shfl_sync(kFullMask, my_id, r) : 0;
                     if (i < n_ext) {
                         const R xr = lds_raw<R>(xsrc + r * kRowBytes), dr = dout_row(r);
                         const int q = t0 + i - (W - 1);   // dx position produced now
@@ -1405,7 +1404,7 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
                         const T *df = (dfin_base != nullptr && q >= L - (W - 1)) ? dfin_base + (q - (L - (W - 1))) * a.df_ls : nullptr;
                         T *di = st_di ? dinit_base + (q + (W - 1)) * a.di_ls : nullptr;
                         bwd_cl_position<T, W, C, kSilu, kSeqIdx, kTanh>(
-                            xr, dr, sid[r], i < n_in, st_dx, st_di, xwin, gwin, swin, wv, wy, bv, dw, df, a.df_cs, optr + r * os, di);
+                            xr, dr, sid, i < n_in, st_dx, st_di, xwin, gwin, swin, wv, wy, bv, dw, df, a.df_cs, optr + r * os, di);
                     }
                 }
             }
@@ -1454,6 +1453,8 @@ bwd_cl_tma_kernel(const BwdClArgs a, const __grid_constant__ CUtensorMap xmap, c
 }
 
 int pick_tokens_per_thread(int64_t batch, int64_t ncols, int64_t seqlen, int sms, int max_tpt);
+int pick_chunk_tokens(int64_t batch, int64_t ncolblk, int64_t seqlen, int warps_per_cta, int64_t resident_ctas,
+                      const int *candidates, int n, int overhead);
 
 struct ClPlan {
     int tpt;
@@ -1467,6 +1468,14 @@ static ClPlan plan_channel_last(const cc1d_bwd_params &p) {
     pl.tpt = pick_tokens_per_thread(p.batch, ncols, p.seqlen, kTilingSMs / 2, 128);
     pl.ncols = (uint32_t)ncols;
     pl.ncolblk = (uint32_t)((ncols + 31) / 32);
+    if (pl.tpt == 128 && p.itype != CC1D_F32) {
+        // 16-bit (TMA) kernel on a problem of several waves: pick the chunk length by the waves it makes.
+        // Measured, bf16: (1,5376,32768) 128 tokens (6.05 waves) 204 us, 160 tokens (4.9 waves) 196 us;
+        // (8,5120,2048) 128 tokens (2.9 waves) 103 us, 160 tokens 116 us.  Multiples of 8 tokens: a
+        // channel-first dout box starts at the chunk's first token.
+        static const int kChunks[] = {128, 160, 192};
+        pl.tpt = pick_chunk_tokens(p.batch, pl.ncolblk, p.seqlen, kBwdClRows, (int64_t)kTilingSMs * CC1D_BWD_CL_MINBLK, kChunks, 3, 16);
+    }
     const int64_t chunks = (p.seqlen + pl.tpt - 1) / pl.tpt;
     pl.ngroups = (uint32_t)((chunks + kBwdClRows - 1) / kBwdClRows);
     return pl;

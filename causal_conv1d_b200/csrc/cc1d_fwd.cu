@@ -666,6 +666,25 @@ int pick_tokens_per_thread(int64_t batch, int64_t ncols, int64_t seqlen, int sms
     return tpt;
 }
 
+// Chunk length (tokens a warp walks) for the TMA kernels on a problem of several waves.  The grid runs in
+// waves of `resident_ctas`; a chunk costs its tokens plus about `overhead` tokens of prologue, halo and
+// epilogue; the candidate with the smallest waves x (tokens + overhead) wins, the first one on a tie.
+int pick_chunk_tokens(int64_t batch, int64_t ncolblk, int64_t seqlen, int warps_per_cta, int64_t resident_ctas,
+                      const int *candidates, int n, int overhead) {
+    int best = candidates[0];
+    double best_cost = 0.0;
+    for (int i = 0; i < n; ++i) {
+        const int tpt = candidates[i];
+        const int64_t chunks = (seqlen + tpt - 1) / tpt;
+        const int64_t groups = (chunks + warps_per_cta - 1) / warps_per_cta;
+        const double ctas = (double)ncolblk * (double)groups * (double)batch;
+        const double waves = ceil(ctas / (double)resident_ctas);
+        const double cost = waves * (double)(tpt + overhead);
+        if (i == 0 || cost < best_cost) { best = tpt; best_cost = cost; }
+    }
+    return best;
+}
+
 int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream) {
     if (p.batch == 0 || p.dim == 0 || p.seqlen == 0) return CC1D_OK;
     // token positions are 32-bit integers in the kernels (chunk starts plus a halo must not wrap)
@@ -701,6 +720,12 @@ int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream) {
         make_channel_last_tensor_map(&xmap, p.itype, p.x, p.dim, p.seqlen, p.batch, p.x_l_stride, p.x_batch_stride)) {
         // each warp keeps kTmaStages boxes in flight, so fewer and longer chunks fill the machine
         a.tpt = pick_tokens_per_thread(p.batch, ncols, p.seqlen, sms / 2, CC1D_TMA_TPT);
+        if (a.tpt == 64) {
+            // several waves: measured, bf16 (8,5120,2048): 64 tokens (4.3 waves) 61.4 us, 48 tokens (5.95
+            // waves) 57.6 us; (1,5376,32768): 114.3-114.4 us with 48, 56 and 64 tokens
+            static const int kChunks[] = {64, 56, 48};
+            a.tpt = pick_chunk_tokens(p.batch, a.ncolblk, p.seqlen, kTmaWarps, (int64_t)sms * CC1D_FWD_TMA_MINBLK, kChunks, 3, 8);
+        }
         const int64_t tchunks = (p.seqlen + a.tpt - 1) / a.tpt;
         a.ngroups = (uint32_t)((tchunks + kTmaWarps - 1) / kTmaWarps);
         const uint64_t tctas = (uint64_t)a.ncolblk * a.ngroups * (uint64_t)p.batch;

@@ -95,9 +95,12 @@ def test_bwd_workspace_and_rejects(lib):
     assert lib.cc1d_bwd(ctypes.byref(p), None) == 1
     p.width = 9
     assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(p)) == 0
-    # channel-last problem: partial rows per (batch, group of 4 chunks of 128 tokens)
+    # channel-last problem: partial rows per (batch, group of 4 chunks); 16-bit I/O picks the chunk
+    # length by the waves of CTAs it makes (here 160 tokens: 52 groups), fp32 keeps 128 tokens
     q = cabi.BwdParams(itype=cabi.BF16, wtype=cabi.BF16, width=4, silu=1, batch=1, dim=5376, seqlen=32768,
                        x=FAKE, x_batch_stride=5376 * 32768, x_c_stride=1, x_l_stride=5376)
+    assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(q)) == 52 * 5376 * 5 * 4
+    q.itype = cabi.F32
     assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(q)) == 64 * 5376 * 5 * 4
 
 

@@ -500,6 +500,9 @@ __device__ __forceinline__ void st_stream32(void *p, const uint4 &a, const uint4
 #ifndef CC1D_BWD_WIDE_PREFETCH
 #define CC1D_BWD_WIDE_PREFETCH 0   // 1: the next group's vectors are requested before the current group is computed
 #endif
+#ifndef CC1D_BWD_WIDE_L2PF
+#define CC1D_BWD_WIDE_L2PF 1       // steps asked into L2 by bulk prefetches ahead of the step being loaded (0: none)
+#endif
 constexpr int kWideSlots = kCfVecs / 2;       // same group size (and partial rows) as the 16-byte kernel
 constexpr uint32_t kWideSlotElems = 32 * 16;
 
@@ -529,6 +532,12 @@ __device__ __forceinline__ void wide_load(WideGroup<kSlots> &r, const T *__restr
         const uint2 t = *reinterpret_cast<const uint2 *>(xr + gs - 4);
         r.cz = t.x; r.cw = t.y;
     }
+}
+
+// `bytes` (a multiple of 16) from the 16-byte aligned address p into L2: issued by one thread, holds no
+// register and no shared memory, completes on its own.
+__device__ __forceinline__ void l2_prefetch_bulk(const void *p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(p), "r"(bytes) : "memory");
 }
 
 template <typename T, int W, bool kSilu, int kSlots, bool kWhole>
@@ -616,6 +625,24 @@ __global__ void __launch_bounds__(CC1D_BWD_WIDE_THREADS, CC1D_BWD_WIDE_MINBLK) b
         const uint32_t s0 = g0 * (kSlots / kStep), s1 = g1 * (kSlots / kStep);
         WideGroup<kStep> cur;
         wide_load<T, kStep, kWhole>(cur, xr, dr, s1 - 1, lane, a.seqlen);
+        // A warp cannot hold the next step's vectors in registers while it computes this one, so its loads
+        // come after the arithmetic and would wait on DRAM; instead one lane asks the step after the one
+        // being loaded into L2 (2 x 2 KB), where those loads then find it.
+        auto prefetch_step = [&](uint32_t s) {
+            if (CC1D_BWD_WIDE_L2PF > 0 && !kPrefetch && lane == 0) {
+                const uint32_t e0 = s * (kStep * kWideSlotElems);
+                uint32_t n = kStep * kWideSlotElems;
+                if (!kWhole) n = e0 >= a.seqlen ? 0u : (a.seqlen - e0 < n ? a.seqlen - e0 : n);
+                if (n > 0) {
+                    l2_prefetch_bulk(xr + e0, n * (uint32_t)sizeof(T));
+                    l2_prefetch_bulk(dr + e0, n * (uint32_t)sizeof(T));
+                }
+            }
+        };
+        #pragma unroll
+        for (uint32_t d = 1; d <= CC1D_BWD_WIDE_L2PF; ++d) {
+            if (s1 - 1 >= s0 + d) prefetch_step(s1 - 1 - d);
+        }
 
         float wv[W], wy[W];
         constexpr float pre = ActGrad<kTanh>::kPre, post = 1.f / ActGrad<kTanh>::kGScale;
@@ -660,6 +687,7 @@ __global__ void __launch_bounds__(CC1D_BWD_WIDE_THREADS, CC1D_BWD_WIDE_MINBLK) b
                 wide_group<T, W, kSilu, kStep, kWhole>(cur, wv, wy, by, gfirst, dw2, db2, dxr, s, lane, a.seqlen);
                 if (s == s0) break;
                 wide_load<T, kStep, kWhole>(cur, xr, dr, s - 1, lane, a.seqlen);
+                if (s - 1 >= s0 + CC1D_BWD_WIDE_L2PF) prefetch_step(s - 1 - CC1D_BWD_WIDE_L2PF);
             }
         }
 

@@ -1548,14 +1548,22 @@ int launch_bwd_channel_last(const cc1d_bwd_params &p, cudaStream_t stream) {
 #if CC1D_BWD_CL_TMA
         CUtensorMap xmap, dmap;
         const int row_bytes = 32 * kBwdClC * elem_size(p.itype);
-        // 16-bit I/O only: fp32 stages would leave room for a single CTA per SM
-        if (p.itype != CC1D_F32 && p.seqlen < (1ll << 31) - 16 && p.batch < (1ll << 31) &&
+        // fp32 stages are twice as large (2 CTAs per SM instead of 3): still 3 % ahead of the register-prefetch
+        // kernel; a channel-first dout is read in place for 16-bit types only
+        if ((p.itype != CC1D_F32 || !dout_cf) && p.seqlen < (1ll << 31) - 16 && p.batch < (1ll << 31) &&
             make_channel_last_tensor_map(&xmap, p.itype, p.x, p.dim, p.seqlen, p.batch, p.x_l_stride, p.x_batch_stride, row_bytes) &&
             (dout_cf ? make_channel_first_tensor_map(&dmap, p.itype, p.dout, p.seqlen, p.dim, p.batch, p.dout_c_stride,
                                                      p.dout_batch_stride, kTmaRows, 32 * kBwdClC)
                      : make_channel_last_tensor_map(&dmap, p.itype, p.dout, p.dim, p.seqlen, p.batch, p.dout_l_stride,
                                                     p.dout_batch_stride, row_bytes))) {
-            if (p.itype == CC1D_BF16) {
+            if (p.itype == CC1D_F32) {
+                using T = float;
+                CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
+                        auto kernel = bwd_cl_tma_kernel<T, W, kSilu, kSeqIdx, false>;
+                        allow_dynamic_smem(reinterpret_cast<const void *>(kernel), BwdTma<T>::kSmem);
+                        launch_k(kernel, dim3((unsigned)ctas), dim3(32 * kBwdClRows), BwdTma<T>::kSmem, stream, a, xmap, dmap);
+                    });););
+            } else if (p.itype == CC1D_BF16) {
                 using T = __nv_bfloat16;
                 CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu, CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx,
                     CC1D_DISPATCH_BOOL(dout_cf, kDoutCf, {

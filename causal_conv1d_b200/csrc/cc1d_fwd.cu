@@ -714,9 +714,9 @@ int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream) {
     const int64_t chunks = (p.seqlen + a.tpt - 1) / a.tpt;
     a.ngroups = (uint32_t)((chunks + kClRows - 1) / kClRows);
 #if CC1D_FWD_CL_TMA
-    // TMA path: 16-bit I/O only (the fp32 kernel is already at the memory roof without it)
+    // TMA path (all I/O types; fp32 (8,5120,2048): 105 us against 120 us with the register-prefetch kernel)
     CUtensorMap xmap;
-    if (p.itype != CC1D_F32 && p.seqlen < (1ll << 31) && p.batch < (1ll << 31) &&
+    if (p.seqlen < (1ll << 31) && p.batch < (1ll << 31) &&
         make_channel_last_tensor_map(&xmap, p.itype, p.x, p.dim, p.seqlen, p.batch, p.x_l_stride, p.x_batch_stride)) {
         // each warp keeps kTmaStages boxes in flight, so fewer and longer chunks fill the machine
         a.tpt = pick_tokens_per_thread(p.batch, ncols, p.seqlen, sms / 2, CC1D_TMA_TPT);

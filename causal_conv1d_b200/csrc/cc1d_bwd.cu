@@ -501,7 +501,7 @@ __device__ __forceinline__ void st_stream32(void *p, const uint4 &a, const uint4
 #define CC1D_BWD_WIDE_PREFETCH 0   // 1: the next group's vectors are requested before the current group is computed
 #endif
 #ifndef CC1D_BWD_WIDE_L2PF
-#define CC1D_BWD_WIDE_L2PF 1       // steps asked into L2 by bulk prefetches ahead of the step being loaded (0: none)
+#define CC1D_BWD_WIDE_L2PF 1       // steps asked into L2 ahead of the step being loaded (0: none)
 #endif
 constexpr int kWideSlots = kCfVecs / 2;       // same group size (and partial rows) as the 16-byte kernel
 constexpr uint32_t kWideSlotElems = 32 * 16;
@@ -532,12 +532,6 @@ __device__ __forceinline__ void wide_load(WideGroup<kSlots> &r, const T *__restr
         const uint2 t = *reinterpret_cast<const uint2 *>(xr + gs - 4);
         r.cz = t.x; r.cw = t.y;
     }
-}
-
-// `bytes` (a multiple of 16) from the 16-byte aligned address p into L2: issued by one thread, holds no
-// register and no shared memory, completes on its own.
-__device__ __forceinline__ void l2_prefetch_bulk(const void *p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(p), "r"(bytes) : "memory");
 }
 
 template <typename T, int W, bool kSilu, int kSlots, bool kWhole>
@@ -626,17 +620,15 @@ __global__ void __launch_bounds__(CC1D_BWD_WIDE_THREADS, CC1D_BWD_WIDE_MINBLK) b
         WideGroup<kStep> cur;
         wide_load<T, kStep, kWhole>(cur, xr, dr, s1 - 1, lane, a.seqlen);
         // A warp cannot hold the next step's vectors in registers while it computes this one, so its loads
-        // come after the arithmetic and would wait on DRAM; instead one lane asks the step after the one
-        // being loaded into L2 (2 x 2 KB), where those loads then find it.
+        // come after the arithmetic and would wait on DRAM; instead the step after the one being loaded is
+        // asked into L2, where those loads then find it: one 128-byte line per lane, lanes 0-15 the 2 KB of
+        // x, lanes 16-31 the 2 KB of dout.  Holds no register and no shared memory.
         auto prefetch_step = [&](uint32_t s) {
-            if (CC1D_BWD_WIDE_L2PF > 0 && !kPrefetch && lane == 0) {
-                const uint32_t e0 = s * (kStep * kWideSlotElems);
-                uint32_t n = kStep * kWideSlotElems;
-                if (!kWhole) n = e0 >= a.seqlen ? 0u : (a.seqlen - e0 < n ? a.seqlen - e0 : n);
-                if (n > 0) {
-                    l2_prefetch_bulk(xr + e0, n * (uint32_t)sizeof(T));
-                    l2_prefetch_bulk(dr + e0, n * (uint32_t)sizeof(T));
-                }
+            if (CC1D_BWD_WIDE_L2PF > 0 && !kPrefetch) {
+                static_assert(kPrefetch || kStep * kWideSlotElems * sizeof(T) == 16 * 128, "16 lines per tensor and step");
+                const uint32_t e = s * (kStep * kWideSlotElems) + (lane & 15) * 64;
+                const T *p = (lane < 16 ? xr : dr) + e;
+                if (kWhole || e < a.seqlen) asm volatile("prefetch.global.L2 [%0];" :: "l"(p));
             }
         };
         #pragma unroll

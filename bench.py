@@ -38,7 +38,7 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes of one launch of the backward kernel, from an ncu capture of this workload:
 # dram__bytes_read.sum + dram__bytes_write.sum (write-back of the last ~26 MB of dx is still
 # pending in L2 when the counter stops)
-BWD_KERNEL_DRAM_TRAFFIC_BYTES = 335688704 + 142050816
+BWD_KERNEL_DRAM_TRAFFIC_BYTES = 335708416 + 141833984
 
 
 def algorithmic_bytes(batch):

@@ -8,9 +8,9 @@
 // aligned rows take fwd_cf_wide_kernel: 32 bytes per lane (256-bit loads and stores),
 // arithmetic on fp32 pairs, half of the halos inside the lane.
 //
-// Channel-last (x[b, :, t] contiguous): a thread owns one 16-byte vector of channels and
-// slides down `tpt` consecutive tokens keeping the last width-1 vectors in registers; a
-// warp covers 512 contiguous bytes of one token.  seq_idx masking, initial_states (halo of
+// Channel-last (x[b, :, t] contiguous): a thread owns 4 adjacent channels (TMA kernel; one 16-byte
+// vector in the kernel kept for tensors without a tensor map) and slides down `tpt` consecutive
+// tokens keeping the last width-1 vectors in registers; a warp covers 128 channels of one token.  seq_idx masking, initial_states (halo of
 // the first chunk) and final_states (the window left after the last token) ride along.
 //
 // Replaces csrc/causal_conv1d_fwd.cu:46-137 (channel-first) and :205-348 (channel-last)
@@ -349,7 +349,10 @@ struct FwdClArgs {
 #define CC1D_FWD_CL_TMA 1
 #endif
 #ifndef CC1D_FWD_TMA_MINBLK
-#define CC1D_FWD_TMA_MINBLK 4        // 128 registers: 4 CTAs (16 warps) per SM
+#define CC1D_FWD_TMA_MINBLK 4        // fp32 I/O: 4 CTAs (16 warps) per SM
+#endif
+#ifndef CC1D_FWD_TMA_MINBLK_16BIT
+#define CC1D_FWD_TMA_MINBLK_16BIT 5  // 16-bit I/O: 94 registers, 5 CTAs (20 warps) per SM
 #endif
 constexpr int kClRows = 8;    // token chunks per CTA (threadIdx.y)
 constexpr int kClUnroll = 4;  // tokens per block: loads of one block are in flight while the previous computes
@@ -513,13 +516,32 @@ __global__ void __launch_bounds__(32 * kClRows, 2) fwd_cl_kernel(const FwdClArgs
 #endif
 constexpr int kTmaWarps = CC1D_TMA_WARPS;
 constexpr int kTmaStages = CC1D_TMA_STAGES;
-constexpr size_t kFwdTmaSmem = (size_t)kTmaWarps * kTmaStages * kTmaStageBytes + (size_t)kTmaWarps * kTmaStages * 8;
+
+// A thread owns kFwdTmaC = 4 adjacent channels (8 bytes of a 16-bit tensor, 16 of an fp32 one): with 8
+// channels of a 16-bit tensor per thread the kernel needed 128 registers and ran 16 warps per SM at 0.94
+// of the copy rate on (1,5376,32768) bf16; with 4 it needs 94, runs 20 and reaches 0.99 (bit-identical).
+constexpr int kFwdTmaC = 4;
+template <typename T> struct FwdTma {
+    static constexpr int kRowBytes = 32 * kFwdTmaC * (int)sizeof(T);     // one token of a warp's strip
+    static constexpr int kStageBytes = kTmaRows * kRowBytes;
+    static constexpr size_t kSmem = (size_t)kTmaWarps * kTmaStages * kStageBytes + (size_t)kTmaWarps * kTmaStages * 8;
+    static constexpr int kMinBlocks = sizeof(T) == 4 ? CC1D_FWD_TMA_MINBLK : CC1D_FWD_TMA_MINBLK_16BIT;
+};
+template <typename R> __device__ __forceinline__ R fwd_lds(uint32_t addr);
+template <> __device__ __forceinline__ uint4 fwd_lds<uint4>(uint32_t addr) { return lds128(addr); }
+template <> __device__ __forceinline__ uint2 fwd_lds<uint2>(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
 
 template <typename T, int W, bool kSilu, bool kSeqIdx>
-__global__ void __launch_bounds__(32 * kTmaWarps, CC1D_FWD_TMA_MINBLK) fwd_cl_tma_kernel(const FwdClArgs a, const __grid_constant__ CUtensorMap xmap) {
+__global__ void __launch_bounds__(32 * kTmaWarps, FwdTma<T>::kMinBlocks)
+fwd_cl_tma_kernel(const FwdClArgs a, const __grid_constant__ CUtensorMap xmap) {
     pdl_wait();
-    constexpr int C = Elem<T>::kVec;
+    constexpr int C = kFwdTmaC;
     constexpr bool kTanh = kSilu && UseTanhSilu<T>::value;
+    constexpr int kTmaRowBytes = FwdTma<T>::kRowBytes, kTmaStageBytes = FwdTma<T>::kStageBytes;   // of this I/O type
     using R = Raw<T, C>;
     extern __shared__ __align__(1024) unsigned char smem[];
 
@@ -600,7 +622,7 @@ __global__ void __launch_bounds__(32 * kTmaWarps, CC1D_FWD_TMA_MINBLK) fwd_cl_tm
             g_tma_wait_expired = 1;                    // never expected; leave without touching more memory
             return;
         }
-        const uint32_t src = ring + s * kTmaStageBytes + lane * 16;
+        const uint32_t src = ring + s * kTmaStageBytes + lane * (C * (int)sizeof(T));
         // one test per box instead of one per token: a box whose tokens and window all carry the
         // same non-negative sequence id needs no masking at all (warp-uniform branch)
         bool plain = rows >= kTmaRows;
@@ -619,20 +641,20 @@ __global__ void __launch_bounds__(32 * kTmaWarps, CC1D_FWD_TMA_MINBLK) fwd_cl_tm
         if (plain) {
             #pragma unroll
             for (int r = 0; r < kTmaRows; ++r) {
-                const R raw = lds128(src + r * kTmaRowBytes);
+                const R raw = fwd_lds<R>(src + r * kTmaRowBytes);
                 fwd_cl_token_impl<T, W, C, kSilu, false, kTanh>(raw, 0, win, sw, wv, bv, optr + r * os, lane_ok);
             }
         } else if (rows >= kTmaRows) {
             #pragma unroll
             for (int r = 0; r < kTmaRows; ++r) {
-                const R raw = lds128(src + r * kTmaRowBytes);
+                const R raw = fwd_lds<R>(src + r * kTmaRowBytes);
                 fwd_cl_token_impl<T, W, C, kSilu, kSeqIdx, kTanh>(raw, sid[r], win, sw, wv, bv, optr + r * os, lane_ok);
             }
         } else {
             #pragma unroll
             for (int r = 0; r < kTmaRows; ++r) {
                 if (r < rows) {
-                    const R raw = lds128(src + r * kTmaRowBytes);
+                    const R raw = fwd_lds<R>(src + r * kTmaRowBytes);
                     fwd_cl_token<T, W, C, kSilu, kSeqIdx, kTanh>(raw, sid[r], win, sw, wv, bv, optr + r * os, lane_ok);
                 }
             }
@@ -714,27 +736,39 @@ int launch_fwd_channel_last(const cc1d_fwd_params &p, cudaStream_t stream) {
     const int64_t chunks = (p.seqlen + a.tpt - 1) / a.tpt;
     a.ngroups = (uint32_t)((chunks + kClRows - 1) / kClRows);
 #if CC1D_FWD_CL_TMA
-    // TMA path (all I/O types; fp32 (8,5120,2048): 105 us against 120 us with the register-prefetch kernel)
+    // TMA path, 4 channels per thread for every I/O type (fp32 (8,5120,2048): 105 us against 120 us with the
+    // register-prefetch kernel below, which stays for tensors the driver refuses a map for)
     CUtensorMap xmap;
     if (p.seqlen < (1ll << 31) && p.batch < (1ll << 31) &&
-        make_channel_last_tensor_map(&xmap, p.itype, p.x, p.dim, p.seqlen, p.batch, p.x_l_stride, p.x_batch_stride)) {
+        make_channel_last_tensor_map(&xmap, p.itype, p.x, p.dim, p.seqlen, p.batch, p.x_l_stride, p.x_batch_stride,
+                                     32 * kFwdTmaC * elem_size(p.itype))) {
+        FwdClArgs t = a;
+        const int64_t tcols = p.dim / kFwdTmaC;
+        t.ncols = (uint32_t)tcols;
+        t.ncolblk = (uint32_t)((tcols + 31) / 32);
         // each warp keeps kTmaStages boxes in flight, so fewer and longer chunks fill the machine
-        a.tpt = pick_tokens_per_thread(p.batch, ncols, p.seqlen, sms / 2, CC1D_TMA_TPT);
-        if (a.tpt == 64) {
-            // several waves: measured, bf16 (8,5120,2048): 64 tokens (4.3 waves) 61.4 us, 48 tokens (5.95
-            // waves) 57.6 us; (1,5376,32768): 114.3-114.4 us with 48, 56 and 64 tokens
-            static const int kChunks[] = {64, 56, 48};
-            a.tpt = pick_chunk_tokens(p.batch, a.ncolblk, p.seqlen, kTmaWarps, (int64_t)sms * CC1D_FWD_TMA_MINBLK, kChunks, 3, 8);
+        if (p.itype == CC1D_F32) {
+            t.tpt = pick_tokens_per_thread(p.batch, tcols, p.seqlen, sms / 2, CC1D_TMA_TPT);
+            if (t.tpt == 64) {
+                // several waves: pick the chunk by the waves it makes (measured with 8 channels per thread, bf16
+                // (8,5120,2048): 64 tokens, 4.3 waves, 61.4 us; 48 tokens, 5.95 waves, 57.6 us)
+                static const int kChunks[] = {64, 56, 48};
+                t.tpt = pick_chunk_tokens(p.batch, t.ncolblk, p.seqlen, kTmaWarps, (int64_t)sms * CC1D_FWD_TMA_MINBLK, kChunks, 3, 8);
+            }
+        } else {
+            // measured, bf16, 48 / 56 / 64 / 80 tokens: (1,5376,32768) 108.9 / 109.1 / 109.3 / 110.9 us,
+            // (8,5120,2048) 54.7 / 55.5 / 55.9 / 57.2 us
+            t.tpt = pick_tokens_per_thread(p.batch, tcols, p.seqlen, sms / 2, 48);
         }
-        const int64_t tchunks = (p.seqlen + a.tpt - 1) / a.tpt;
-        a.ngroups = (uint32_t)((tchunks + kTmaWarps - 1) / kTmaWarps);
-        const uint64_t tctas = (uint64_t)a.ncolblk * a.ngroups * (uint64_t)p.batch;
+        const int64_t tchunks = (p.seqlen + t.tpt - 1) / t.tpt;
+        t.ngroups = (uint32_t)((tchunks + kTmaWarps - 1) / kTmaWarps);
+        const uint64_t tctas = (uint64_t)t.ncolblk * t.ngroups * (uint64_t)p.batch;
         if (tctas >= (1ull << 31)) return CC1D_ERR_TOO_LARGE;
         CC1D_DISPATCH_ITYPE(p.itype, CC1D_DISPATCH_WIDTH(p.width, CC1D_DISPATCH_BOOL(p.silu != 0, kSilu,
             CC1D_DISPATCH_BOOL(p.seq_idx != nullptr, kSeqIdx, {
                 auto kernel = fwd_cl_tma_kernel<T, W, kSilu, kSeqIdx>;
-                allow_dynamic_smem(reinterpret_cast<const void *>(kernel), kFwdTmaSmem);
-                launch_k(kernel, dim3((unsigned)tctas), dim3(32 * kTmaWarps), kFwdTmaSmem, stream, a, xmap);
+                allow_dynamic_smem(reinterpret_cast<const void *>(kernel), FwdTma<T>::kSmem);
+                launch_k(kernel, dim3((unsigned)tctas), dim3(32 * kTmaWarps), FwdTma<T>::kSmem, stream, t, xmap);
             }););););
         return check_launch();
     }

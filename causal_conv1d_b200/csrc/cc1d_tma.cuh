@@ -1,9 +1,9 @@
 // TMA (cp.async.bulk.tensor) + mbarrier helpers for the channel-last kernels (sm_100a).
 //
-// The channel-last tensors are walked token by token; a warp owns a 512-byte-wide strip of
-// channels.  Instead of holding the in-flight loads in registers, one lane of the warp asks the
-// TMA unit for a box of [kTmaRows tokens x 512 bytes] into shared memory and every lane then
-// reads its 16 bytes per token with ld.shared.  Bytes in flight are bounded by shared memory,
+// The channel-last tensors are walked token by token; a warp owns a strip of 128 channels (256
+// or 512 bytes wide).  Instead of holding the in-flight loads in registers, one lane of the warp
+// asks the TMA unit for a box of [kTmaRows tokens x strip] into shared memory and every lane then
+// reads its 8 or 16 bytes per token with ld.shared.  Bytes in flight are bounded by shared memory,
 // not by registers or occupancy.  No multicast, no cluster: every box is this GPU's own memory
 // going to this CTA's own shared memory.
 #pragma once
@@ -15,7 +15,7 @@
 namespace cc1d {
 
 constexpr int kTmaRows = 8;          // tokens per box
-constexpr int kTmaRowBytes = 512;    // 32 lanes x 16 bytes
+constexpr int kTmaRowBytes = 512;    // default strip width: 32 lanes x 16 bytes
 constexpr int kTmaStageBytes = kTmaRows * kTmaRowBytes;
 constexpr uint32_t kTmaSpinLimit = 1u << 22;   // bounded wait: try_wait attempts before giving up
 

@@ -463,87 +463,97 @@ def run_b200(args):
     # Three streams, the way a host-fed pipeline is normally written: step i's host->device copies,
     # step i-1's kernels and step i-2's device->host copies overlap (PCIe is full duplex).  Every
     # step still pays for all of its own copies inside the timed region.
-    # With --e2e-copy-streams n every large tensor travels as n batch slices on n streams per direction
-    # (several copy engines per direction keep more of the PCIe link busy than one).
-    ncs = max(1, min(B, args.e2e_copy_streams))
-    cuts = [(k * B // ncs, (k + 1) * B // ncs) for k in range(ncs)]
+    # With n copy streams every large tensor travels as n batch slices on n streams per direction.  Which n
+    # keeps more of the host link busy differs from host to host (measured: 1 stream 116 GB/s against 111 GB/s
+    # with 2 on one box, 92 against 107-110 on another), so --e2e-copy-streams 0 (the default) tries 1 and 2 for
+    # a few steps outside the timed region and takes the faster.
     s_run = torch.cuda.Stream()
-    s_ins, s_outs = [torch.cuda.Stream() for _ in range(ncs)], [torch.cuda.Stream() for _ in range(ncs)]
-    s_in, s_out = s_ins[0], s_outs[0]
-    slots = [{"x": torch.empty(B, DIM, SEQLEN, device=dev, dtype=torch.bfloat16),
-              "dout": torch.empty(B, DIM, SEQLEN, device=dev, dtype=torch.bfloat16),
-              "in_done": [torch.cuda.Event() for _ in range(ncs)], "run_done": torch.cuda.Event(),
-              "out_done": [torch.cuda.Event() for _ in range(ncs)]}
-             for _ in range(2)]
+    dev_slots = [(torch.empty(B, DIM, SEQLEN, device=dev, dtype=torch.bfloat16),
+                  torch.empty(B, DIM, SEQLEN, device=dev, dtype=torch.bfloat16)) for _ in range(2)]
     wps = [weight.clone().requires_grad_() for _ in range(2)]
     bps = [bias.clone().requires_grad_() for _ in range(2)]
 
-    def e2e_step(i):
-        sl, wq, bq = slots[i % 2], wps[i % 2], bps[i % 2]
-        for j, (lo, hi) in enumerate(cuts):
-            st = s_ins[j]
-            with torch.cuda.stream(st):
-                st.wait_event(sl["run_done"])        # the slot's previous kernels have read x / dout
-                sl["x"][lo:hi].copy_(hx[lo:hi], non_blocking=True)
-                sl["dout"][lo:hi].copy_(hdout[lo:hi], non_blocking=True)
-                sl["in_done"][j].record(st)
-        with torch.cuda.stream(s_run):
-            for j in range(ncs):
-                s_run.wait_event(sl["in_done"][j])
-                s_run.wait_event(sl["out_done"][j])  # the slot's previous results have left the device
-            xd = sl["x"].detach().requires_grad_()
-            wq.grad = bq.grad = None
-            out = causal_conv1d_fn(xd, wq, bq, activation="silu")
-            out.backward(sl["dout"])
-            if world > 1:
-                dist.all_reduce(wq.grad)
-                dist.all_reduce(bq.grad)
-            sl["run_done"].record()
-        od, dxg = out.detach(), xd.grad
-        for j, (lo, hi) in enumerate(cuts):
-            st = s_outs[j]
-            with torch.cuda.stream(st):
-                st.wait_event(sl["run_done"])
-                for t in (od, dxg, wq.grad, bq.grad):
-                    t.record_stream(st)
-                hout[lo:hi].copy_(od[lo:hi], non_blocking=True)
-                hdx[lo:hi].copy_(dxg[lo:hi], non_blocking=True)
-                if j == 0:
-                    hdw.copy_(wq.grad, non_blocking=True)
-                    hdb.copy_(bq.grad, non_blocking=True)
-                sl["out_done"][j].record(st)
+    def run_e2e(ncs, steps, warm=2):
+        cuts = [(k * B // ncs, (k + 1) * B // ncs) for k in range(ncs)]
+        s_ins, s_outs = [torch.cuda.Stream() for _ in range(ncs)], [torch.cuda.Stream() for _ in range(ncs)]
+        slots = [{"x": dev_slots[k][0], "dout": dev_slots[k][1],
+                  "in_done": [torch.cuda.Event() for _ in range(ncs)], "run_done": torch.cuda.Event(),
+                  "out_done": [torch.cuda.Event() for _ in range(ncs)]} for k in range(2)]
 
-    all_streams = [s_run] + s_ins + s_outs
+        def e2e_step(i):
+            sl, wq, bq = slots[i % 2], wps[i % 2], bps[i % 2]
+            for j, (lo, hi) in enumerate(cuts):
+                st = s_ins[j]
+                with torch.cuda.stream(st):
+                    st.wait_event(sl["run_done"])        # the slot's previous kernels have read x / dout
+                    sl["x"][lo:hi].copy_(hx[lo:hi], non_blocking=True)
+                    sl["dout"][lo:hi].copy_(hdout[lo:hi], non_blocking=True)
+                    sl["in_done"][j].record(st)
+            with torch.cuda.stream(s_run):
+                for j in range(ncs):
+                    s_run.wait_event(sl["in_done"][j])
+                    s_run.wait_event(sl["out_done"][j])  # the slot's previous results have left the device
+                xd = sl["x"].detach().requires_grad_()
+                wq.grad = bq.grad = None
+                out = causal_conv1d_fn(xd, wq, bq, activation="silu")
+                out.backward(sl["dout"])
+                if world > 1:
+                    dist.all_reduce(wq.grad)
+                    dist.all_reduce(bq.grad)
+                sl["run_done"].record()
+            od, dxg = out.detach(), xd.grad
+            for j, (lo, hi) in enumerate(cuts):
+                st = s_outs[j]
+                with torch.cuda.stream(st):
+                    st.wait_event(sl["run_done"])
+                    for t in (od, dxg, wq.grad, bq.grad):
+                        t.record_stream(st)
+                    hout[lo:hi].copy_(od[lo:hi], non_blocking=True)
+                    hdx[lo:hi].copy_(dxg[lo:hi], non_blocking=True)
+                    if j == 0:
+                        hdw.copy_(wq.grad, non_blocking=True)
+                        hdb.copy_(bq.grad, non_blocking=True)
+                    sl["out_done"][j].record(st)
 
-    def e2e_join():
-        cur = torch.cuda.current_stream()
+        all_streams = [s_run] + s_ins + s_outs
+
+        def e2e_join():
+            cur = torch.cuda.current_stream()
+            for st in all_streams:
+                cur.wait_stream(st)
+
         for st in all_streams:
-            cur.wait_stream(st)
+            st.wait_stream(torch.cuda.current_stream())
+        for i in range(warm):
+            e2e_step(i)
+        e2e_join()
+        barrier()
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s2.record()
+        for st in all_streams:
+            st.wait_event(s2)
+        for i in range(steps):
+            e2e_step(i)
+        e2e_join()
+        e2.record()
+        barrier()
+        ms = s2.elapsed_time(e2)
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
 
-    for st in all_streams:
-        st.wait_stream(torch.cuda.current_stream())
-    for i in range(2):
-        e2e_step(i)
-    e2e_join()
-    barrier()
-    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s2.record()
-    for st in all_streams:
-        st.wait_event(s2)
-    for i in range(k_e2e):
-        e2e_step(i)
-    e2e_join()
-    e2.record()
-    barrier()
-    e2e_ms = s2.elapsed_time(e2)
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    if args.e2e_copy_streams > 0:
+        ncs = max(1, min(B, args.e2e_copy_streams))
+    else:
+        trial = {n: run_e2e(n, 4) for n in (1, 2) if n <= B}     # max over ranks: every rank picks the same n
+        ncs = min(trial, key=trial.get)
+    e2e_ms = run_e2e(ncs, k_e2e)
     e2e_value = (fwd_b + bwd_b) * world / (e2e_ms / k_e2e * 1e-3) / 1e9
     h2d = hx.numel() * ELEM + hdout.numel() * ELEM
     d2h = hout.numel() * ELEM + hdx.numel() * ELEM + hdw.numel() * ELEM + hdb.numel() * ELEM
-    del hx, hdout, hout, hdx, slots
+    del hx, hdout, hout, hdx, dev_slots
 
     # ---- the exchange step alone: NCCL all-reduce vs the one-shot peer-memory kernel --------------
     allreduce_us = None
@@ -944,8 +954,8 @@ def main():
                     help="N > 1: auto (default) = peer when peer memory can be set up on every rank, else nccl; peer: the "
                          "one-shot peer-memory all-reduce kernel after the backward; fused: the exchange inside the "
                          "backward's finishing kernel; nccl: NCCL all-reduce launched from the host")
-    ap.add_argument("--e2e-copy-streams", type=int, default=2,
-                    help="streams (batch slices in flight) per direction in the end-to-end measurement")
+    ap.add_argument("--e2e-copy-streams", type=int, default=0,
+                    help="streams (batch slices in flight) per direction in the end-to-end measurement; 0: try 1 and 2, take the faster")
     ap.add_argument("--no-graph", action="store_true", help="launch every timed step from the host instead of replaying CUDA graphs")
     ap.add_argument("--no-secondary", action="store_true", help="skip the extra workloads reported under `secondary`")
     ap.add_argument("--measure-allreduce", action="store_true",

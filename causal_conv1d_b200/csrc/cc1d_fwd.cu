@@ -10,8 +10,9 @@
 //
 // Channel-last (x[b, :, t] contiguous): a thread owns 4 adjacent channels (TMA kernel; one 16-byte
 // vector in the kernel kept for tensors without a tensor map) and slides down `tpt` consecutive
-// tokens keeping the last width-1 vectors in registers; a warp covers 128 channels of one token.  seq_idx masking, initial_states (halo of
-// the first chunk) and final_states (the window left after the last token) ride along.
+// tokens keeping the last width-1 vectors in registers; a warp covers 128 channels of one token.
+// seq_idx masking, initial_states (halo of the first chunk) and final_states (the window left
+// after the last token) ride along.
 //
 // Replaces csrc/causal_conv1d_fwd.cu:46-137 (channel-first) and :205-348 (channel-last)
 // of the reference.

@@ -102,6 +102,10 @@ def test_bwd_workspace_and_rejects(lib):
     assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(q)) == 52 * 5376 * 5 * 4
     q.itype = cabi.F32
     assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(q)) == 64 * 5376 * 5 * 4
+    # (8,5120,2048) channel-last: 128-token chunks make fewer waves than 160 here (4 groups per batch row)
+    r = cabi.BwdParams(itype=cabi.BF16, wtype=cabi.BF16, width=4, silu=1, batch=8, dim=5120, seqlen=2048,
+                       x=FAKE, x_batch_stride=5120 * 2048, x_c_stride=1, x_l_stride=5120)
+    assert lib.cc1d_bwd_workspace_bytes(ctypes.byref(r)) == 8 * 4 * 5120 * 5 * 4
 
 
 def test_bwd_rejects_seq_idx_with_states_phase_and_long_sequences(lib):

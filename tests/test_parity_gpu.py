@@ -540,7 +540,8 @@ def test_strided_slices_in_and_out(channel_last):
 
 @pytest.mark.parametrize("itype", [torch.float16, torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("mode", ["plain", "seq_idx", "states"])
-@pytest.mark.parametrize("batch,dim,seqlen", [(2, 264, 1000), (1, 128, 64), (3, 40, 333), (2, 512, 4096)])
+@pytest.mark.parametrize("batch,dim,seqlen", [(2, 264, 1000), (1, 128, 64), (3, 40, 333), (2, 512, 4096),
+                                              (1, 5376, 16384)])   # the last one is large enough for 160-token chunks
 def test_channel_first_dout_beside_channel_last_x(batch, dim, seqlen, mode, itype):
     """Autograd may hand the backward a channel-first dout although x (and so out) is channel-last.
     The 16-bit kernels read such a dout where it lies (rows 16-byte aligned: seqlen % 8 == 0), every

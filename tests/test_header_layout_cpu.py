@@ -42,3 +42,36 @@ def test_header_is_plain_c_and_matches_the_ctypes_mirror(tmp_path):
         assert int(got[cname]) == ctypes.sizeof(st), cname
         for fname, _ in st._fields_:
             assert int(got[f"{cname}.{fname}"]) == getattr(st, fname).offset, f"{cname}.{fname}"
+
+
+@pytest.mark.skipif(shutil.which("gcc") is None, reason="needs gcc")
+def test_a_plain_c_host_links_and_gets_status_codes(tmp_path):
+    """What INTEGRATION.md describes for a C host: include the header, link libcc1d.so, fill a block, call.
+    No GPU is touched: argument validation comes before any launch."""
+    libdir = os.path.join(ROOT, "causal_conv1d_b200")
+    if not os.path.exists(os.path.join(libdir, "libcc1d.so")):
+        pytest.skip("libcc1d.so not built")
+    src = tmp_path / "host.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include <string.h>
+#include "cc1d.h"
+int main(void) {
+    cc1d_fwd_params p;
+    memset(&p, 0, sizeof p);
+    p.itype = CC1D_BF16; p.wtype = CC1D_BF16; p.width = 9; p.silu = 1;
+    p.batch = 1; p.dim = 8; p.seqlen = 16;
+    p.x = (void *)0x1000; p.out = (void *)0x2000; p.weight = (void *)0x3000;
+    p.x_batch_stride = 128; p.x_c_stride = 16; p.x_l_stride = 1;
+    p.out_batch_stride = 128; p.out_c_stride = 16; p.out_l_stride = 1;
+    p.weight_c_stride = 9; p.weight_width_stride = 1;
+    int rc = cc1d_fwd(&p, (cc1d_stream_t)0);
+    printf("%d %d %s\n", cc1d_abi_version(), rc, cc1d_status_str(rc));
+    return rc == CC1D_ERR_WIDTH ? 0 : 1;
+}
+''')
+    exe = tmp_path / "host"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                    "-L", libdir, "-l:libcc1d.so", f"-Wl,-rpath,{libdir}"], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split(None, 2)
+    assert int(out[0]) >= 4 and "width" in out[2]
